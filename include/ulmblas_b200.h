@@ -1,0 +1,207 @@
+/*
+ * ulmblas_b200 -- C ABI of libulmblas_b200.so
+ *
+ * Two layers, both plain C (pointers and sizes only):
+ *
+ *  1. The BLAS entry points of ulmBLAS's Level-3 GEMM path, same symbols, same
+ *     argument meaning, same xerbla convention as the reference shims.  A
+ *     program linked against the reference's libf77blas / libcblas for these
+ *     routines links against this library unchanged.  Operand pointers may be
+ *     host pointers (staged through the device) or device pointers (used in
+ *     place); the call returns when the result is visible to the caller.
+ *
+ *  2. The device ABI behind them (ulmb200_*): operands already resident in
+ *     device memory, 64-bit sizes, an explicit stream, an int status.
+ *
+ * Matrices are column-major with a leading dimension, as in the reference.
+ * "Reference" citations are paths inside the ulmBLAS source tree.
+ */
+#ifndef ULMBLAS_B200_H
+#define ULMBLAS_B200_H 1
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* status codes returned by every ulmb200_* function                          */
+/* ------------------------------------------------------------------------ */
+enum {
+    ULMB200_OK            = 0,
+    ULMB200_BAD_ARGUMENT  = 1,   /* negative size, ld too small, bad flag      */
+    ULMB200_CUDA_ERROR    = 2,   /* a CUDA runtime / driver call failed        */
+    ULMB200_NO_DEVICE     = 3,   /* no usable sm_100 device                    */
+    ULMB200_KERNEL_FAULT  = 4,   /* a kernel's bounded wait ran out            */
+    ULMB200_TOO_LARGE     = 5    /* request exceeds a stated fixed limit       */
+};
+
+/* Status of the most recent ulmb200_* / BLAS call made by this thread.       */
+int         ulmb200_last_status(void);
+const char *ulmb200_status_string(int status);
+
+/* ------------------------------------------------------------------------ */
+/* 1. BLAS entry points (Fortran ABI: every argument by reference, 32-bit int) */
+/* ------------------------------------------------------------------------ */
+
+/* replaces F77BLAS(dgemm), interfaces/blas/F77/gemm.cc:132-249
+ * xerbla_ codes {1,2,3,4,5,8,10,13}, gemm.cc:169-199                         */
+void dgemm_(const char *transA, const char *transB,
+            const int *m, const int *n, const int *k,
+            const double *alpha, const double *A, const int *ldA,
+            const double *B, const int *ldB,
+            const double *beta, double *C, const int *ldC);
+
+/* replaces F77BLAS(sgemm), interfaces/blas/F77/gemm.cc:11-128               */
+void sgemm_(const char *transA, const char *transB,
+            const int *m, const int *n, const int *k,
+            const float *alpha, const float *A, const int *ldA,
+            const float *B, const int *ldB,
+            const float *beta, float *C, const int *ldC);
+
+/* replaces F77BLAS(dtrsm), interfaces/blas/F77/trsm.cc:121-228
+ * xerbla_ codes {1,2,3,4,5,6,9,11}, trsm.cc:154-178                          */
+void dtrsm_(const char *side, const char *upLo, const char *transA, const char *diag,
+            const int *m, const int *n, const double *alpha,
+            const double *A, const int *ldA, double *B, const int *ldB);
+
+/* replaces F77BLAS(dsyrk), interfaces/blas/F77/syrk.cc:87-158
+ * xerbla_ codes {1,2,3,4,7,10}, syrk.cc:118-140                              */
+void dsyrk_(const char *upLo, const char *trans, const int *n, const int *k,
+            const double *alpha, const double *A, const int *ldA,
+            const double *beta, double *C, const int *ldC);
+
+/* replaces F77BLAS(xerbla), interfaces/blas/F77/xerbla.cc:6-10.  Weak symbol:
+ * a test harness may supply its own, exactly as the Netlib testers do.       */
+void xerbla_(const char rout[6], const int *info);
+
+/* ------------------------------------------------------------------------ */
+/*    CBLAS entry points (interfaces/blas/C/cblas.h.in of the reference)      */
+/* ------------------------------------------------------------------------ */
+#ifndef ULMBLAS_B200_NO_CBLAS_ENUMS
+enum CBLAS_ORDER     { CblasRowMajor = 101, CblasColMajor = 102 };
+enum CBLAS_TRANSPOSE { CblasNoTrans = 111, CblasTrans = 112, CblasConjTrans = 113,
+                       AtlasConj = 114 };
+enum CBLAS_UPLO      { CblasUpper = 121, CblasLower = 122 };
+enum CBLAS_DIAG      { CblasNonUnit = 131, CblasUnit = 132 };
+enum CBLAS_SIDE      { CblasLeft = 141, CblasRight = 142 };
+#endif
+
+/* replaces CBLAS(dgemm), interfaces/blas/C/gemm.cc:392-485 (row-major by
+ * operand swap, :478-484; cblas_xerbla codes :426-466)                       */
+void cblas_dgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA,
+                 enum CBLAS_TRANSPOSE transB, int m, int n, int k,
+                 double alpha, const double *A, int ldA, const double *B, int ldB,
+                 double beta, double *C, int ldC);
+/* replaces CBLAS(sgemm), interfaces/blas/C/gemm.cc:296-389                   */
+void cblas_sgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA,
+                 enum CBLAS_TRANSPOSE transB, int m, int n, int k,
+                 float alpha, const float *A, int ldA, const float *B, int ldB,
+                 float beta, float *C, int ldC);
+/* replaces CBLAS(dtrsm), interfaces/blas/C/trsm.cc                           */
+void cblas_dtrsm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n,
+                 double alpha, const double *A, int ldA, double *B, int ldB);
+/* replaces CBLAS(dsyrk), interfaces/blas/C/syrk.cc                           */
+void cblas_dsyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE trans, int n, int k,
+                 double alpha, const double *A, int ldA, double beta, double *C, int ldC);
+
+/* column-major-only twins, ULMBLAS(dgemm) interfaces/blas/C/gemm.cc:76-138 ...*/
+void ulmblas_dgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                   int m, int n, int k, double alpha, const double *A, int ldA,
+                   const double *B, int ldB, double beta, double *C, int ldC);
+void ulmblas_sgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                   int m, int n, int k, float alpha, const float *A, int ldA,
+                   const float *B, int ldB, float beta, float *C, int ldC);
+void ulmblas_dtrsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                   enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n,
+                   double alpha, const double *A, int ldA, double *B, int ldB);
+void ulmblas_dsyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k,
+                   double alpha, const double *A, int ldA, double beta, double *C, int ldC);
+
+/* replaces CBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-17 (weak)            */
+void cblas_xerbla(int info, const char *rout, const char *form, ...);
+/* interfaces/blas/C/cblas_globals.cc:3-4 (the Netlib C testers read these)   */
+extern int CBLAS_CallFromC;
+extern int RowMajorStrg;
+
+/* ------------------------------------------------------------------------ */
+/* 2. Device ABI: operands in device memory, work queued on `stream`          */
+/*    (a cudaStream_t passed as void*, NULL = default stream), asynchronous.  */
+/*    transX: 0 = as stored, 1 = transposed.                                  */
+/* ------------------------------------------------------------------------ */
+
+/* C <- alpha*op(A)*op(B) + beta*C on the FP64 tensor-core (DMMA) path.
+ * Replaces ulmBLAS::gemm + gepack_A/B + mgemm + ugemm<double>
+ * (ulmblas/level3/gemm.tcc:16-87, pack/gepack.tcc, mkernel/mgemm.tcc,
+ * ukernel/sse/ugemm.tcc).                                                    */
+int ulmb200_dgemm(void *stream, int transA, int transB,
+                  int64_t m, int64_t n, int64_t k, double alpha,
+                  const double *dA, int64_t ldA, const double *dB, int64_t ldB,
+                  double beta, double *dC, int64_t ldC);
+
+/* SGEMM.  mode 0: FP32 FMA pipes; mode 1: opt-in 3xTF32 on tcgen05 tensor
+ * cores with FP32 accumulation in tensor memory.  Replaces the float
+ * instantiation of the same reference path.                                  */
+enum { ULMB200_SGEMM_FP32 = 0, ULMB200_SGEMM_3XTF32 = 1 };
+int ulmb200_sgemm(void *stream, int mode, int transA, int transB,
+                  int64_t m, int64_t n, int64_t k, float alpha,
+                  const float *dA, int64_t ldA, const float *dB, int64_t ldB,
+                  float beta, float *dC, int64_t ldC);
+
+/* B <- alpha * op(A)^-1 * B (left) or alpha * B * op(A)^-1 (right).
+ * side 0 = left, 1 = right; lower 1 = lower triangle; unit 1 = unit diagonal.
+ * Replaces ulmBLAS::trlsm / trusm (ulmblas/level3/trlsm.tcc, trusm.tcc).      */
+int ulmb200_dtrsm(void *stream, int side, int lower, int transA, int unit,
+                  int64_t m, int64_t n, double alpha,
+                  const double *dA, int64_t ldA, double *dB, int64_t ldB);
+
+/* `lower`-or-upper triangle of C <- alpha*op(A)*op(A)^T + beta*C.
+ * Replaces ulmBLAS::syurk / sylrk (ulmblas/level3/syurk.tcc, sylrk.tcc).      */
+int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int64_t k,
+                  double alpha, const double *dA, int64_t ldA,
+                  double beta, double *dC, int64_t ldC);
+
+/* Deterministic test/bench matrices: element (i,j) of matrix `mat` under
+ * `seed` is a pure function of (seed, mat, i, j), identical on host and device,
+ * uniform in [-1,1).  Fills the rows x cols block whose top-left element has
+ * global index (row0, col0).  dist 0 = uniform[-1,1); 1 = the same scaled by
+ * `scale` off the diagonal and uniform[1,2) on the diagonal (triangular
+ * solver inputs).  (Plays the role of ATL_gegen in bench/l3blastst.c.)        */
+int ulmb200_fill_f64(void *stream, double *d, int64_t ld, int64_t rows, int64_t cols,
+                     uint64_t seed, uint32_t mat, int64_t row0, int64_t col0,
+                     int dist, double scale);
+int ulmb200_fill_f32(void *stream, float *d, int64_t ld, int64_t rows, int64_t cols,
+                     uint64_t seed, uint32_t mat, int64_t row0, int64_t col0);
+void ulmb200_host_fill_f64(double *h, int64_t ld, int64_t rows, int64_t cols,
+                           uint64_t seed, uint32_t mat, int64_t row0, int64_t col0,
+                           int dist, double scale);
+void ulmb200_host_fill_f32(float *h, int64_t ld, int64_t rows, int64_t cols,
+                           uint64_t seed, uint32_t mat, int64_t row0, int64_t col0);
+
+/* Largest gauge-scaled error of a result (device buffers):
+ *   max_ij |C - Cref| / (|alpha| * (|A||B|)_ij + |beta| * |C0|_ij)
+ * with the gauge product computed by the library's own kernel on |A|, |B|.
+ * Used by the bench to check full-size results without a host copy.          */
+int ulmb200_abs_f64(void *stream, double *d, int64_t ld, int64_t rows, int64_t cols);
+
+/* Register-only throughput probes (FP64 DMMA shapes, FP64 FMA, FP32 FMA):
+ * runs `iters` dependent-free instruction groups per warp on every SM and
+ * returns achieved TFLOP/s in *tflops.  which: 0 dmma.m8n8k4, 1 dmma.m16n8k4,
+ * 2 dmma.m16n8k8, 3 dmma.m16n8k16, 4 dfma, 5 ffma, 6 dmma+dfma mixed.         */
+int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms);
+
+/* Number of kernels this library has launched in this process so far.        */
+int64_t ulmb200_launch_count(void);
+
+/* Host-pointer staging used by the BLAS entry points: 1 = caller's buffers
+ * are pinned with cudaHostRegister for the duration of the call (default),
+ * 0 = copied as pageable memory.                                              */
+void ulmb200_set_pin_host(int on);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ULMBLAS_B200_H */

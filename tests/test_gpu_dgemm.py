@@ -1,0 +1,179 @@
+"""DGEMM parity on the GPU: libulmblas_b200's dgemm_ / ulmb200_dgemm against the reference
+(compiled ulmBLAS when oracle/_ref is present, its C restatement otherwise), under the
+componentwise bound  |C - Cref| <= 2*k*eps*(|alpha||A||B| + |beta||C|)."""
+import itertools
+import os
+
+import numpy as np
+import pytest
+
+from helpers import (EPS64, ROGUE, bound_ratio, det_uniform, gemm_gauge, golden_inputs, load_golden,
+                     padded, port, ref, repair_nonfinite)
+
+pytestmark = pytest.mark.gpu
+
+
+def reference_dgemm(ta, tb, m, n, k, alpha, A, B, beta, C0, ldc):
+    """Reference result on a copy of C0's allocation; NaN entries the SSE build emits on
+    finite inputs are replaced by the (bit-identical elsewhere) restatement."""
+    R = ref("")
+    want = C0.copy(order="F")
+    if R is not None:
+        R.dgemm(ta, tb, m, n, k, alpha, A, B, beta, want[:m, :n], ldc=ldc)
+        if not np.isfinite(want[:m, :n]).all():
+            alt = C0.copy(order="F")
+            port().dgemm(ta, tb, m, n, k, alpha, A, B, beta, alt[:m, :n], ldc=ldc)
+            repair_nonfinite(want, alt)
+    else:
+        port().dgemm(ta, tb, m, n, k, alpha, A, B, beta, want[:m, :n], ldc=ldc)
+    return want
+
+
+def op(M, t):
+    return M.T if t in "TC" else M
+
+
+def check_case(ulm, ta, tb, m, n, k, alpha, beta, seed, lda=None, ldb=None, ldc=None, gen=None):
+    ra, ca = (m, k) if ta == "N" else (k, m)
+    rb, cb = (k, n) if tb == "N" else (n, k)
+    gen = gen or det_uniform
+    A, Ab = padded(gen(seed, ra, ca), lda or ra)
+    B, Bb = padded(gen(seed + 1, rb, cb), ldb or rb)
+    C0v, C0b = padded(gen(seed + 2, m, n), ldc or m)
+    ldc_ = C0b.shape[0]
+    Ab0, Bb0 = Ab.copy(order="F"), Bb.copy(order="F")
+    want = reference_dgemm(ta, tb, m, n, k, alpha, A, B, beta, C0b, ldc_)
+    got = C0b.copy(order="F")
+    st = ulm.dgemm(ta, tb, m, n, k, alpha, A, B, beta, got[:m, :n], lda=Ab.shape[0], ldb=Bb.shape[0], ldc=ldc_)
+    assert st == ulm.OK, ulm.status_string(st)
+    assert np.array_equal(Ab, Ab0) and np.array_equal(Bb, Bb0), "an input operand was modified"
+    assert np.array_equal(got[m:, :], C0b[m:, :]), "padding rows of C were written"
+    ratio = bound_ratio(got[:m, :n], want[:m, :n], gemm_gauge(alpha, op(A, ta), op(B, tb), beta, C0v), k, EPS64)
+    assert ratio <= 1.0, f"{ta}{tb} {m}x{n}x{k} alpha={alpha} beta={beta}: error/bound = {ratio:.3g}"
+    return ratio
+
+
+def test_config1_dgemm_1024(ulm):
+    """DGEMM C = 1.5*A*B + 0.5*C, m=n=k=1024, seed 42, through dgemm_ with host pointers."""
+    m = n = k = 1024
+    A, _ = ulm.fmat(m, k); B, _ = ulm.fmat(k, n); C0, _ = ulm.fmat(m, n)
+    ulm.host_fill(A, 42, 0); ulm.host_fill(B, 42, 1); ulm.host_fill(C0, 42, 2)
+    want = reference_dgemm("N", "N", m, n, k, 1.5, A, B, 0.5, C0, m)
+    got = C0.copy(order="F")
+    before = ulm.launch_count()
+    assert ulm.dgemm("N", "N", m, n, k, 1.5, A, B, 0.5, got) == ulm.OK
+    assert ulm.launch_count() > before, "no kernel of this library was launched"
+    ratio = bound_ratio(got, want, gemm_gauge(1.5, A, B, 0.5, C0), k, EPS64)
+    assert ratio <= 1.0, ratio
+
+
+def _normal(seed, r, c, dtype=np.float64):
+    rng = np.random.default_rng(seed)
+    return np.asfortranarray(rng.standard_normal((r, c)).astype(dtype))
+
+
+@pytest.mark.parametrize("ta,tb", list(itertools.product("NT", "NT")))
+def test_config3_ragged_padded(ulm, ta, tb):
+    """m=3001 n=2047 k=513, padded leading dimensions, alpha=-0.7 beta=1.3, normal(0,1), seed 11.
+    ldb is 640 only where that is a legal argument (B stored 513 x 2047); for B^T the stored
+    matrix has 2047 rows and ldb = 2048."""
+    check_case(ulm, ta, tb, 3001, 2047, 513, -0.7, 1.3, 11, lda=3072, ldb=640 if tb == "N" else 2048,
+               ldc=3008, gen=_normal)
+
+
+def test_tester_grid_small_shapes(ulm):
+    """Sizes, alphas, betas and the ld = dim+1 rule of the reference's Level-3 tester
+    (test/F77/dblat3.dat:9-14): odd leading dimensions exercise the non-TMA kernel."""
+    sizes = [0, 1, 2, 3, 7, 12, 31]
+    seed = 1000
+    count = 0
+    for (m, n, k) in [(1, 1, 1), (2, 3, 1), (7, 12, 31), (31, 7, 12), (12, 31, 7), (31, 31, 31), (3, 0, 7),
+                      (0, 3, 7), (7, 3, 0), (1, 31, 2)]:
+        assert m in sizes and n in sizes and k in sizes
+        for ta, tb in itertools.product("NT", "NT"):
+            for alpha, beta in itertools.product([0.0, 1.0, 0.7], [0.0, 1.0, 1.3]):
+                seed += 3
+                ra = (m if ta == "N" else k) + 1
+                rb = (k if tb == "N" else n) + 1
+                check_case(ulm, ta, tb, m, n, k, alpha, beta, seed, lda=ra, ldb=rb, ldc=m + 1)
+                count += 1
+    assert count == 360
+
+
+@pytest.mark.parametrize("tile,path", [("64", ""), ("128", ""), ("64", "ldg"), ("128", "ldg")])
+def test_every_kernel_variant(ulm, tile, path, monkeypatch):
+    """Force each tile shape on each load path (TMA / plain loads) over all four transpositions,
+    on shapes with ragged edges in m, n and k."""
+    monkeypatch.setenv("ULMB200_DGEMM_TILE", tile)
+    if path:
+        monkeypatch.setenv("ULMB200_DGEMM_PATH", path)
+    seed = 5000
+    for (m, n, k) in [(300, 260, 100), (129, 65, 17), (64, 64, 16), (200, 1, 33)]:
+        for ta, tb in itertools.product("NT", "NT"):
+            seed += 3
+            ra = (m if ta == "N" else k)
+            rb = (k if tb == "N" else n)
+            check_case(ulm, ta, tb, m, n, k, 1.25, -0.5, seed, lda=ra + (ra % 2), ldb=rb + (rb % 2), ldc=m + 4)
+
+
+def test_golden_fixture_cases_on_gpu(ulm):
+    """The committed outputs of the compiled reference, reproduced on the GPU within the bound."""
+    for name, c in load_golden().items():
+        if c["kind"] != "dgemm":
+            continue
+        A, B, C0 = golden_inputs(c)
+        got = C0.copy(order="F")
+        assert ulm.dgemm(c["ta"], c["tb"], c["m"], c["n"], c["k"], c["alpha"], A, B, c["beta"], got) == ulm.OK
+        ratio = bound_ratio(got, c["C"], gemm_gauge(c["alpha"], op(A, c["ta"]), op(B, c["tb"]), c["beta"], C0),
+                            c["k"], EPS64)
+        assert ratio <= 1.0, (name, ratio)
+
+
+def test_device_pointer_path_and_beta_zero_ignores_c(ulm, torch_cuda):
+    """Device-resident operands through ulmb200_dgemm; with beta == 0, NaN in C must not propagate
+    (BLAS semantics; the reference's SSE kernel differs here on full tiles)."""
+    torch = torch_cuda
+    m, n, k = 777, 513, 260
+    A = det_uniform(1, m, k); B = det_uniform(2, k, n)
+    dA = torch.from_numpy(np.ascontiguousarray(A.T)).cuda()      # column-major m x k == row-major k x m
+    dB = torch.from_numpy(np.ascontiguousarray(B.T)).cuda()
+    dC = torch.full((n, m), float("nan"), dtype=torch.float64, device="cuda")
+    ulm.dev_dgemm(0, 0, m, n, k, 2.0, dA.data_ptr(), m, dB.data_ptr(), k, 0.0, dC.data_ptr(), m,
+                  stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = dC.cpu().numpy().T
+    want = np.zeros((m, n), order="F")
+    port().dgemm("N", "N", m, n, k, 2.0, A, B, 0.0, want)
+    assert np.isfinite(got).all()
+    assert bound_ratio(got, want, gemm_gauge(2.0, A, B, 0.0, want), k, EPS64) <= 1.0
+
+
+def test_cblas_row_major(ulm):
+    """cblas_dgemm row-major = the column-major product with operands swapped
+    (interfaces/blas/C/gemm.cc:478-484); checked against numpy."""
+    m, n, k = 50, 70, 33
+    rng = np.random.default_rng(3)
+    A = rng.uniform(-1, 1, (m, k)); B = rng.uniform(-1, 1, (n, k)); C0 = rng.uniform(-1, 1, (m, n))
+    got = C0.copy()
+    ulm.lib.cblas_dgemm(ulm.CblasRowMajor, ulm.CblasNoTrans, ulm.CblasTrans, m, n, k, 0.5,
+                        A.ctypes.data, k, B.ctypes.data, k, 2.0, got.ctypes.data, n)
+    assert ulm.last_status() == ulm.OK
+    want = 0.5 * A @ B.T + 2.0 * C0
+    assert bound_ratio(got, want, 0.5 * np.abs(A) @ np.abs(B.T) + 2.0 * np.abs(C0), k, EPS64) <= 1.0
+
+
+def test_device_fill_matches_host_fill(ulm, torch_cuda):
+    torch = torch_cuda
+    rows, cols, ld = 301, 77, 304
+    d = torch.zeros((cols, ld), dtype=torch.float64, device="cuda")
+    ulm.dev_fill_f64(d.data_ptr(), ld, rows, cols, 99, 2, row0=5, col0=1000)
+    torch.cuda.synchronize()
+    h, _ = ulm.fmat(rows, cols)
+    ulm.host_fill(h, 99, 2, row0=5, col0=1000)
+    assert np.array_equal(d.cpu().numpy().T[:rows, :], h)
+    f = torch.zeros((cols, ld), dtype=torch.float32, device="cuda")
+    ulm.dev_fill_f32(f.data_ptr(), ld, rows, cols, 7, 0)
+    torch.cuda.synchronize()
+    hf, _ = ulm.fmat(rows, cols, dtype=np.float32)
+    ulm.host_fill(hf, 7, 0)
+    assert np.array_equal(f.cpu().numpy().T[:rows, :], hf)

@@ -1,0 +1,557 @@
+// The reference-facing boundary: the Fortran-ABI and CBLAS symbols of
+// ulmBLAS's Level-3 GEMM path (interfaces/blas/F77/{gemm,trsm,syrk,xerbla}.cc,
+// interfaces/blas/C/{gemm,trsm,syrk,xerbla,cblas_globals}.cc), with the same
+// argument decoding, the same first-bad-argument codes and the same xerbla
+// protocol.  Behind them nothing of the reference remains: operands are used in
+// place when they already live in device memory, and are staged through cached
+// device buffers (column blocks of B/C pipelined against the compute) when
+// they are host pointers.  There is no CPU path: without a usable sm_100 device
+// the call reports through stderr and ulmb200_last_status() and leaves C alone.
+//
+// One deliberate difference from the reference: after reporting a bad argument
+// through xerbla_ these entry points return; the reference falls through and
+// computes anyway (interfaces/blas/F77/gemm.cc:197-204).
+#include "common.h"
+
+#include <algorithm>
+#include <cctype>
+#include <cstdarg>
+#include <cstring>
+
+namespace ulmb200 {
+
+int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
+                 int64_t k, double alpha, const double *A, int64_t lda, const double *B,
+                 int64_t ldb, double beta, double *C, int64_t ldc);
+int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, int64_t n,
+                 int64_t k, float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
+                 float beta, float *C, int64_t ldc);
+int dsyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
+                 const double *A, int64_t lda, double beta, double *C, int64_t ldc);
+int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                 double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
+
+static int g_pin_host = 0;
+
+// ---- where does a pointer live? -------------------------------------------
+static bool on_device(const void *p)
+{
+    if (!p) return false;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// ---- per-thread streams and events for staged calls -------------------------
+struct Streams {
+    cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+    cudaEvent_t ev[64] = {};
+    int dev = -1;
+    bool ok = false;
+};
+static thread_local Streams t_streams;
+
+static Streams *streams()
+{
+    Streams &s = t_streams;
+    const int dev = current_device();
+    if (s.ok && s.dev == dev) return &s;
+    if (s.ok) return &s;     // one device per thread for staged calls
+    if (cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithFlags(&s.run, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    for (auto &e : s.ev)
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    s.dev = dev;
+    s.ok = true;
+    return &s;
+}
+
+// Optional page-locking of the caller's buffers for the duration of a call.
+struct HostPin {
+    void *p = nullptr;
+    HostPin(const void *ptr, size_t bytes)
+    {
+        if (g_pin_host && ptr && bytes >= (size_t)(1 << 20)) {
+            cudaPointerAttributes a;
+            if (cudaPointerGetAttributes(&a, ptr) == cudaSuccess && a.type == cudaMemoryTypeUnregistered &&
+                cudaHostRegister(const_cast<void *>(ptr), bytes, cudaHostRegisterDefault) == cudaSuccess)
+                p = const_cast<void *>(ptr);
+            else
+                cudaGetLastError();
+        }
+    }
+    ~HostPin() { if (p) cudaHostUnregister(p); }
+};
+
+template <typename T>
+static cudaError_t copy_in(T *d, int64_t ldd, const T *h, int64_t ldh, int64_t rows, int64_t cols,
+                           cudaStream_t st)
+{
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    return cudaMemcpy2DAsync(d, ldd * sizeof(T), h, ldh * sizeof(T), rows * sizeof(T), cols,
+                             cudaMemcpyHostToDevice, st);
+}
+
+template <typename T>
+static cudaError_t copy_out(T *h, int64_t ldh, const T *d, int64_t ldd, int64_t rows, int64_t cols,
+                            cudaStream_t st)
+{
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    return cudaMemcpy2DAsync(h, ldh * sizeof(T), d, ldd * sizeof(T), rows * sizeof(T), cols,
+                             cudaMemcpyDeviceToHost, st);
+}
+
+static int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+static int finish(Streams *s)
+{
+    cudaError_t e = cudaStreamSynchronize(s->in);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->run);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->out);
+    if (e != cudaSuccess) return check_cuda(e, "stream synchronize", __FILE__, __LINE__);
+    return poll_device_error();
+}
+
+// C <- alpha*op(A)*op(B) + beta*C with host or device pointers.
+// Host operands: A goes over whole; B (and C when beta != 0) go over in column
+// blocks on the copy-in stream, each block's product runs on the compute
+// stream as soon as its inputs have landed, and its C block returns on the
+// copy-out stream while the next block computes.
+template <typename T, typename Launch>
+static int gemm_any(Launch launch, int transA, int transB, int64_t m, int64_t n, int64_t k,
+                    const T *A, int64_t lda, const T *B, int64_t ldb, bool read_c, T *C, int64_t ldc)
+{
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    const bool dA = on_device(A), dB = on_device(B), dC = on_device(C);
+    if (dA && dB && dC) {
+        int st = launch(nullptr, A, lda, B, ldb, C, ldc, 0, n);
+        if (st != ULMB200_OK) return set_status(st);
+        if (int e = check_cuda(cudaStreamSynchronize(nullptr), "synchronize", __FILE__, __LINE__)) return e;
+        return set_status(poll_device_error());
+    }
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+
+    const int64_t rowsA = transA ? k : m, colsA = transA ? m : k;
+    const int64_t rowsB = transB ? n : k, colsB = transB ? k : n;
+    const int64_t dlda = round_up(std::max<int64_t>(rowsA, 1), 2);
+    const int64_t dldb = round_up(std::max<int64_t>(rowsB, 1), 2);
+    const int64_t dldc = round_up(m, 2);
+    const T *Ad = A, *Bd = B;
+    T *Cd = C;
+    int64_t ua = lda, ub = ldb, uc = ldc;
+    if (!dA) { Ad = static_cast<T *>(device_scratch(0, sizeof(T) * dlda * std::max<int64_t>(colsA, 1))); ua = dlda; }
+    if (!dB) { Bd = static_cast<T *>(device_scratch(1, sizeof(T) * dldb * std::max<int64_t>(colsB, 1))); ub = dldb; }
+    if (!dC) { Cd = static_cast<T *>(device_scratch(2, sizeof(T) * dldc * n)); uc = dldc; }
+    if (!Ad || !Bd || !Cd) return set_status(ULMB200_CUDA_ERROR);
+
+    HostPin pa(dA ? nullptr : A, sizeof(T) * ((colsA - 1) * lda + rowsA));
+    HostPin pb(dB ? nullptr : B, sizeof(T) * ((colsB - 1) * ldb + rowsB));
+    HostPin pc(dC ? nullptr : C, sizeof(T) * ((n - 1) * ldc + m));
+
+    cudaError_t e = cudaSuccess;
+    if (!dA && k > 0) e = copy_in(const_cast<T *>(Ad), ua, A, lda, rowsA, colsA, s->in);
+    if (e != cudaSuccess) return check_cuda(e, "copy A", __FILE__, __LINE__);
+
+    // column blocks: big enough to keep the GEMM efficient, small enough to overlap
+    int64_t nblk = std::min<int64_t>(16, std::max<int64_t>(1, (sizeof(T) * m * n) >> 27));
+    int64_t nc = round_up((n + nblk - 1) / nblk, 128);
+    nblk = (n + nc - 1) / nc;
+    if (nblk > 31) { nc = round_up((n + 30) / 31, 128); nblk = (n + nc - 1) / nc; }
+    // B^T blocks are row ranges of the stored matrix: ship B whole in that case
+    if (!dB && transB && k > 0) {
+        e = copy_in(const_cast<T *>(Bd), ub, B, ldb, rowsB, colsB, s->in);
+        if (e != cudaSuccess) return check_cuda(e, "copy B", __FILE__, __LINE__);
+    }
+    for (int64_t b = 0; b < nblk; ++b) {
+        const int64_t j0 = b * nc, jn = std::min(nc, n - j0);
+        if (!dB && !transB && k > 0) e = copy_in(const_cast<T *>(Bd) + j0 * ub, ub, B + j0 * ldb, ldb, rowsB, jn, s->in);
+        if (e == cudaSuccess && !dC && read_c) e = copy_in(Cd + j0 * uc, uc, C + j0 * ldc, ldc, m, jn, s->in);
+        if (e == cudaSuccess) e = cudaEventRecord(s->ev[2 * b], s->in);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->run, s->ev[2 * b], 0);
+        if (e != cudaSuccess) return check_cuda(e, "stage block", __FILE__, __LINE__);
+        int st = launch(s->run, Ad, ua, Bd, ub, Cd, uc, j0, jn);
+        if (st != ULMB200_OK) { finish(s); return set_status(st); }
+        if (!dC) {
+            e = cudaEventRecord(s->ev[2 * b + 1], s->run);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(s->out, s->ev[2 * b + 1], 0);
+            if (e == cudaSuccess) e = copy_out(C + j0 * ldc, ldc, Cd + j0 * uc, uc, m, jn, s->out);
+            if (e != cudaSuccess) return check_cuda(e, "return block", __FILE__, __LINE__);
+        }
+    }
+    return set_status(finish(s));
+}
+
+static int dgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, double alpha,
+                     const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
+                     double *C, int64_t ldc)
+{
+    auto launch = [=](cudaStream_t st, const double *Ad, int64_t ua, const double *Bd, int64_t ub,
+                      double *Cd, int64_t uc, int64_t j0, int64_t jn) {
+        const double *Bblk = transB ? Bd + j0 : Bd + j0 * ub;
+        return dgemm_device(st, 0, transA, transB, m, jn, k, alpha, Ad, ua, Bblk, ub, beta,
+                            Cd + j0 * uc, uc);
+    };
+    return gemm_any<double>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0, C, ldc);
+}
+
+static int sgemm_mode()
+{
+    const char *e = getenv("ULMB200_SGEMM");
+    return (e && (e[0] == '3' || e[0] == 't')) ? ULMB200_SGEMM_3XTF32 : ULMB200_SGEMM_FP32;
+}
+
+static int sgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, float alpha,
+                     const float *A, int64_t lda, const float *B, int64_t ldb, float beta, float *C,
+                     int64_t ldc)
+{
+    const int mode = sgemm_mode();
+    auto launch = [=](cudaStream_t st, const float *Ad, int64_t ua, const float *Bd, int64_t ub,
+                      float *Cd, int64_t uc, int64_t j0, int64_t jn) {
+        const float *Bblk = transB ? Bd + j0 : Bd + j0 * ub;
+        return sgemm_device(st, mode, transA, transB, m, jn, k, alpha, Ad, ua, Bblk, ub, beta,
+                            Cd + j0 * uc, uc);
+    };
+    return gemm_any<float>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0f, C, ldc);
+}
+
+// Staging for the two-operand routines (whole matrices; no pipelining).
+static int dsyrk_any(int lower, int trans, int64_t n, int64_t k, double alpha, const double *A,
+                     int64_t lda, double beta, double *C, int64_t ldc)
+{
+    if (n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    const bool dA = on_device(A), dC = on_device(C);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t rowsA = trans ? k : n, colsA = trans ? n : k;
+    const double *Ad = A;
+    double *Cd = C;
+    int64_t ua = lda, uc = ldc;
+    if (!dA) { ua = round_up(std::max<int64_t>(rowsA, 1), 2); Ad = static_cast<double *>(device_scratch(0, 8 * ua * std::max<int64_t>(colsA, 1))); }
+    if (!dC) { uc = round_up(n, 2); Cd = static_cast<double *>(device_scratch(2, 8 * uc * n)); }
+    if (!Ad || !Cd) return set_status(ULMB200_CUDA_ERROR);
+    cudaError_t e = cudaSuccess;
+    if (!dA && k > 0) e = copy_in(const_cast<double *>(Ad), ua, A, lda, rowsA, colsA, s->run);
+    // the whole square goes over and comes back; the kernel only writes the triangle,
+    // so the other triangle returns bit-identical
+    if (e == cudaSuccess && !dC) e = copy_in(Cd, uc, C, ldc, n, n, s->run);
+    if (e != cudaSuccess) return check_cuda(e, "copy in", __FILE__, __LINE__);
+    int st = dsyrk_device(s->run, lower, trans, n, k, alpha, Ad, ua, beta, Cd, uc);
+    if (st != ULMB200_OK) { finish(s); return set_status(st); }
+    if (!dC) {
+        e = copy_out(C, ldc, Cd, uc, n, n, s->run);
+        if (e != cudaSuccess) return check_cuda(e, "copy out", __FILE__, __LINE__);
+    }
+    return set_status(finish(s));
+}
+
+static int dtrsm_any(int side, int lower, int transA, int unit, int64_t m, int64_t n, double alpha,
+                     const double *A, int64_t lda, double *B, int64_t ldb)
+{
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    const bool dA = on_device(A), dB = on_device(B);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t dim = side == 0 ? m : n;
+    const double *Ad = A;
+    double *Bd = B;
+    int64_t ua = lda, ub = ldb;
+    if (!dA) { ua = round_up(dim, 2); Ad = static_cast<double *>(device_scratch(0, 8 * ua * dim)); }
+    if (!dB) { ub = round_up(m, 2); Bd = static_cast<double *>(device_scratch(2, 8 * ub * n)); }
+    if (!Ad || !Bd) return set_status(ULMB200_CUDA_ERROR);
+    cudaError_t e = cudaSuccess;
+    // The whole square of A is shipped, but the kernels only ever read the
+    // referenced triangle (and skip the diagonal when it is unit).
+    if (!dA) e = copy_in(const_cast<double *>(Ad), ua, A, lda, dim, dim, s->run);
+    if (e == cudaSuccess && !dB) e = copy_in(Bd, ub, B, ldb, m, n, s->run);
+    if (e != cudaSuccess) return check_cuda(e, "copy in", __FILE__, __LINE__);
+    int st = dtrsm_device(s->run, side, lower, transA, unit, m, n, alpha, Ad, ua, Bd, ub);
+    if (st != ULMB200_OK) { finish(s); return set_status(st); }
+    if (!dB) {
+        e = copy_out(B, ldb, Bd, ub, m, n, s->run);
+        if (e != cudaSuccess) return check_cuda(e, "copy out", __FILE__, __LINE__);
+    }
+    return set_status(finish(s));
+}
+
+// ---- argument decoding shared by the shims ---------------------------------
+static inline int up(const char *c) { return std::toupper((unsigned char)*c); }
+static inline bool is_trans(const char *c) { int u = up(c); return u == 'T' || u == 'C'; }
+static inline bool valid_trans(const char *c) { int u = up(c); return u == 'N' || u == 'T' || u == 'C' || u == 'R'; }
+
+static int gemm_info(const char *ta, const char *tb, int m, int n, int k, int lda, int ldb, int ldc)
+{
+    const int rowsA = !is_trans(ta) ? m : k, rowsB = !is_trans(tb) ? k : n;
+    if (!valid_trans(ta)) return 1;
+    if (!valid_trans(tb)) return 2;
+    if (m < 0) return 3;
+    if (n < 0) return 4;
+    if (k < 0) return 5;
+    if (lda < std::max(1, rowsA)) return 8;
+    if (ldb < std::max(1, rowsB)) return 10;
+    if (ldc < std::max(1, m)) return 13;
+    return 0;
+}
+
+}  // namespace ulmb200
+
+using namespace ulmb200;
+
+extern "C" {
+
+int CBLAS_CallFromC = 0;
+int RowMajorStrg = 0;
+
+__attribute__((weak)) void xerbla_(const char rout[6], const int *info)
+{
+    // same text as interfaces/blas/F77/xerbla.cc:9; rout is 6 blank-padded characters
+    fprintf(stderr, "Parameter %d to routine %.6s was incorrect\n", *info, rout);
+}
+
+__attribute__((weak)) void cblas_xerbla(int info, const char *rout, const char *form, ...)
+{
+    (void)form;
+    fprintf(stderr, "Parameter %d to routine %s was incorrect\n", info, rout);
+}
+
+void ulmb200_set_pin_host(int on) { g_pin_host = on ? 1 : 0; }
+
+// ---------------------------- Fortran ABI -----------------------------------
+
+void dgemm_(const char *transA, const char *transB, const int *m, const int *n, const int *k,
+            const double *alpha, const double *A, const int *ldA, const double *B, const int *ldB,
+            const double *beta, double *C, const int *ldC)
+{
+    int info = gemm_info(transA, transB, *m, *n, *k, *ldA, *ldB, *ldC);
+    if (info != 0) {
+        xerbla_("DGEMM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    dgemm_any(is_trans(transA), is_trans(transB), *m, *n, *k, *alpha, A, *ldA, B, *ldB, *beta, C, *ldC);
+}
+
+void sgemm_(const char *transA, const char *transB, const int *m, const int *n, const int *k,
+            const float *alpha, const float *A, const int *ldA, const float *B, const int *ldB,
+            const float *beta, float *C, const int *ldC)
+{
+    int info = gemm_info(transA, transB, *m, *n, *k, *ldA, *ldB, *ldC);
+    if (info != 0) {
+        xerbla_("SGEMM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    sgemm_any(is_trans(transA), is_trans(transB), *m, *n, *k, *alpha, A, *ldA, B, *ldB, *beta, C, *ldC);
+}
+
+void dtrsm_(const char *side, const char *upLo, const char *transA, const char *diag, const int *m,
+            const int *n, const double *alpha, const double *A, const int *ldA, double *B,
+            const int *ldB)
+{
+    const bool left = up(side) == 'L';
+    const int rowsA = left ? *m : *n;
+    int info = 0;
+    if (up(side) != 'L' && up(side) != 'R') info = 1;
+    else if (up(upLo) != 'L' && up(upLo) != 'U') info = 2;
+    else if (!valid_trans(transA)) info = 3;
+    else if (up(diag) != 'U' && up(diag) != 'N') info = 4;
+    else if (*m < 0) info = 5;
+    else if (*n < 0) info = 6;
+    else if (*ldA < std::max(1, rowsA)) info = 9;
+    else if (*ldB < std::max(1, *m)) info = 11;
+    if (info != 0) {
+        xerbla_("DTRSM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    dtrsm_any(left ? 0 : 1, up(upLo) == 'L', is_trans(transA), up(diag) == 'U', *m, *n, *alpha, A, *ldA, B, *ldB);
+}
+
+void dsyrk_(const char *upLo, const char *trans, const int *n, const int *k, const double *alpha,
+            const double *A, const int *ldA, const double *beta, double *C, const int *ldC)
+{
+    const int rowsA = is_trans(trans) ? *k : *n;
+    int info = 0;
+    if (up(upLo) != 'L' && up(upLo) != 'U') info = 1;
+    else if (!valid_trans(trans)) info = 2;
+    else if (*n < 0) info = 3;
+    else if (*k < 0) info = 4;
+    else if (*ldA < std::max(1, rowsA)) info = 7;
+    else if (*ldC < std::max(1, *n)) info = 10;
+    if (info != 0) {
+        xerbla_("DSYRK ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    dsyrk_any(up(upLo) == 'L', is_trans(trans), *n, *k, *alpha, A, *ldA, *beta, C, *ldC);
+}
+
+// ------------------------------- CBLAS ---------------------------------------
+
+static inline bool c_notrans(int t) { return t == CblasNoTrans || t == AtlasConj; }
+static inline bool c_valid_trans(int t)
+{
+    return t == CblasNoTrans || t == CblasTrans || t == AtlasConj || t == CblasConjTrans;
+}
+
+void ulmblas_dgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB, int m, int n, int k,
+                   double alpha, const double *A, int ldA, const double *B, int ldB, double beta,
+                   double *C, int ldC)
+{
+    dgemm_any(!c_notrans(transA), !c_notrans(transB), m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
+void ulmblas_sgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB, int m, int n, int k,
+                   float alpha, const float *A, int ldA, const float *B, int ldB, float beta,
+                   float *C, int ldC)
+{
+    sgemm_any(!c_notrans(transA), !c_notrans(transB), m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
+// first-bad-argument code of CBLAS(dgemm)/CBLAS(sgemm), interfaces/blas/C/gemm.cc:426-466
+static int cblas_gemm_info(int order, int transA, int transB, int m, int n, int k, int ldA, int ldB, int ldC)
+{
+    int rowsA, rowsB;
+    if (order == CblasColMajor) {
+        rowsA = c_notrans(transA) ? m : k;
+        rowsB = c_notrans(transB) ? k : n;
+    } else {
+        rowsB = c_notrans(transB) ? n : k;
+        rowsA = c_notrans(transA) ? k : m;
+    }
+    if (order != CblasColMajor && order != CblasRowMajor) return 1;
+    if (!c_valid_trans(transA)) return 2;
+    if (!c_valid_trans(transB)) return 3;
+    if (order == CblasColMajor) {
+        if (m < 0) return 4;
+        if (n < 0) return 5;
+        if (k < 0) return 6;
+        if (ldA < std::max(1, rowsA)) return 9;
+        if (ldB < std::max(1, rowsB)) return 11;
+        if (ldC < std::max(1, m)) return 14;
+    } else {
+        if (n < 0) return 4;
+        if (m < 0) return 5;
+        if (k < 0) return 6;
+        if (ldB < std::max(1, rowsB)) return 9;
+        if (ldA < std::max(1, rowsA)) return 11;
+        if (ldC < std::max(1, n)) return 14;
+    }
+    return 0;
+}
+
+void cblas_dgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                 int m, int n, int k, double alpha, const double *A, int ldA, const double *B,
+                 int ldB, double beta, double *C, int ldC)
+{
+    int info = cblas_gemm_info(order, transA, transB, m, n, k, ldA, ldB, ldC);
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_dgemm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    // row-major C = A*B is column-major C^T = B^T * A^T: swap the operands (gemm.cc:478-484)
+    if (order == CblasColMajor) ulmblas_dgemm(transA, transB, m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+    else                        ulmblas_dgemm(transB, transA, n, m, k, alpha, B, ldB, A, ldA, beta, C, ldC);
+}
+
+void cblas_sgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                 int m, int n, int k, float alpha, const float *A, int ldA, const float *B, int ldB,
+                 float beta, float *C, int ldC)
+{
+    int info = cblas_gemm_info(order, transA, transB, m, n, k, ldA, ldB, ldC);
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_sgemm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) ulmblas_sgemm(transA, transB, m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+    else                        ulmblas_sgemm(transB, transA, n, m, k, alpha, B, ldB, A, ldA, beta, C, ldC);
+}
+
+void ulmblas_dtrsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE transA,
+                   enum CBLAS_DIAG diag, int m, int n, double alpha, const double *A, int ldA,
+                   double *B, int ldB)
+{
+    dtrsm_any(side == CblasLeft ? 0 : 1, upLo == CblasLower, !c_notrans(transA), diag == CblasUnit, m, n,
+              alpha, A, ldA, B, ldB);
+}
+
+void cblas_dtrsm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n, double alpha,
+                 const double *A, int ldA, double *B, int ldB)
+{
+    const int rowsA = (side == CblasLeft) ? m : n;
+    int info = 0;
+    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
+    else if (side != CblasLeft && side != CblasRight) info = 2;
+    else if (upLo != CblasLower && upLo != CblasUpper) info = 3;
+    else if (!c_valid_trans(transA)) info = 4;
+    else if (diag != CblasUnit && diag != CblasNonUnit) info = 5;
+    else if (order == CblasColMajor) {
+        if (m < 0) info = 6;
+        else if (n < 0) info = 7;
+        else if (ldA < std::max(1, rowsA)) info = 10;
+        else if (ldB < std::max(1, m)) info = 12;
+    } else {
+        if (n < 0) info = 6;
+        else if (m < 0) info = 7;
+        else if (ldA < std::max(1, rowsA)) info = 10;
+        else if (ldB < std::max(1, n)) info = 12;
+    }
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_dtrsm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) {
+        ulmblas_dtrsm(side, upLo, transA, diag, m, n, alpha, A, ldA, B, ldB);
+    } else {
+        // interfaces/blas/C/trsm.cc:455-457
+        ulmblas_dtrsm(side == CblasLeft ? CblasRight : CblasLeft,
+                      upLo == CblasUpper ? CblasLower : CblasUpper, transA, diag, n, m, alpha, A, ldA, B, ldB);
+    }
+}
+
+void ulmblas_dsyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k, double alpha,
+                   const double *A, int ldA, double beta, double *C, int ldC)
+{
+    dsyrk_any(upLo == CblasLower, !c_notrans(trans), n, k, alpha, A, ldA, beta, C, ldC);
+}
+
+void cblas_dsyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n,
+                 int k, double alpha, const double *A, int ldA, double beta, double *C, int ldC)
+{
+    int rowsA;
+    if (order == CblasColMajor) rowsA = c_notrans(trans) ? n : k;
+    else                        rowsA = c_notrans(trans) ? k : n;
+    int info = 0;
+    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
+    else if (upLo != CblasLower && upLo != CblasUpper) info = 2;
+    else if (!c_valid_trans(trans)) info = 3;
+    else if (n < 0) info = 4;
+    else if (k < 0) info = 5;
+    else if (ldA < std::max(1, rowsA)) info = 8;
+    else if (ldC < std::max(1, n)) info = 11;
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_dsyrk", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) {
+        ulmblas_dsyrk(upLo, trans, n, k, alpha, A, ldA, beta, C, ldC);
+    } else {
+        // interfaces/blas/C/syrk.cc:259-261
+        ulmblas_dsyrk(upLo == CblasUpper ? CblasLower : CblasUpper,
+                      c_notrans(trans) ? CblasTrans : CblasNoTrans, n, k, alpha, A, ldA, beta, C, ldC);
+    }
+}
+
+}  // extern "C"

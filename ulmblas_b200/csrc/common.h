@@ -1,0 +1,146 @@
+// Shared host/device helpers of libulmblas_b200: status plumbing, launch
+// accounting, and the sm_100a PTX wrappers (mbarrier, TMA) the kernels use.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/ulmblas_b200.h"
+
+namespace ulmb200 {
+
+// ---- host-side status ------------------------------------------------------
+
+int  set_status(int st);                 // records the thread's last status, returns it
+void count_launch(int n = 1);            // feeds ulmb200_launch_count()
+int  check_cuda(cudaError_t e, const char *what, const char *file, int line);
+int  ensure_device();                    // 0 if the current device is sm_100
+constexpr int kMaxDevices = 64;
+int  current_device();                   // cudaGetDevice, clamped to [0, kMaxDevices)
+int  sm_count();                         // SMs of the current device
+
+#define ULMB_CUDA(call)                                                            \
+    do {                                                                           \
+        int st__ = ::ulmb200::check_cuda((call), #call, __FILE__, __LINE__);        \
+        if (st__ != ULMB200_OK) return st__;                                       \
+    } while (0)
+
+// Device-side error word (one per device, zero-initialised).  A kernel whose
+// bounded wait runs out stores a non-zero code here and returns normally.
+int *device_error_word();                // device pointer, for the current device
+int  poll_device_error();                // syncs nothing; reads the word with a blocking copy
+
+// Cached scratch buffers in device memory (grow-only, one set per device),
+// the counterpart of the reference's MemoryPool (ulmblas/auxiliary/memorypool.tcc).
+void *device_scratch(int slot, size_t bytes);
+
+// cuTensorMapEncodeTiled fetched through the runtime (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// 2-D tensor map over a column-major matrix: dim0 = contiguous dimension
+// (extent d0), dim1 = the strided one (extent d1, stride ld elements), box
+// b0 x b1 elements, 128-byte swizzle.  Returns false if the driver refuses.
+bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base,
+                  uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1);
+
+#ifdef __CUDACC__
+// ---- device-side PTX wrappers ---------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_barrier_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: every mbarrier wait in this library gives up after a fixed
+// number of polls (seconds of wall time, far beyond any legitimate wait) and
+// reports failure instead of spinning forever.
+constexpr uint32_t kWaitPollLimit = 1u << 24;
+
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+
+// One 2-D TMA tile load, no multicast; completion is signalled on `bar`.
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int32_t x,
+                                            int32_t y, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y),
+        "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
+
+// Warp-uniform election of one lane.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+#endif  // __CUDACC__
+
+}  // namespace ulmb200

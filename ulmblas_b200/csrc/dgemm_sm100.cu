@@ -1,0 +1,541 @@
+// FP64 GEMM for sm_100a:  C <- alpha * op(A) * op(B) + beta * C, column-major.
+//
+// Replaces the reference's cache-blocking driver, panel packing, macro-kernel
+// and SSE micro-kernel (ulmblas/level3/gemm.tcc:16-87, pack/gepack.tcc,
+// mkernel/mgemm.tcc, ukernel/sse/ugemm.tcc).  Where the reference packs A and B
+// into contiguous panels so its 4x4 register kernel streams them, this kernel
+// has TMA drop 128-byte-swizzled operand tiles straight into shared memory
+// (no packed copy in global memory) and feeds them to the FP64 tensor-core
+// instruction (mma.sync m16n8k8 .f64 -- tcgen05 has no FP64 kind).  The
+// transposes are absorbed by the tile layout, alpha/beta by the epilogue.
+//
+// Two kernels share the fragment code:
+//   dgemm_tma_kernel  persistent, warp-specialised: one producer warp issues
+//                     TMA loads into a ring of stages guarded by mbarriers,
+//                     the consumer warps run DMMA out of shared memory.
+//                     Needs 16-byte aligned A/B and even leading dimensions.
+//   dgemm_ldg_kernel  same tile and fragment layout filled with predicated
+//                     8-byte global loads; any alignment, any ld.
+#include "common.h"
+#include "tile_layout.h"
+
+namespace ulmb200 {
+
+struct GemmParams {
+    int64_t m, n, k;
+    double alpha, beta;
+    const double *A, *B;      // used by the ldg kernel only
+    int64_t lda, ldb;
+    double *C;
+    int64_t ldc;
+    int tiles_m, tiles_n;
+    int tri;                  // 0 full, 1 upper triangle only (row<=col), 2 lower (row>=col)
+    int *err;                 // device error word
+};
+
+__device__ __forceinline__ void dmma_16x8x8(double (&c)[4], const double (&a)[4], const double (&b)[2])
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
+        : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(b[0]), "d"(b[1]));
+}
+
+__device__ __forceinline__ double2 lds128(uint32_t addr)
+{
+    double2 v;
+    asm volatile("ld.shared.v2.f64 {%0,%1}, [%2];" : "=d"(v.x), "=d"(v.y) : "r"(addr));
+    return v;
+}
+
+// One pipeline stage (16 k) of a warp's MT x NT grid of m16n8 tiles.
+template <int MAJOR_A, int MAJOR_B, int MT, int NT>
+__device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32_t (&ba)[2],
+                                          const uint32_t (&bb)[2], double (&acc)[MT][NT][4])
+{
+    static_assert(NT % 2 == 0, "n8 tiles come in pairs");
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        double a[MT][4];
+        double b[NT][2];
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            if (MAJOR_A == K_MAJOR) {
+                double2 lo = lds128(sA + ba[h] + i * 2048);
+                double2 hi = lds128(sA + ba[h] + i * 2048 + 1024);
+                a[i][0] = lo.x; a[i][2] = lo.y; a[i][1] = hi.x; a[i][3] = hi.y;
+            } else {
+                double2 s0 = lds128(sA + ba[0] + i * 2048 + h * 1024);
+                double2 s1 = lds128(sA + ba[1] + i * 2048 + h * 1024);
+                a[i][0] = s0.x; a[i][1] = s0.y; a[i][2] = s1.x; a[i][3] = s1.y;
+            }
+        }
+        if (MAJOR_B == K_MAJOR) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                double2 v = lds128(sB + bb[h] + j * 1024);
+                b[j][0] = v.x; b[j][1] = v.y;
+            }
+        } else {
+#pragma unroll
+            for (int jj = 0; jj < NT / 2; ++jj) {
+                double2 s0 = lds128(sB + bb[0] + jj * 2048 + h * 1024);
+                double2 s1 = lds128(sB + bb[1] + jj * 2048 + h * 1024);
+                b[2 * jj][0] = s0.x; b[2 * jj + 1][0] = s0.y;
+                b[2 * jj][1] = s1.x; b[2 * jj + 1][1] = s1.y;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) dmma_16x8x8(acc[i][j], a[i], b[j]);
+    }
+}
+
+// C(row, col) <- alpha*acc + beta*C for the warp's accumulators; rows/cols
+// outside m x n (and outside the requested triangle) are skipped.
+template <int MAJOR_A, int MAJOR_B, int MT, int NT>
+__device__ __forceinline__ void epilogue(const GemmParams &p, int64_t m0, int64_t n0, int wm0,
+                                         int wn0, int lane, double (&acc)[MT][NT][4])
+{
+    const double alpha = p.alpha, beta = p.beta;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int64_t row = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, half);
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
+                    bool ok = row < p.m && col < p.n;
+                    if (p.tri == 1) ok = ok && row <= col;
+                    if (p.tri == 2) ok = ok && row >= col;
+                    if (ok) {
+                        double *c = p.C + row + col * p.ldc;
+                        double v = alpha * acc[i][j][2 * half + w];
+                        if (beta != 0.0) v = fma(beta, *c, v);
+                        *c = v;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Persistent tile order: groups of 8 tile-rows swept column by column, so the
+// CTAs running together share a handful of A and B panels in L2.
+__device__ __forceinline__ void tile_coord(int id, int tiles_m, int tiles_n, int &tm, int &tn)
+{
+    constexpr int GM = 8;
+    const int per_group = GM * tiles_n;
+    const int group = id / per_group;
+    const int first = group * GM;
+    const int gsz = min(GM, tiles_m - first);
+    const int r = id - group * per_group;
+    tm = first + r % gsz;
+    tn = r / gsz;
+}
+
+// true if the whole tile lies outside the requested triangle
+__device__ __forceinline__ bool tile_skipped(int tri, int64_t m0, int64_t n0, int bm, int bn)
+{
+    if (tri == 1) return m0 > n0 + bn - 1;      // all rows below the diagonal
+    if (tri == 2) return m0 + bm - 1 < n0;      // all rows above the diagonal
+    return false;
+}
+
+// Thread layout: WARPS_M*WARPS_N consumer warps (whole warpgroups) followed by one
+// producer warpgroup of which a single lane issues the TMA loads.  Registers are
+// budgeted per 4-warp group, so with 8 consumer warps the kernel launches at the
+// 168-register cap of 384 threads and then moves registers from the producer
+// group to the consumers (setmaxnreg), which hold 64 accumulators plus fragments.
+template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B, int STAGES, int MIN_CTAS>
+__global__ void __launch_bounds__((WARPS_M *WARPS_N + 4) * 32, MIN_CTAS)
+dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p)
+{
+    constexpr int NCW = WARPS_M * WARPS_N;          // consumer warps
+    constexpr int WM = BM / WARPS_M, WN = BN / WARPS_N;
+    constexpr int MT = WM / 16, NT = WN / 8;
+    constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN * 128;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static_assert(WM % 16 == 0 && WN % 16 == 0, "warp tile must be a multiple of 16x16");
+
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the swizzle pattern is a function of the address
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                ~uintptr_t(1023));
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    uint64_t *empty = full + STAGES;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + STAGES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NCW);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+    }
+    __syncthreads();
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int kt = (int)((p.k + kBK - 1) / kBK);
+
+    constexpr bool REBALANCE = (NCW == 8 && MIN_CTAS == 1);
+    if (warp >= NCW) {
+        // ---------------- producer warpgroup ----------------
+        if (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == NCW && lane == 0) {
+            uint32_t it = 0;
+            bool live = true;
+            for (int tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
+                int tm, tn;
+                tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
+                const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+                if (tile_skipped(p.tri, m0, n0, BM, BN)) continue;
+                for (int kc = 0; kc < kt; ++kc, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
+                        *abort_flag = 1;
+                        atomicExch(p.err, 101);
+                        live = false;
+                        break;
+                    }
+                    uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    const int k0 = kc * kBK;
+                    if (MAJOR_A == K_MAJOR) {
+                        tma_load_2d(sa, &tmA, k0, (int)m0, &full[s]);
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < BM / 16; ++b)
+                            tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0, &full[s]);
+                    }
+                    if (MAJOR_B == K_MAJOR) {
+                        tma_load_2d(sb, &tmB, k0, (int)n0, &full[s]);
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < BN / 16; ++b)
+                            tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0, &full[s]);
+                    }
+                }
+            }
+            if (!live) {
+                // give loads already in flight a bounded time to land before the CTA retires
+                for (int s = 0; s < STAGES; ++s)
+                    for (int i = 0; i < 1024 && !mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1); ++i)
+                        __nanosleep(256);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    if (REBALANCE) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int wm0 = (warp % WARPS_M) * WM;
+    const int wn0 = (warp / WARPS_M) * WN;
+    uint32_t ba[2], bb[2];
+    frag_base<MAJOR_A>(wm0, lane, ba);
+    frag_base<MAJOR_B>(wn0, lane, bb);
+    const uint32_t smem_base = smem_u32(smem);
+
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        int tm, tn;
+        tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+        if (tile_skipped(p.tri, m0, n0, BM, BN)) continue;
+
+        double acc[MT][NT][4];
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0;
+
+        for (int kc = 0; kc < kt; ++kc, ++it) {
+            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+            if (*abort_flag || !mbar_wait(&full[s], ph)) {
+                *abort_flag = 1;
+                atomicExch(p.err, 102);
+                return;
+            }
+            const uint32_t sA = smem_base + s * STAGE_BYTES;
+            mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane, acc);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Same tiles, filled by ordinary loads: any base alignment, any ld.
+// ---------------------------------------------------------------------------
+template <int BMN, int MAJOR, int NTHREADS>
+__device__ __forceinline__ void ldg_tile(double (&r)[BMN * kBK / NTHREADS], const double *base,
+                                         int64_t ld, int64_t mn0, int64_t mn_ext, int64_t k0,
+                                         int64_t k_ext)
+{
+    // MN-major storage: element (mn, k) at base[mn + k*ld]; K-major: base[k + mn*ld]
+    constexpr int PER = BMN * kBK / NTHREADS;
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+        const int e = threadIdx.x + q * NTHREADS;
+        int rr, kk;
+        if (MAJOR == MN_MAJOR) { rr = e % BMN; kk = e / BMN; }
+        else                   { kk = e % kBK; rr = e / kBK; }
+        const int64_t gmn = mn0 + rr, gk = k0 + kk;
+        double v = 0.0;
+        if (gmn < mn_ext && gk < k_ext)
+            v = (MAJOR == MN_MAJOR) ? __ldg(base + gmn + gk * ld) : __ldg(base + gk + gmn * ld);
+        r[q] = v;
+    }
+}
+
+template <int BMN, int MAJOR, int NTHREADS>
+__device__ __forceinline__ void sts_tile(uint8_t *s, const double (&r)[BMN * kBK / NTHREADS])
+{
+    constexpr int PER = BMN * kBK / NTHREADS;
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+        const int e = threadIdx.x + q * NTHREADS;
+        int rr, kk;
+        if (MAJOR == MN_MAJOR) { rr = e % BMN; kk = e / BMN; }
+        else                   { kk = e % kBK; rr = e / kBK; }
+        *reinterpret_cast<double *>(s + elem_off<MAJOR>(rr, kk)) = r[q];
+    }
+}
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B>
+__global__ void __launch_bounds__(WARPS_M *WARPS_N * 32)
+dgemm_ldg_kernel(const GemmParams p)
+{
+    constexpr int NTHREADS = WARPS_M * WARPS_N * 32;
+    constexpr int WM = BM / WARPS_M, WN = BN / WARPS_N;
+    constexpr int MT = WM / 16, NT = WN / 8;
+    constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN * 128;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm0 = (warp % WARPS_M) * WM;
+    const int wn0 = (warp / WARPS_M) * WN;
+    uint32_t ba[2], bb[2];
+    frag_base<MAJOR_A>(wm0, lane, ba);
+    frag_base<MAJOR_B>(wn0, lane, bb);
+    const uint32_t smem_base = smem_u32(smem);
+
+    const int tile = blockIdx.x;
+    int tm, tn;
+    tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
+    const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+    if (tile_skipped(p.tri, m0, n0, BM, BN)) return;
+    const int kt = (int)((p.k + kBK - 1) / kBK);
+
+    double acc[MT][NT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0;
+
+    double ra[BM * kBK / NTHREADS], rb[BN * kBK / NTHREADS];
+    ldg_tile<BM, MAJOR_A, NTHREADS>(ra, p.A, p.lda, m0, p.m, 0, p.k);
+    ldg_tile<BN, MAJOR_B, NTHREADS>(rb, p.B, p.ldb, n0, p.n, 0, p.k);
+    sts_tile<BM, MAJOR_A, NTHREADS>(smem, ra);
+    sts_tile<BN, MAJOR_B, NTHREADS>(smem + A_BYTES, rb);
+    __syncthreads();
+
+    for (int kc = 0; kc < kt; ++kc) {
+        const int cur = kc & 1;
+        if (kc + 1 < kt) {
+            ldg_tile<BM, MAJOR_A, NTHREADS>(ra, p.A, p.lda, m0, p.m, (int64_t)(kc + 1) * kBK, p.k);
+            ldg_tile<BN, MAJOR_B, NTHREADS>(rb, p.B, p.ldb, n0, p.n, (int64_t)(kc + 1) * kBK, p.k);
+        }
+        const uint32_t sA = smem_base + cur * STAGE_BYTES;
+        mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
+        if (kc + 1 < kt) {
+            uint8_t *nxt = smem + (cur ^ 1) * STAGE_BYTES;
+            sts_tile<BM, MAJOR_A, NTHREADS>(nxt, ra);
+            sts_tile<BN, MAJOR_B, NTHREADS>(nxt + A_BYTES, rb);
+        }
+        __syncthreads();
+    }
+    epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane, acc);
+}
+
+// C <- beta*C (beta == 0 assigns zeros), the alpha == 0 / k == 0 quick path
+// (ulmblas/level3/gemm.tcc:52-55 -> level1extensions/gescal.tcc:11-39).
+__global__ void dscal_matrix_kernel(double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri)
+{
+    const int64_t total = m * n;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = e % m, j = e / m;
+        if (tri == 1 && i > j) continue;
+        if (tri == 2 && i < j) continue;
+        double *c = C + i + j * ldc;
+        *c = (beta == 0.0) ? 0.0 : *c * beta;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri)
+{
+    if (beta == 1.0 || m <= 0 || n <= 0) return ULMB200_OK;
+    int64_t blocks = (m * n + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    dscal_matrix_kernel<<<(int)blocks, 256, 0, st>>>(C, ldc, m, n, beta, tri);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "dscal_matrix_kernel", __FILE__, __LINE__);
+}
+
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B, int STAGES, int CTAS_PER_SM>
+static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, const double *B)
+{
+    constexpr int ctas_per_sm = CTAS_PER_SM;
+    CUtensorMap tmA, tmB;
+    bool ok;
+    // K-major: dim0 = k (contiguous), dim1 = m|n, box 16 x BM|BN.  MN-major: dim0 = m|n, dim1 = k, box 16 x 16.
+    if (MAJOR_A == K_MAJOR)
+        ok = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, A, p.k, p.m, p.lda, kBK, BM);
+    else
+        ok = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, A, p.m, p.k, p.lda, 16, kBK);
+    if (MAJOR_B == K_MAJOR)
+        ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, p.k, p.n, p.ldb, kBK, BN);
+    else
+        ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, p.n, p.k, p.ldb, 16, kBK);
+    if (!ok) return -1;   // caller falls back to the ldg kernel
+
+    constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * 128 + 2 * STAGES * 8 + 16 + 1024;
+    auto kern = dgemm_tma_kernel<BM, BN, WARPS_M, WARPS_N, MAJOR_A, MAJOR_B, STAGES, CTAS_PER_SM>;
+    static bool attr_done[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!attr_done[dev]) {
+        ULMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+        attr_done[dev] = true;
+    }
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
+    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, p);
+    count_launch();
+    ULMB_CUDA(cudaGetLastError());
+    return ULMB200_OK;
+}
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B>
+static int launch_ldg(cudaStream_t st, const GemmParams &p)
+{
+    constexpr size_t SMEM = (size_t)2 * (BM + BN) * 128 + 1024;
+    auto kern = dgemm_ldg_kernel<BM, BN, WARPS_M, WARPS_N, MAJOR_A, MAJOR_B>;
+    static bool attr_done[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!attr_done[dev]) {
+        ULMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+        attr_done[dev] = true;
+    }
+    kern<<<p.tiles_m * p.tiles_n, WARPS_M * WARPS_N * 32, SMEM, st>>>(p);
+    count_launch();
+    ULMB_CUDA(cudaGetLastError());
+    return ULMB200_OK;
+}
+
+template <int MAJOR_A, int MAJOR_B>
+static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, int force_tile, int force_path)
+{
+    // Large tiles once they fill the machine; small tiles for small problems.
+    const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+    bool big = t128 >= (int64_t)sm_count() * 3 / 4;
+    if (force_tile == 128) big = true;
+    if (force_tile == 64) big = false;
+    if (force_path == 1) tma_ok = false;
+    if (big) {
+        p.tiles_m = (int)((p.m + 127) / 128);
+        p.tiles_n = (int)((p.n + 127) / 128);
+        if (tma_ok) {
+            int r = launch_tma<128, 128, 2, 4, MAJOR_A, MAJOR_B, 4, 1>(st, p, p.A, p.B);
+            if (r >= 0) return r;
+        }
+        return launch_ldg<128, 128, 2, 4, MAJOR_A, MAJOR_B>(st, p);
+    }
+    p.tiles_m = (int)((p.m + 63) / 64);
+    p.tiles_n = (int)((p.n + 63) / 64);
+    if (tma_ok) {
+        int r = launch_tma<64, 64, 2, 2, MAJOR_A, MAJOR_B, 4, 2>(st, p, p.A, p.B);
+        if (r >= 0) return r;
+    }
+    return launch_ldg<64, 64, 2, 2, MAJOR_A, MAJOR_B>(st, p);
+}
+
+// Test hooks (environment, read per call so tests can flip them):
+//   ULMB200_DGEMM_TILE = 64 | 128   force a tile shape
+//   ULMB200_DGEMM_PATH = ldg        force the non-TMA kernel
+static void read_overrides(int &tile, int &path)
+{
+    tile = 0; path = 0;
+    if (const char *t = getenv("ULMB200_DGEMM_TILE")) tile = atoi(t);
+    if (const char *s = getenv("ULMB200_DGEMM_PATH")) path = (s[0] == 'l') ? 1 : 0;
+}
+
+int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
+                 int64_t k, double alpha, const double *A, int64_t lda, const double *B,
+                 int64_t ldb, double beta, double *C, int64_t ldc)
+{
+    if (m < 0 || n < 0 || k < 0) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t rowsA = transA ? k : m, rowsB = transB ? n : k;
+    if (lda < (rowsA > 1 ? rowsA : 1) || ldb < (rowsB > 1 ? rowsB : 1) || ldc < (m > 1 ? m : 1))
+        return set_status(ULMB200_BAD_ARGUMENT);
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int st0 = ensure_device()) return set_status(st0);
+
+    if (alpha == 0.0 || k == 0) return set_status(scale_matrix_device(st, C, ldc, m, n, beta, tri));
+
+    GemmParams p;
+    p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
+    p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
+    p.tiles_m = p.tiles_n = 0; p.tri = tri;
+    p.err = device_error_word();
+    if (!p.err) return set_status(ULMB200_CUDA_ERROR);
+
+    // TMA needs 16-byte aligned bases and row pitches, and 32-bit coordinates.
+    const bool tma_ok = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
+                        (lda % 2 == 0) && (ldb % 2 == 0) && m < (1ll << 31) - 256 &&
+                        n < (1ll << 31) - 256 && k < (1ll << 31) - 256 &&
+                        lda < (1ll << 36) && ldb < (1ll << 36);
+    int ftile, fpath;
+    read_overrides(ftile, fpath);
+    int r;
+    if (!transA && !transB)      r = dispatch<MN_MAJOR, K_MAJOR>(st, p, tma_ok, ftile, fpath);
+    else if (!transA && transB)  r = dispatch<MN_MAJOR, MN_MAJOR>(st, p, tma_ok, ftile, fpath);
+    else if (transA && !transB)  r = dispatch<K_MAJOR, K_MAJOR>(st, p, tma_ok, ftile, fpath);
+    else                         r = dispatch<K_MAJOR, MN_MAJOR>(st, p, tma_ok, ftile, fpath);
+    return set_status(r);
+}
+
+}  // namespace ulmb200
+
+extern "C" int ulmb200_dgemm(void *stream, int transA, int transB, int64_t m, int64_t n, int64_t k,
+                             double alpha, const double *dA, int64_t ldA, const double *dB,
+                             int64_t ldB, double beta, double *dC, int64_t ldC)
+{
+    return ulmb200::dgemm_device(static_cast<cudaStream_t>(stream), 0, transA, transB, m, n, k,
+                                 alpha, dA, ldA, dB, ldB, beta, dC, ldC);
+}

@@ -1,0 +1,255 @@
+// The Level-3 routines the reference builds on its gemm macro-kernel, rebuilt on
+// the device GEMM:
+//
+//   dsyrk  ulmblas/level3/syurk.tcc, sylrk.tcc (+ mkernel/msy?rk, ukernel/usy?rk):
+//          the reference restricts its block loops to one triangle and masks
+//          the diagonal tiles; here the GEMM kernel gets a triangle predicate
+//          (whole tiles outside the triangle are never scheduled, tiles on the
+//          diagonal mask their stores), so the other triangle is never touched.
+//
+//   dtrsm  ulmblas/level3/trlsm.tcc, trusm.tcc (+ mkernel/mtr?sm, ukernel/utr?sm,
+//          pack/tr?spack): the reference solves 4x4 diagonal tiles by
+//          multiplying with reciprocal diagonals and pushes everything else
+//          through its gemm macro-kernel.  Here the diagonal blocks are 128x128,
+//          inverted once by a small kernel, and every other flop -- applying a
+//          block inverse, updating the remaining rows -- is a device GEMM,
+//          arranged recursively so the updates have large inner dimensions.
+#include "common.h"
+
+namespace ulmb200 {
+
+int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
+                 int64_t k, double alpha, const double *A, int64_t lda, const double *B,
+                 int64_t ldb, double beta, double *C, int64_t ldc);
+
+int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri);
+
+// ---------------------------------------------------------------------------
+// syrk
+// ---------------------------------------------------------------------------
+int dsyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
+                 const double *A, int64_t lda, double beta, double *C, int64_t ldc)
+{
+    if (n < 0 || k < 0) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t rowsA = trans ? k : n;
+    if (lda < (rowsA > 1 ? rowsA : 1) || ldc < (n > 1 ? n : 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    // quick returns of syurk.tcc:44-51
+    if (n == 0 || ((alpha == 0.0 || k == 0) && beta == 1.0)) return set_status(ULMB200_OK);
+    const int tri = lower ? 2 : 1;
+    // op(A) * op(A)^T: the second operand is the same array read with the opposite transposition
+    return dgemm_device(st, tri, trans ? 1 : 0, trans ? 0 : 1, n, n, k, alpha, A, lda, A, lda, beta, C, ldc);
+}
+
+// ---------------------------------------------------------------------------
+// trsm
+// ---------------------------------------------------------------------------
+constexpr int kNB = 128;          // diagonal block size
+
+// Inverse of one triangular diagonal block per CTA.  T(i,p) = A[i*sr + p*sc]
+// addresses the block as a LOWER triangular matrix (an upper-stored block is
+// read transposed); X = T^-1 is built row by row,
+//     x(i,:) = (e_i - sum_{p<i} T(i,p) x(p,:)) / T(i,i),
+// thread j owning column j.  The result is written as the inverse of the block
+// as stored (so transposed back for upper), the other triangle zero-filled.
+__global__ void __launch_bounds__(kNB)
+trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *inv)
+{
+    extern __shared__ double X[];           // X[p*kNB + j]
+    const int blk = blockIdx.x;
+    const int64_t r0 = (int64_t)blk * kNB;
+    const int len = (int)((dim - r0) < kNB ? (dim - r0) : kNB);
+    const double *Ab = A + r0 + r0 * lda;
+    const int64_t sr = lower ? 1 : lda, sc = lower ? lda : 1;
+    const int j = threadIdx.x;
+
+    for (int i = 0; i < len; ++i) {
+        double s = (i == j) ? 1.0 : 0.0;
+        // columns j > i stay zero; rows p < j of column j are zero, start at p = j
+        if (j <= i) {
+            for (int p = j; p < i; ++p) s -= __ldg(Ab + i * sr + p * sc) * X[p * kNB + j];
+            if (!unit) s /= __ldg(Ab + i * sr + i * sc);
+        }
+        X[i * kNB + j] = s;
+    }
+    __syncthreads();
+    // write the full kNB x kNB block (zeros outside len x len and outside the triangle)
+    double *out = inv + (int64_t)blk * kNB * kNB;
+    for (int i = 0; i < kNB; ++i) {
+        // element (i, j) of the lower-view inverse
+        double v = (i < len && j < len && j <= i) ? X[i * kNB + j] : 0.0;
+        if (lower) out[i + j * kNB] = v;      // coalescing is irrelevant at this size
+        else       out[j + i * kNB] = v;
+    }
+}
+
+__global__ void copy_matrix_kernel(double *dst, int64_t ldd, const double *src, int64_t lds,
+                                   int64_t rows, int64_t cols)
+{
+    const int64_t total = rows * cols;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = e % rows, j = e / rows;
+        dst[i + j * ldd] = src[i + j * lds];
+    }
+}
+
+struct TrsmCtx {
+    cudaStream_t st;
+    int left, lower, trans;
+    int eff_lower;            // op(A) is lower triangular
+    int64_t m, n;             // B is m x n
+    const double *A; int64_t lda;
+    double *B; int64_t ldb;
+    const double *inv;        // kNB x kNB inverses of the diagonal blocks
+    double *W; int64_t ldw;   // leaf result before it is copied back
+    int status;
+};
+
+static void launch_copy(TrsmCtx &c, double *dst, int64_t ldd, const double *src, int64_t lds,
+                        int64_t rows, int64_t cols)
+{
+    int64_t blocks = (rows * cols + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    copy_matrix_kernel<<<(int)blocks, 256, 0, c.st>>>(dst, ldd, src, lds, rows, cols);
+    count_launch();
+}
+
+// element block (i0.., j0..) of op(A): pointer + flag for the GEMM
+static const double *opA_block(const TrsmCtx &c, int64_t i0, int64_t j0)
+{
+    return c.trans ? c.A + j0 + i0 * c.lda : c.A + i0 + j0 * c.lda;
+}
+
+static void gemm_chk(TrsmCtx &c, int ta, int tb, int64_t m, int64_t n, int64_t k, double alpha,
+                     const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
+                     double *C, int64_t ldc)
+{
+    if (c.status != ULMB200_OK) return;
+    c.status = dgemm_device(c.st, 0, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+}
+
+// Left:  rows [r0, r0+len) of B <- op(A)[r0.., r0..]^-1 * B[r0.., :]
+static void solve_left(TrsmCtx &c, int64_t r0, int64_t len)
+{
+    if (c.status != ULMB200_OK) return;
+    if (len <= kNB) {
+        const double *iv = c.inv + (r0 / kNB) * kNB * kNB;
+        gemm_chk(c, c.trans, 0, len, c.n, len, 1.0, iv, kNB, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
+        launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
+        return;
+    }
+    const int64_t half = ((len / 2 + kNB - 1) / kNB) * kNB;
+    const int64_t l1 = half, l2 = len - half;
+    if (c.eff_lower) {
+        solve_left(c, r0, l1);
+        // B2 -= op(A)[r0+l1.., r0..r0+l1) * X1
+        gemm_chk(c, c.trans, 0, l2, c.n, l1, -1.0, opA_block(c, r0 + l1, r0), c.lda, c.B + r0, c.ldb,
+                 1.0, c.B + r0 + l1, c.ldb);
+        solve_left(c, r0 + l1, l2);
+    } else {
+        solve_left(c, r0 + l1, l2);
+        // B1 -= op(A)[r0..r0+l1, r0+l1..) * X2
+        gemm_chk(c, c.trans, 0, l1, c.n, l2, -1.0, opA_block(c, r0, r0 + l1), c.lda, c.B + r0 + l1,
+                 c.ldb, 1.0, c.B + r0, c.ldb);
+        solve_left(c, r0, l1);
+    }
+}
+
+// Right: columns [c0, c0+len) of B <- B[:, c0..] * op(A)[c0.., c0..]^-1
+static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
+{
+    if (c.status != ULMB200_OK) return;
+    if (len <= kNB) {
+        const double *iv = c.inv + (c0 / kNB) * kNB * kNB;
+        gemm_chk(c, 0, c.trans, c.m, len, len, 1.0, c.B + c0 * c.ldb, c.ldb, iv, kNB, 0.0, c.W, c.ldw);
+        launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
+        return;
+    }
+    const int64_t half = ((len / 2 + kNB - 1) / kNB) * kNB;
+    const int64_t l1 = half, l2 = len - half;
+    if (c.eff_lower) {
+        // X * L = B: last columns first, then B1 -= X2 * L21
+        solve_right(c, c0 + l1, l2);
+        gemm_chk(c, 0, c.trans, c.m, l1, l2, -1.0, c.B + (c0 + l1) * c.ldb, c.ldb,
+                 opA_block(c, c0 + l1, c0), c.lda, 1.0, c.B + c0 * c.ldb, c.ldb);
+        solve_right(c, c0, l1);
+    } else {
+        // X * U = B: first columns first, then B2 -= X1 * U12
+        solve_right(c, c0, l1);
+        gemm_chk(c, 0, c.trans, c.m, l2, l1, -1.0, c.B + c0 * c.ldb, c.ldb,
+                 opA_block(c, c0, c0 + l1), c.lda, 1.0, c.B + (c0 + l1) * c.ldb, c.ldb);
+        solve_right(c, c0 + l1, l2);
+    }
+}
+
+// Shared by the allocating entry point and any caller that brings its own
+// scratch: inv must hold ceil(dim/kNB) * kNB * kNB doubles, W kNB*n (left) or
+// m*kNB (right) doubles.
+int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m,
+                       int64_t n, double alpha, const double *A, int64_t lda, double *B,
+                       int64_t ldb, double *inv, double *W)
+{
+    const int left = (side == 0);
+    const int64_t dim = left ? m : n;
+    if (alpha == 0.0)              // trlsm.tcc:46-49
+        return scale_matrix_device(st, B, ldb, m, n, 0.0, 0);
+    if (alpha != 1.0) {
+        int s = scale_matrix_device(st, B, ldb, m, n, alpha, 0);
+        if (s != ULMB200_OK) return s;
+    }
+    const int nblk = (int)((dim + kNB - 1) / kNB);
+    static bool attr_done[kMaxDevices] = {};
+    const int dev = current_device();
+    const int smem = kNB * kNB * (int)sizeof(double);
+    if (!attr_done[dev]) {
+        ULMB_CUDA(cudaFuncSetAttribute(trtri_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done[dev] = true;
+    }
+    trtri_blocks_kernel<<<nblk, kNB, smem, st>>>(A, lda, dim, lower, unit, inv);
+    count_launch();
+    ULMB_CUDA(cudaGetLastError());
+
+    TrsmCtx c;
+    c.st = st; c.left = left; c.lower = lower; c.trans = transA;
+    c.eff_lower = (lower != 0) != (transA != 0);
+    c.m = m; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb;
+    c.inv = inv; c.W = W; c.ldw = left ? kNB : m;
+    c.status = ULMB200_OK;
+    if (left) solve_left(c, 0, m);
+    else      solve_right(c, 0, n);
+    return c.status;
+}
+
+int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                 double alpha, const double *A, int64_t lda, double *B, int64_t ldb)
+{
+    if (m < 0 || n < 0 || (side != 0 && side != 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t dim = (side == 0) ? m : n;
+    if (lda < (dim > 1 ? dim : 1) || ldb < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s = ensure_device()) return set_status(s);
+    const int64_t nblk = (dim + kNB - 1) / kNB;
+    double *inv = static_cast<double *>(device_scratch(3, (size_t)nblk * kNB * kNB * sizeof(double)));
+    const int64_t wel = (side == 0) ? (int64_t)kNB * n : m * (int64_t)kNB;
+    double *W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
+    if (!inv || !W) return set_status(ULMB200_CUDA_ERROR);
+    return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, A, lda, B, ldb, inv, W));
+}
+
+}  // namespace ulmb200
+
+extern "C" int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int64_t k, double alpha,
+                             const double *dA, int64_t ldA, double beta, double *dC, int64_t ldC)
+{
+    return ulmb200::dsyrk_device(static_cast<cudaStream_t>(stream), lower, trans, n, k, alpha, dA, ldA,
+                                 beta, dC, ldC);
+}
+
+extern "C" int ulmb200_dtrsm(void *stream, int side, int lower, int transA, int unit, int64_t m,
+                             int64_t n, double alpha, const double *dA, int64_t ldA, double *dB,
+                             int64_t ldB)
+{
+    return ulmb200::dtrsm_device(static_cast<cudaStream_t>(stream), side, lower, transA, unit, m, n, alpha,
+                                 dA, ldA, dB, ldB);
+}

@@ -1,0 +1,268 @@
+// FP32 GEMM on the FP32 FMA pipes:  C <- alpha*op(A)*op(B) + beta*C.
+//
+// Replaces the float instantiation of the reference's gemm path
+// (ulmblas/level3/gemm.tcc with ukernel/ref/ugemm.tcc, MR=8 NR=4).  The
+// reference's sgemm_ widens to double internally (interfaces/blas/F77/gemm.cc:33,36);
+// this kernel accumulates in FP32, which stays inside the 2*k*eps32 componentwise
+// bound the results are held to.
+//
+// 128x128x16 CTA tile, 256 threads, 8x8 outputs per thread.  Operand tiles are
+// kept in shared memory as [k][m] / [k][n] whatever the global layout (the
+// transposition happens on the way in), so every thread reads its A and B
+// slivers with 16-byte loads that are broadcast within the warp: 4 shared
+// wavefronts per 64 FMAs per warp.
+#include "common.h"
+
+namespace ulmb200 {
+
+namespace sg {
+constexpr int BM = 128, BN = 128, BK = 16, NT = 256;
+constexpr int LDS_ = BM + 4;                 // padded row of a [k][m] tile, floats
+constexpr int TILE = BK * LDS_;              // floats per operand tile
+}  // namespace sg
+
+struct SgemmParams {
+    int64_t m, n, k;
+    float alpha, beta;
+    const float *A, *B;
+    int64_t lda, ldb;
+    float *C;
+    int64_t ldc;
+    int tiles_m, tiles_n;
+};
+
+// Global -> registers for one 128 x 16 operand tile.
+//   MN-contiguous storage (element (r,kk) at base[r + kk*ld]): each thread takes two
+//   runs of 4 consecutive r.  K-contiguous storage (base[kk + r*ld]): two runs of 4
+//   consecutive kk for one r.  VEC: 16-byte loads are legal (aligned base and ld).
+template <bool K_CONTIG, bool VEC>
+__device__ __forceinline__ void sg_load(float (&v)[8], const float *base, int64_t ld, int64_t r0,
+                                        int64_t r_ext, int64_t k0, int64_t k_ext)
+{
+    using namespace sg;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int f = threadIdx.x + q * NT;            // which float4 of the tile
+        int r, kk;
+        if (!K_CONTIG) { r = (f % (BM / 4)) * 4; kk = f / (BM / 4); }
+        else           { r = f % BM;             kk = (f / BM) * 4; }
+        const int64_t gr = r0 + r, gk = k0 + kk;
+        const float *p = K_CONTIG ? base + gk + gr * ld : base + gr + gk * ld;
+        const bool inner_full = K_CONTIG ? (gk + 3 < k_ext) : (gr + 3 < r_ext);
+        const bool outer_ok = K_CONTIG ? (gr < r_ext) : (gk < k_ext);
+        if (VEC && inner_full && outer_ok) {
+            const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+            v[4 * q + 0] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const bool ok = outer_ok && (K_CONTIG ? (gk + e < k_ext) : (gr + e < r_ext));
+                v[4 * q + e] = ok ? __ldg(p + e) : 0.0f;
+            }
+        }
+    }
+}
+
+// Registers -> shared [k][r] tile.
+template <bool K_CONTIG>
+__device__ __forceinline__ void sg_store(float *tile, const float (&v)[8])
+{
+    using namespace sg;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int f = threadIdx.x + q * NT;
+        if (!K_CONTIG) {
+            const int r = (f % (BM / 4)) * 4, kk = f / (BM / 4);
+            *reinterpret_cast<float4 *>(tile + kk * LDS_ + r) =
+                make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+            const int r = f % BM, kk = (f / BM) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tile[(kk + e) * LDS_ + r] = v[4 * q + e];
+        }
+    }
+}
+
+template <bool TA, bool TB, bool VEC>
+__global__ void __launch_bounds__(sg::NT, 2) sgemm_fp32_kernel(const SgemmParams p)
+{
+    using namespace sg;
+    extern __shared__ float smem_f[];
+    float *As = smem_f;                     // [2][TILE]
+    float *Bs = smem_f + 2 * TILE;          // [2][TILE]
+
+    // tile order: groups of 8 tile-rows swept column by column (L2 reuse)
+    int tm, tn;
+    {
+        constexpr int GM = 8;
+        const int id = blockIdx.x, per_group = GM * p.tiles_n, group = id / per_group;
+        const int first = group * GM, gsz = min(GM, p.tiles_m - first), r = id - group * per_group;
+        tm = first + r % gsz;
+        tn = r / gsz;
+    }
+    const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm0 = (warp & 1) * 64, wn0 = (warp >> 1) * 32;
+    const int ly = lane >> 2, lx = lane & 3;
+    const int am = wm0 + ly * 4;            // rows am..am+3 and am+32..am+35
+    const int bn = wn0 + lx * 4;            // cols bn..bn+3 and bn+16..bn+19
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    const int kt = (int)((p.k + BK - 1) / BK);
+    float ra[8], rb[8];
+    // op(A) is m x k: stored MN-contiguous when not transposed, K-contiguous when transposed.
+    // op(B) is k x n: stored K-contiguous when not transposed, N-contiguous when transposed.
+    sg_load<TA, VEC>(ra, p.A, p.lda, m0, p.m, 0, p.k);
+    sg_load<!TB, VEC>(rb, p.B, p.ldb, n0, p.n, 0, p.k);
+    sg_store<TA>(As, ra);
+    sg_store<!TB>(Bs, rb);
+    __syncthreads();
+
+    for (int kc = 0; kc < kt; ++kc) {
+        const int cur = kc & 1;
+        if (kc + 1 < kt) {
+            sg_load<TA, VEC>(ra, p.A, p.lda, m0, p.m, (int64_t)(kc + 1) * BK, p.k);
+            sg_load<!TB, VEC>(rb, p.B, p.ldb, n0, p.n, (int64_t)(kc + 1) * BK, p.k);
+        }
+        const float *a_t = As + cur * TILE, *b_t = Bs + cur * TILE;
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(a_t + kk * LDS_ + am);
+            const float4 a1 = *reinterpret_cast<const float4 *>(a_t + kk * LDS_ + am + 32);
+            const float4 b0 = *reinterpret_cast<const float4 *>(b_t + kk * LDS_ + bn);
+            const float4 b1 = *reinterpret_cast<const float4 *>(b_t + kk * LDS_ + bn + 16);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kc + 1 < kt) {
+            sg_store<TA>(As + (cur ^ 1) * TILE, ra);
+            sg_store<!TB>(Bs + (cur ^ 1) * TILE, rb);
+        }
+        __syncthreads();
+    }
+
+    // epilogue: column-major C, 4 consecutive rows per 16-byte store when legal
+    const float alpha = p.alpha, beta = p.beta;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int64_t col = n0 + bn + (j & 3) + (j >> 2) * 16;
+        if (col >= p.n) continue;
+#pragma unroll
+        for (int ih = 0; ih < 2; ++ih) {
+            const int64_t row = m0 + am + ih * 32;
+            float *c = p.C + row + col * p.ldc;
+            if (VEC && row + 3 < p.m && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
+                float4 o = make_float4(alpha * acc[4 * ih][j], alpha * acc[4 * ih + 1][j],
+                                       alpha * acc[4 * ih + 2][j], alpha * acc[4 * ih + 3][j]);
+                if (beta != 0.0f) {
+                    const float4 old = *reinterpret_cast<const float4 *>(c);
+                    o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y);
+                    o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w);
+                }
+                *reinterpret_cast<float4 *>(c) = o;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (row + e < p.m) {
+                        float o = alpha * acc[4 * ih + e][j];
+                        if (beta != 0.0f) o = fmaf(beta, c[e], o);
+                        c[e] = o;
+                    }
+                }
+            }
+        }
+    }
+}
+
+__global__ void sscal_matrix_kernel(float *C, int64_t ldc, int64_t m, int64_t n, float beta)
+{
+    const int64_t total = m * n;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        float *c = C + e % m + (e / m) * ldc;
+        *c = (beta == 0.0f) ? 0.0f : *c * beta;
+    }
+}
+
+template <bool TA, bool TB, bool VEC>
+static int launch_fp32(cudaStream_t st, const SgemmParams &p)
+{
+    constexpr int SMEM = 4 * sg::TILE * (int)sizeof(float);
+    auto kern = sgemm_fp32_kernel<TA, TB, VEC>;
+    static bool attr_done[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!attr_done[dev]) {
+        ULMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        attr_done[dev] = true;
+    }
+    kern<<<p.tiles_m * p.tiles_n, sg::NT, SMEM, st>>>(p);
+    count_launch();
+    ULMB_CUDA(cudaGetLastError());
+    return ULMB200_OK;
+}
+
+int sgemm_3xtf32_device(cudaStream_t st, int transA, int transB, int64_t m, int64_t n, int64_t k,
+                        float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
+                        float beta, float *C, int64_t ldc);
+
+int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, int64_t n,
+                 int64_t k, float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
+                 float beta, float *C, int64_t ldc)
+{
+    if (m < 0 || n < 0 || k < 0) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t rowsA = transA ? k : m, rowsB = transB ? n : k;
+    if (lda < (rowsA > 1 ? rowsA : 1) || ldb < (rowsB > 1 ? rowsB : 1) || ldc < (m > 1 ? m : 1))
+        return set_status(ULMB200_BAD_ARGUMENT);
+    if (mode != ULMB200_SGEMM_FP32 && mode != ULMB200_SGEMM_3XTF32) return set_status(ULMB200_BAD_ARGUMENT);
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+
+    if (alpha == 0.0f || k == 0) {
+        if (beta == 1.0f) return set_status(ULMB200_OK);
+        int64_t blocks = (m * n + 255) / 256;
+        const int64_t cap = (int64_t)sm_count() * 16;
+        if (blocks > cap) blocks = cap;
+        sscal_matrix_kernel<<<(int)blocks, 256, 0, st>>>(C, ldc, m, n, beta);
+        count_launch();
+        return set_status(check_cuda(cudaGetLastError(), "sscal_matrix_kernel", __FILE__, __LINE__));
+    }
+    if (mode == ULMB200_SGEMM_3XTF32)
+        return set_status(sgemm_3xtf32_device(st, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc));
+
+    SgemmParams p;
+    p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
+    p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
+    p.tiles_m = (int)((m + sg::BM - 1) / sg::BM);
+    p.tiles_n = (int)((n + sg::BN - 1) / sg::BN);
+    const bool vec = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
+                     lda % 4 == 0 && ldb % 4 == 0;
+    int r;
+#define ULMB_SG(TA_, TB_)                                                          \
+    r = vec ? launch_fp32<TA_, TB_, true>(st, p) : launch_fp32<TA_, TB_, false>(st, p)
+    if (!transA && !transB)      { ULMB_SG(false, false); }
+    else if (!transA && transB)  { ULMB_SG(false, true); }
+    else if (transA && !transB)  { ULMB_SG(true, false); }
+    else                         { ULMB_SG(true, true); }
+#undef ULMB_SG
+    return set_status(r);
+}
+
+}  // namespace ulmb200
+
+extern "C" int ulmb200_sgemm(void *stream, int mode, int transA, int transB, int64_t m, int64_t n,
+                             int64_t k, float alpha, const float *dA, int64_t ldA, const float *dB,
+                             int64_t ldB, float beta, float *dC, int64_t ldC)
+{
+    return ulmb200::sgemm_device(static_cast<cudaStream_t>(stream), mode, transA, transB, m, n, k, alpha,
+                                 dA, ldA, dB, ldB, beta, dC, ldC);
+}
