@@ -60,6 +60,17 @@ __global__ void __launch_bounds__(256) probe_kernel(int iters, double *sink)
             } else if (WHICH == 5) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) facc[s * 4 + q] = fmaf(facc[s * 4 + q], fa, fb);
+            } else if (WHICH == 7) {
+                // packed FP32: two FMAs per lane per instruction
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    unsigned long long d, a2, b2;
+                    asm("mov.b64 %0, {%1,%2};" : "=l"(d) : "f"(facc[s * 4 + 2 * q]), "f"(facc[s * 4 + 2 * q + 1]));
+                    asm("mov.b64 %0, {%1,%1};" : "=l"(a2) : "f"(fa));
+                    asm("mov.b64 %0, {%1,%1};" : "=l"(b2) : "f"(fb));
+                    asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(d) : "l"(a2), "l"(b2));
+                    asm("mov.b64 {%0,%1}, %2;" : "=f"(facc[s * 4 + 2 * q]), "=f"(facc[s * 4 + 2 * q + 1]) : "l"(d));
+                }
             }
         }
     }
@@ -119,6 +130,7 @@ extern "C" int ulmb200_peak_probe(int which, int iters, double *tflops, double *
     case 4: st = run_probe<4>(iters, blocks, &ms); flops_per_set = 2.0 * 4 * 32; break;
     case 5: st = run_probe<5>(iters, blocks, &ms); flops_per_set = 2.0 * 4 * 32; break;
     case 6: st = run_probe<6>(iters, blocks, &ms); flops_per_set = 2.0 * 16 * 8 * 8 + 2.0 * 4 * 32; break;
+    case 7: st = run_probe<7>(iters, blocks, &ms); flops_per_set = 2.0 * 4 * 32; break;
     default: return set_status(ULMB200_BAD_ARGUMENT);
     }
     if (st != ULMB200_OK) return set_status(st);
