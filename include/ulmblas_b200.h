@@ -158,6 +158,21 @@ int ulmb200_dtrsm(void *stream, int side, int lower, int transA, int unit,
                   int64_t m, int64_t n, double alpha,
                   const double *dA, int64_t ldA, double *dB, int64_t ldB);
 
+/* Same operation and arguments as ulmb200_dtrsm, for callers that are not allowed to
+ * allocate device memory (a latency-critical loop, a plug-in with a fixed memory budget,
+ * a process whose device memory is fully committed elsewhere).  It has no counterpart in
+ * the reference.  The solver's work areas live in a fixed array inside the library image
+ * (about 6.3 MB on every GPU that loads the library, until exit) instead of the growing
+ * cache ulmb200_dtrsm uses; no cudaMalloc/cudaFree or allocating routine is called.
+ * Limits: triangle at most 2048 x 2048, the other dimension of B at most 4096; larger
+ * requests return ULMB200_TOO_LARGE and launch nothing.  All calls on a GPU share the one
+ * array, so calls that overlap in time on the same GPU race -- serialise them.  The first
+ * call on each device resolves the array's device address and sets kernel attributes; make
+ * that call before starting any stream capture.                                         */
+int ulmb200_dtrsm_noalloc(void *stream, int side, int lower, int transA, int unit,
+                          int64_t m, int64_t n, double alpha,
+                          const double *dA, int64_t ldA, double *dB, int64_t ldB);
+
 /* `lower`-or-upper triangle of C <- alpha*op(A)*op(A)^T + beta*C.
  * Replaces ulmBLAS::syurk / sylrk (ulmblas/level3/syurk.tcc, sylrk.tcc).      */
 int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int64_t k,
@@ -190,7 +205,8 @@ int ulmb200_abs_f64(void *stream, double *d, int64_t ld, int64_t rows, int64_t c
 /* Register-only throughput probes (FP64 DMMA shapes, FP64 FMA, FP32 FMA):
  * runs `iters` dependent-free instruction groups per warp on every SM and
  * returns achieved TFLOP/s in *tflops.  which: 0 dmma.m8n8k4, 1 dmma.m16n8k4,
- * 2 dmma.m16n8k8, 3 dmma.m16n8k16, 4 dfma, 5 ffma, 6 dmma+dfma mixed.         */
+ * 2 dmma.m16n8k8, 3 dmma.m16n8k16, 4 dfma, 5 ffma, 6 dmma+dfma mixed,
+ * 7 packed fma.rn.f32x2.         */
 int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms);
 
 /* Number of kernels this library has launched in this process so far.        */

@@ -51,6 +51,7 @@ lib.ulmb200_launch_count.restype = _i64
 lib.ulmb200_dgemm.argtypes = [_vp, _int, _int, _i64, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_sgemm.argtypes = [_vp, _int, _int, _int, _i64, _i64, _i64, _flt, _vp, _i64, _vp, _i64, _flt, _vp, _i64]
 lib.ulmb200_dtrsm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
+lib.ulmb200_dtrsm_noalloc.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
 lib.ulmb200_dsyrk.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_fill_f64.argtypes = [_vp, _vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64, _int, _dbl]
 lib.ulmb200_fill_f32.argtypes = [_vp, _vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64]
@@ -166,6 +167,14 @@ def dev_sgemm(mode, transA, transB, m, n, k, alpha, dA, lda, dB, ldb, beta, dC, 
 def dev_dtrsm(side, lower, transA, unit, m, n, alpha, dA, lda, dB, ldb, stream=0):
     _check(lib.ulmb200_dtrsm(stream, int(side), int(lower), int(transA), int(unit), m, n, alpha, dA, lda,
                              dB, ldb), "ulmb200_dtrsm")
+
+
+def dev_dtrsm_noalloc(side, lower, transA, unit, m, n, alpha, dA, lda, dB, ldb, stream=0):
+    """ulmb200_dtrsm on the library's built-in work area: never allocates device memory.
+    Triangle <= 2048, other dimension <= 4096 (status TOO_LARGE beyond); calls on one GPU
+    must not overlap in time.  Returns the status instead of raising."""
+    return lib.ulmb200_dtrsm_noalloc(stream, int(side), int(lower), int(transA), int(unit), m, n, alpha,
+                                     dA, lda, dB, ldb)
 
 
 def dev_dsyrk(lower, trans, n, k, alpha, dA, lda, beta, dC, ldc, stream=0):

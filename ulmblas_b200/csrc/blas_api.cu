@@ -20,9 +20,6 @@
 
 namespace ulmb200 {
 
-int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
-                 int64_t k, double alpha, const double *A, int64_t lda, const double *B,
-                 int64_t ldb, double beta, double *C, int64_t ldc);
 int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, int64_t n,
                  int64_t k, float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
                  float beta, float *C, int64_t ldc);
@@ -107,6 +104,13 @@ static cudaError_t copy_out(T *h, int64_t ldh, const T *d, int64_t ldd, int64_t 
 
 static int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
+// bytes spanned by a rows x cols column-major matrix with leading dimension ld
+template <typename T>
+static size_t span_bytes(int64_t rows, int64_t cols, int64_t ld)
+{
+    return (rows > 0 && cols > 0) ? sizeof(T) * (size_t)((cols - 1) * ld + rows) : 0;
+}
+
 static int finish(Streams *s)
 {
     cudaError_t e = cudaStreamSynchronize(s->in);
@@ -150,9 +154,9 @@ static int gemm_any(Launch launch, int transA, int transB, int64_t m, int64_t n,
     if (!dC) { Cd = static_cast<T *>(device_scratch(2, sizeof(T) * dldc * n)); uc = dldc; }
     if (!Ad || !Bd || !Cd) return set_status(ULMB200_CUDA_ERROR);
 
-    HostPin pa(dA ? nullptr : A, sizeof(T) * ((colsA - 1) * lda + rowsA));
-    HostPin pb(dB ? nullptr : B, sizeof(T) * ((colsB - 1) * ldb + rowsB));
-    HostPin pc(dC ? nullptr : C, sizeof(T) * ((n - 1) * ldc + m));
+    HostPin pa(dA ? nullptr : A, span_bytes<T>(rowsA, colsA, lda));
+    HostPin pb(dB ? nullptr : B, span_bytes<T>(rowsB, colsB, ldb));
+    HostPin pc(dC ? nullptr : C, span_bytes<T>(m, n, ldc));
 
     cudaError_t e = cudaSuccess;
     if (!dA && k > 0) e = copy_in(const_cast<T *>(Ad), ua, A, lda, rowsA, colsA, s->in);

@@ -49,6 +49,19 @@ EncodeTiledFn encode_tiled_fn();
 bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base,
                   uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1);
 
+// C <- alpha*op(A)*op(B) + beta*C on device operands (dgemm_sm100.cu).  tri: 0 full, 1 upper
+// triangle only, 2 lower.  err_word: device word a kernel writes when a bounded wait runs out;
+// nullptr selects the library's own per-device word.
+int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n, int64_t k,
+                 double alpha, const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
+                 double *C, int64_t ldc, int *err_word = nullptr);
+int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri);
+// B <- alpha*op(A)^-1*B (side 0) or alpha*B*op(A)^-1 (side 1) with caller-provided scratch
+// (level3_sm100.cu): inv holds ceil(dim/128)*128*128 doubles, W 128*n (left) or m*128 (right).
+int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                       double alpha, const double *A, int64_t lda, double *B, int64_t ldb, double *inv,
+                       double *W, int *err_word = nullptr);
+
 #ifdef __CUDACC__
 // ---- device-side PTX wrappers ---------------------------------------------
 

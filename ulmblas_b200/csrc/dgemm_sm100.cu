@@ -497,7 +497,7 @@ static void read_overrides(int &tile, int &path)
 
 int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
                  int64_t k, double alpha, const double *A, int64_t lda, const double *B,
-                 int64_t ldb, double beta, double *C, int64_t ldc)
+                 int64_t ldb, double beta, double *C, int64_t ldc, int *err_word)
 {
     if (m < 0 || n < 0 || k < 0) return set_status(ULMB200_BAD_ARGUMENT);
     const int64_t rowsA = transA ? k : m, rowsB = transB ? n : k;
@@ -512,7 +512,7 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
     p.tiles_m = p.tiles_n = 0; p.tri = tri;
-    p.err = device_error_word();
+    p.err = err_word ? err_word : device_error_word();
     if (!p.err) return set_status(ULMB200_CUDA_ERROR);
 
     // TMA needs 16-byte aligned bases and row pitches, and 32-bit coordinates.

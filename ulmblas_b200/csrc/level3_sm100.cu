@@ -18,12 +18,6 @@
 
 namespace ulmb200 {
 
-int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
-                 int64_t k, double alpha, const double *A, int64_t lda, const double *B,
-                 int64_t ldb, double beta, double *C, int64_t ldc);
-
-int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri);
-
 // ---------------------------------------------------------------------------
 // syrk
 // ---------------------------------------------------------------------------
@@ -102,6 +96,7 @@ struct TrsmCtx {
     double *B; int64_t ldb;
     const double *inv;        // kNB x kNB inverses of the diagonal blocks
     double *W; int64_t ldw;   // leaf result before it is copied back
+    int *err;                 // error word handed to the GEMM kernels (nullptr = library default)
     int status;
 };
 
@@ -126,7 +121,7 @@ static void gemm_chk(TrsmCtx &c, int ta, int tb, int64_t m, int64_t n, int64_t k
                      double *C, int64_t ldc)
 {
     if (c.status != ULMB200_OK) return;
-    c.status = dgemm_device(c.st, 0, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    c.status = dgemm_device(c.st, 0, ta, tb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, c.err);
 }
 
 // Left:  rows [r0, r0+len) of B <- op(A)[r0.., r0..]^-1 * B[r0.., :]
@@ -188,7 +183,7 @@ static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
 // m*kNB (right) doubles.
 int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m,
                        int64_t n, double alpha, const double *A, int64_t lda, double *B,
-                       int64_t ldb, double *inv, double *W)
+                       int64_t ldb, double *inv, double *W, int *err_word)
 {
     const int left = (side == 0);
     const int64_t dim = left ? m : n;
@@ -215,6 +210,7 @@ int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int uni
     c.eff_lower = (lower != 0) != (transA != 0);
     c.m = m; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb;
     c.inv = inv; c.W = W; c.ldw = left ? kNB : m;
+    c.err = err_word;
     c.status = ULMB200_OK;
     if (left) solve_left(c, 0, m);
     else      solve_right(c, 0, n);
