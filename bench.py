@@ -39,7 +39,8 @@ def parse():
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=65536)
     ap.add_argument("--k", type=int, default=16384)
-    ap.add_argument("--kp", type=int, default=2048, help="K-panel of the A broadcast (N > 1)")
+    ap.add_argument("--kp", type=int, default=4096, help="K-panel of the A broadcast (N > 1)")
+    ap.add_argument("--kp-first", type=int, default=1024, help="short first panel (N > 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--extra", action="store_true", help="also time 16384^3 on one GPU (N = 1)")
@@ -198,7 +199,7 @@ def main():
     if rank == 0:
         peak_tf = max(ulm.peak_probe(2, 4000)[0], ulm.peak_probe(2, 20000)[0])
 
-    eng = ShardedDgemm(m, n, k, kp=a.kp)
+    eng = ShardedDgemm(m, n, k, kp=a.kp, first=a.kp_first)
 
     def barrier():
         torch.cuda.synchronize()
@@ -274,14 +275,15 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": t_ms / a.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": workload_name(a), "m": m, "n": n, "k": k, "kp": (k if world == 1 else a.kp),
+            "config": {"workload": workload_name(a), "m": m, "n": n, "k": k, "k_panels": [l1 - l0 for (l0, l1) in eng.plan.panels],
                        "parallelism": f"column blocks x{world}", "l2": "operands (>= 8 GB per GPU) exceed L2"},
             "roofline": {"bound": "tensor", "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (ach_tf / peak_tf) if (ach_tf and peak_tf) else None,
                          "traffic": None,
                          "peak_source": "FP64 DMMA (mma.sync m16n8k8.f64) register-only probe run on this GPU "
                                         "just before the timed region; MEASURED_PEAKS.json holds no FP64 figure",
-                         "kernel": "dgemm_tma_kernel<128,128>", "launches_timed": len(kdur)},
+                         "kernel": "dgemm_tma_kernel<128,128>", "launches_timed": len(kdur),
+                         "launch_ms_first_step": [round(x, 3) for x in kdur[:len(eng.plan.panels)]]},
             "cpu_baseline": cpu,
             "e2e": e2e,
             "gpu_launches": launches,

@@ -34,6 +34,7 @@ def test_k_panels():
     assert k_panels(8, 100) == [(0, 8)]
     assert PanelPlan(4, 4, 16384, 1, 0, 2048).panels == [(0, 16384)]          # one GPU: one piece
     assert len(PanelPlan(4, 4, 16384, 8, 0, 2048).panels) == 8
+    assert PanelPlan(4, 4, 16384, 8, 0, 4096, 1024).panels == [(0, 1024), (1024, 5120), (5120, 9216), (9216, 13312), (13312, 16384)]
 
 
 def test_run_panels_orders_beta_and_waits():

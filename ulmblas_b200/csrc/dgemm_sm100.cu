@@ -94,34 +94,75 @@ __device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32
 }
 
 // C(row, col) <- alpha*acc + beta*C for the warp's accumulators; rows/cols
-// outside m x n (and outside the requested triangle) are skipped.
+// outside m x n (and outside the requested triangle) are skipped.  Per m16 tile
+// all old values of C are fetched first (independent loads in flight together),
+// then combined and stored.  With M-contiguous A the two rows a lane holds are
+// adjacent (2g, 2g+1), so a 16-byte aligned C moves them as one 16-byte access.
 template <int MAJOR_A, int MAJOR_B, int MT, int NT>
 __device__ __forceinline__ void epilogue(const GemmParams &p, int64_t m0, int64_t n0, int wm0,
                                          int wn0, int lane, double (&acc)[MT][NT][4])
 {
     const double alpha = p.alpha, beta = p.beta;
+    const bool use_c = beta != 0.0;
+    const bool vec = MAJOR_A == MN_MAJOR && p.tri == 0 &&
+                     ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 2 == 0);
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
+        const int64_t r0 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 0);
+        const int64_t r1 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 1);
+        if (vec && r1 < p.m) {
+            // rows r0 (even) and r1 = r0 + 1: registers {0,2} of column 2t, {1,3} of column 2t+1
+            double2 old[NT][2];
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int64_t row = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, half);
+            for (int j = 0; j < NT; ++j)
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
-                    bool ok = row < p.m && col < p.n;
-                    if (p.tri == 1) ok = ok && row <= col;
-                    if (p.tri == 2) ok = ok && row >= col;
-                    if (ok) {
-                        double *c = p.C + row + col * p.ldc;
-                        double v = alpha * acc[i][j][2 * half + w];
-                        if (beta != 0.0) v = fma(beta, *c, v);
-                        *c = v;
+                    old[j][w] = (use_c && col < p.n)
+                                    ? *reinterpret_cast<const double2 *>(p.C + r0 + col * p.ldc)
+                                    : make_double2(0.0, 0.0);
+                }
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
+                    if (col < p.n) {
+                        double2 o;
+                        o.x = alpha * acc[i][j][w];
+                        o.y = alpha * acc[i][j][2 + w];
+                        if (use_c) { o.x = fma(beta, old[j][w].x, o.x); o.y = fma(beta, old[j][w].y, o.y); }
+                        *reinterpret_cast<double2 *>(p.C + r0 + col * p.ldc) = o;
                     }
                 }
-            }
+            continue;
         }
+        double old[NT][4];
+        bool ok[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int64_t row = (e >> 1) ? r1 : r0;
+                const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
+                bool v = row < p.m && col < p.n;
+                if (p.tri == 1) v = v && row <= col;
+                if (p.tri == 2) v = v && row >= col;
+                ok[j][e] = v;
+                old[j][e] = (v && use_c) ? p.C[row + col * p.ldc] : 0.0;
+            }
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (ok[j][e]) {
+                    const int64_t row = (e >> 1) ? r1 : r0;
+                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
+                    double v = alpha * acc[i][j][e];
+                    if (use_c) v = fma(beta, old[j][e], v);
+                    p.C[row + col * p.ldc] = v;
+                }
+            }
     }
 }
 

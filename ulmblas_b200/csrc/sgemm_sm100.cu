@@ -6,19 +6,22 @@
 // this kernel accumulates in FP32, which stays inside the 2*k*eps32 componentwise
 // bound the results are held to.
 //
-// 128x128x16 CTA tile, 256 threads, 8x8 outputs per thread.  Operand tiles are
-// kept in shared memory as [k][m] / [k][n] whatever the global layout (the
-// transposition happens on the way in), so every thread reads its A and B
-// slivers with 16-byte loads that are broadcast within the warp: 4 shared
-// wavefronts per 64 FMAs per warp.
+// 256x128x16 CTA tile, 256 threads, 16x8 outputs per thread, one CTA per SM.
+// Operand tiles are kept in shared memory as [k][m] / [k][n] whatever the global
+// layout (the transposition happens on the way in).  Measured on this part, a
+// 16-byte shared load costs 2 cycles when each aligned group of 4 lanes reads one
+// address and 4 cycles otherwise, so the long side of the thread tile (16 rows of
+// A, 4 loads) is indexed by lane/4 and the short side (8 columns of B, 2 loads)
+// by lane%4: 16 shared-memory cycles per 128 FMAs.  The FMAs are issued as packed
+// fma.rn.f32x2 on row pairs, which halves the issue slots they need.
 #include "common.h"
 
 namespace ulmb200 {
 
 namespace sg {
-constexpr int BM = 128, BN = 128, BK = 16, NT = 256;
-constexpr int LDS_ = BM + 4;                 // padded row of a [k][m] tile, floats
-constexpr int TILE = BK * LDS_;              // floats per operand tile
+constexpr int BM = 256, BN = 128, BK = 16, NT = 256;
+constexpr int LDA_ = BM + 4, LDB_ = BN + 4;      // padded rows of the [k][m] / [k][n] tiles, floats
+constexpr int A_TILE = BK * LDA_, B_TILE = BK * LDB_;
 }  // namespace sg
 
 struct SgemmParams {
@@ -31,21 +34,22 @@ struct SgemmParams {
     int tiles_m, tiles_n;
 };
 
-// Global -> registers for one 128 x 16 operand tile.
-//   MN-contiguous storage (element (r,kk) at base[r + kk*ld]): each thread takes two
-//   runs of 4 consecutive r.  K-contiguous storage (base[kk + r*ld]): two runs of 4
-//   consecutive kk for one r.  VEC: 16-byte loads are legal (aligned base and ld).
-template <bool K_CONTIG, bool VEC>
-__device__ __forceinline__ void sg_load(float (&v)[8], const float *base, int64_t ld, int64_t r0,
-                                        int64_t r_ext, int64_t k0, int64_t k_ext)
+// Global -> registers for one BMN x 16 operand tile, BMN*16/4/256 float4 per thread.
+//   MN-contiguous storage (element (r,kk) at base[r + kk*ld]): runs of 4 consecutive r.
+//   K-contiguous storage (base[kk + r*ld]): runs of 4 consecutive kk for one r.
+//   VEC: 16-byte loads are legal (aligned base and ld).
+template <int BMN, bool K_CONTIG, bool VEC>
+__device__ __forceinline__ void sg_load(float (&v)[BMN * sg::BK / sg::NT], const float *base, int64_t ld,
+                                        int64_t r0, int64_t r_ext, int64_t k0, int64_t k_ext)
 {
     using namespace sg;
+    constexpr int NQ = BMN * BK / 4 / NT;
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
+    for (int q = 0; q < NQ; ++q) {
         const int f = threadIdx.x + q * NT;            // which float4 of the tile
         int r, kk;
-        if (!K_CONTIG) { r = (f % (BM / 4)) * 4; kk = f / (BM / 4); }
-        else           { r = f % BM;             kk = (f / BM) * 4; }
+        if (!K_CONTIG) { r = (f % (BMN / 4)) * 4; kk = f / (BMN / 4); }
+        else           { r = f % BMN;             kk = (f / BMN) * 4; }
         const int64_t gr = r0 + r, gk = k0 + kk;
         const float *p = K_CONTIG ? base + gk + gr * ld : base + gr + gk * ld;
         const bool inner_full = K_CONTIG ? (gk + 3 < k_ext) : (gr + 3 < r_ext);
@@ -63,33 +67,39 @@ __device__ __forceinline__ void sg_load(float (&v)[8], const float *base, int64_
     }
 }
 
-// Registers -> shared [k][r] tile.
-template <bool K_CONTIG>
-__device__ __forceinline__ void sg_store(float *tile, const float (&v)[8])
+// Registers -> shared [k][r] tile with row pitch LD floats.
+template <int BMN, int LD, bool K_CONTIG>
+__device__ __forceinline__ void sg_store(float *tile, const float (&v)[BMN * sg::BK / sg::NT])
 {
     using namespace sg;
+    constexpr int NQ = BMN * BK / 4 / NT;
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
+    for (int q = 0; q < NQ; ++q) {
         const int f = threadIdx.x + q * NT;
         if (!K_CONTIG) {
-            const int r = (f % (BM / 4)) * 4, kk = f / (BM / 4);
-            *reinterpret_cast<float4 *>(tile + kk * LDS_ + r) =
+            const int r = (f % (BMN / 4)) * 4, kk = f / (BMN / 4);
+            *reinterpret_cast<float4 *>(tile + kk * LD + r) =
                 make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         } else {
-            const int r = f % BM, kk = (f / BM) * 4;
+            const int r = f % BMN, kk = (f / BMN) * 4;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) tile[(kk + e) * LDS_ + r] = v[4 * q + e];
+            for (int e = 0; e < 4; ++e) tile[(kk + e) * LD + r] = v[4 * q + e];
         }
     }
 }
 
+__device__ __forceinline__ void ffma2(uint64_t &d, uint64_t a, uint64_t b)
+{
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+
 template <bool TA, bool TB, bool VEC>
-__global__ void __launch_bounds__(sg::NT, 2) sgemm_fp32_kernel(const SgemmParams p)
+__global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams p)
 {
     using namespace sg;
     extern __shared__ float smem_f[];
-    float *As = smem_f;                     // [2][TILE]
-    float *Bs = smem_f + 2 * TILE;          // [2][TILE]
+    float *As = smem_f;                       // [2][A_TILE]
+    float *Bs = smem_f + 2 * A_TILE;          // [2][B_TILE]
 
     // tile order: groups of 8 tile-rows swept column by column (L2 reuse)
     int tm, tn;
@@ -103,50 +113,62 @@ __global__ void __launch_bounds__(sg::NT, 2) sgemm_fp32_kernel(const SgemmParams
     const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wm0 = (warp & 1) * 64, wn0 = (warp >> 1) * 32;
+    const int wm0 = (warp & 1) * 128, wn0 = (warp >> 1) * 32;
     const int ly = lane >> 2, lx = lane & 3;
-    const int am = wm0 + ly * 4;            // rows am..am+3 and am+32..am+35
-    const int bn = wn0 + lx * 4;            // cols bn..bn+3 and bn+16..bn+19
+    const int am = wm0 + ly * 4;            // rows am + 32r + {0..3}, r = 0..3
+    const int bn = wn0 + lx * 4;            // cols bn + 16c + {0..3}, c = 0..1
 
-    float acc[8][8];
+    uint64_t acc[8][8];                     // [row pair][column]: rows (am + 32(p/2) + 2(p%2)) + {0,1}
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
 
     const int kt = (int)((p.k + BK - 1) / BK);
-    float ra[8], rb[8];
+    float ra[BM * BK / NT], rb[BN * BK / NT];
     // op(A) is m x k: stored MN-contiguous when not transposed, K-contiguous when transposed.
     // op(B) is k x n: stored K-contiguous when not transposed, N-contiguous when transposed.
-    sg_load<TA, VEC>(ra, p.A, p.lda, m0, p.m, 0, p.k);
-    sg_load<!TB, VEC>(rb, p.B, p.ldb, n0, p.n, 0, p.k);
-    sg_store<TA>(As, ra);
-    sg_store<!TB>(Bs, rb);
+    sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, 0, p.k);
+    sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, 0, p.k);
+    sg_store<BM, LDA_, TA>(As, ra);
+    sg_store<BN, LDB_, !TB>(Bs, rb);
     __syncthreads();
 
     for (int kc = 0; kc < kt; ++kc) {
         const int cur = kc & 1;
         if (kc + 1 < kt) {
-            sg_load<TA, VEC>(ra, p.A, p.lda, m0, p.m, (int64_t)(kc + 1) * BK, p.k);
-            sg_load<!TB, VEC>(rb, p.B, p.ldb, n0, p.n, (int64_t)(kc + 1) * BK, p.k);
+            sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, (int64_t)(kc + 1) * BK, p.k);
+            sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, (int64_t)(kc + 1) * BK, p.k);
         }
-        const float *a_t = As + cur * TILE, *b_t = Bs + cur * TILE;
+        const uint32_t a_s = smem_u32(As + cur * A_TILE + am);
+        const uint32_t b_s = smem_u32(Bs + cur * B_TILE + bn);
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
-            const float4 a0 = *reinterpret_cast<const float4 *>(a_t + kk * LDS_ + am);
-            const float4 a1 = *reinterpret_cast<const float4 *>(a_t + kk * LDS_ + am + 32);
-            const float4 b0 = *reinterpret_cast<const float4 *>(b_t + kk * LDS_ + bn);
-            const float4 b1 = *reinterpret_cast<const float4 *>(b_t + kk * LDS_ + bn + 16);
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            uint64_t a2[8], b2[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int r = 0; r < 4; ++r)
+                asm volatile("ld.shared.v2.b64 {%0,%1}, [%2];"
+                             : "=l"(a2[2 * r]), "=l"(a2[2 * r + 1])
+                             : "r"(a_s + (kk * LDA_ + 32 * r) * 4));
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            for (int c = 0; c < 2; ++c) {
+                float4 b;
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                             : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
+                             : "r"(b_s + (kk * LDB_ + 16 * c) * 4));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 0]) : "f"(b.x));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 1]) : "f"(b.y));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 2]) : "f"(b.z));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 3]) : "f"(b.w));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ffma2(acc[i][j], a2[i], b2[j]);
         }
         if (kc + 1 < kt) {
-            sg_store<TA>(As + (cur ^ 1) * TILE, ra);
-            sg_store<!TB>(Bs + (cur ^ 1) * TILE, rb);
+            sg_store<BM, LDA_, TA>(As + (cur ^ 1) * A_TILE, ra);
+            sg_store<BN, LDB_, !TB>(Bs + (cur ^ 1) * B_TILE, rb);
         }
         __syncthreads();
     }
@@ -158,12 +180,14 @@ __global__ void __launch_bounds__(sg::NT, 2) sgemm_fp32_kernel(const SgemmParams
         const int64_t col = n0 + bn + (j & 3) + (j >> 2) * 16;
         if (col >= p.n) continue;
 #pragma unroll
-        for (int ih = 0; ih < 2; ++ih) {
-            const int64_t row = m0 + am + ih * 32;
+        for (int r = 0; r < 4; ++r) {
+            const int64_t row = m0 + am + 32 * r;
+            float v[4];
+            asm("mov.b64 {%0,%1}, %2;" : "=f"(v[0]), "=f"(v[1]) : "l"(acc[2 * r][j]));
+            asm("mov.b64 {%0,%1}, %2;" : "=f"(v[2]), "=f"(v[3]) : "l"(acc[2 * r + 1][j]));
             float *c = p.C + row + col * p.ldc;
             if (VEC && row + 3 < p.m && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
-                float4 o = make_float4(alpha * acc[4 * ih][j], alpha * acc[4 * ih + 1][j],
-                                       alpha * acc[4 * ih + 2][j], alpha * acc[4 * ih + 3][j]);
+                float4 o = make_float4(alpha * v[0], alpha * v[1], alpha * v[2], alpha * v[3]);
                 if (beta != 0.0f) {
                     const float4 old = *reinterpret_cast<const float4 *>(c);
                     o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y);
@@ -174,7 +198,7 @@ __global__ void __launch_bounds__(sg::NT, 2) sgemm_fp32_kernel(const SgemmParams
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (row + e < p.m) {
-                        float o = alpha * acc[4 * ih + e][j];
+                        float o = alpha * v[e];
                         if (beta != 0.0f) o = fmaf(beta, c[e], o);
                         c[e] = o;
                     }
@@ -197,7 +221,7 @@ __global__ void sscal_matrix_kernel(float *C, int64_t ldc, int64_t m, int64_t n,
 template <bool TA, bool TB, bool VEC>
 static int launch_fp32(cudaStream_t st, const SgemmParams &p)
 {
-    constexpr int SMEM = 4 * sg::TILE * (int)sizeof(float);
+    constexpr int SMEM = 2 * (sg::A_TILE + sg::B_TILE) * (int)sizeof(float);
     auto kern = sgemm_fp32_kernel<TA, TB, VEC>;
     static bool attr_done[kMaxDevices] = {};
     const int dev = current_device();

@@ -33,12 +33,20 @@ def column_block(n, world, rank, align=ALIGN):
     return min(u0 * align, n), min(u1 * align, n)
 
 
-def k_panels(k, kp):
-    """[(l0, l1)] covering [0, k) in panels of kp (the last may be short)."""
+def k_panels(k, kp, first=None):
+    """[(l0, l1)] covering [0, k): an optional short first panel (so the first product can start
+    early), then panels of kp (the last may be short)."""
     if k <= 0:
         return []
     kp = max(1, min(kp, k))
-    return [(l0, min(l0 + kp, k)) for l0 in range(0, k, kp)]
+    out, l0 = [], 0
+    if first is not None and 0 < first < kp and first < k:
+        out.append((0, first))
+        l0 = first
+    while l0 < k:
+        out.append((l0, min(l0 + kp, k)))
+        l0 += kp
+    return out
 
 
 @dataclass
@@ -49,6 +57,7 @@ class PanelPlan:
     world: int
     rank: int
     kp: int
+    first: int = None
 
     @property
     def cols(self):
@@ -57,7 +66,9 @@ class PanelPlan:
     @property
     def panels(self):
         # one GPU needs no transport, so it multiplies in one piece
-        return k_panels(self.k, self.k if self.world == 1 else self.kp)
+        if self.world == 1:
+            return k_panels(self.k, self.k)
+        return k_panels(self.k, self.kp, self.first)
 
 
 def run_panels(plan, alpha, beta, A_panel, recv_panel, gemm):
@@ -93,7 +104,7 @@ class ShardedDgemm:
     Cr : (nr, m)  this rank's column block of C  (column-major m x nr, ld = m)
     """
 
-    def __init__(self, m, n, k, kp=2048, group=None, root=0):
+    def __init__(self, m, n, k, kp=4096, first=1024, group=None, root=0):
         import torch
         import torch.distributed as dist
         from . import api
@@ -101,7 +112,7 @@ class ShardedDgemm:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.group, self.root = group, root
-        self.plan = PanelPlan(m, n, k, self.world, self.rank, kp)
+        self.plan = PanelPlan(m, n, k, self.world, self.rank, kp, first)
         self.compute = torch.cuda.Stream()
         self.comm = torch.cuda.Stream()
         # when set to a list, run() appends (start_event, end_event, flops) per GEMM launch,
