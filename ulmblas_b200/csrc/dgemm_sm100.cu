@@ -19,6 +19,8 @@
 #include "common.h"
 #include "tile_layout.h"
 
+#include <atomic>
+
 namespace ulmb200 {
 
 struct GemmParams {
@@ -31,6 +33,7 @@ struct GemmParams {
     int tiles_m, tiles_n;
     int tri;                  // 0 full, 1 upper triangle only (row<=col), 2 lower (row>=col)
     int *err;                 // device error word
+    int *tile_counter;        // zeroed before the launch; hands out tiles beyond the first wave
 };
 
 __device__ __forceinline__ void dmma_16x8x8(double (&c)[4], const double (&a)[4], const double (&b)[2])
@@ -212,6 +215,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
     uint64_t *empty = full + STAGES;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + STAGES);
+    volatile int *tile_slot = abort_flag + 1;      // tile id carried by each stage, -1 = no more work
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -236,40 +240,61 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---------------- producer warpgroup ----------------
         if (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp == NCW && lane == 0) {
+            // Tiles are handed out dynamically: the first one is the CTA's own index, the rest come
+            // from a global counter.  A CTA that starts late (its SM was busy with another
+            // kernel, e.g. a collective) then simply takes fewer tiles instead of holding up the
+            // whole grid with a fixed share.
             uint32_t it = 0;
             bool live = true;
-            for (int tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
-                int tm, tn;
-                tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
-                const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
-                if (tile_skipped(p.tri, m0, n0, BM, BN)) continue;
-                for (int kc = 0; kc < kt; ++kc, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
-                        *abort_flag = 1;
-                        atomicExch(p.err, 101);
-                        live = false;
-                        break;
-                    }
-                    uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
-                    const int k0 = kc * kBK;
-                    if (MAJOR_A == K_MAJOR) {
-                        tma_load_2d(sa, &tmA, k0, (int)m0, &full[s]);
-                    } else {
+            int tile = blockIdx.x;
+            while (live) {
+                bool skip = false;
+                int64_t m0 = 0, n0 = 0;
+                if (tile < num_tiles) {
+                    int tm, tn;
+                    tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
+                    m0 = (int64_t)tm * BM; n0 = (int64_t)tn * BN;
+                    skip = tile_skipped(p.tri, m0, n0, BM, BN);
+                }
+                if (!skip) {
+                    const int nk = tile < num_tiles ? kt : 1;        // one empty stage carries the end mark
+                    for (int kc = 0; kc < nk; ++kc, ++it) {
+                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                        if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
+                            *abort_flag = 1;
+                            atomicExch(p.err, 101);
+                            live = false;
+                            break;
+                        }
+                        if (tile >= num_tiles) {
+                            tile_slot[s] = -1;
+                            mbar_arrive(&full[s]);
+                            live = false;
+                            break;
+                        }
+                        tile_slot[s] = tile;
+                        uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
+                        mbar_expect_tx(&full[s], STAGE_BYTES);
+                        const int k0 = kc * kBK;
+                        if (MAJOR_A == K_MAJOR) {
+                            tma_load_2d(sa, &tmA, k0, (int)m0, &full[s]);
+                        } else {
 #pragma unroll
-                        for (int b = 0; b < BM / 16; ++b)
-                            tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0, &full[s]);
-                    }
-                    if (MAJOR_B == K_MAJOR) {
-                        tma_load_2d(sb, &tmB, k0, (int)n0, &full[s]);
-                    } else {
+                            for (int b = 0; b < BM / 16; ++b)
+                                tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0, &full[s]);
+                        }
+                        if (MAJOR_B == K_MAJOR) {
+                            tma_load_2d(sb, &tmB, k0, (int)n0, &full[s]);
+                        } else {
 #pragma unroll
-                        for (int b = 0; b < BN / 16; ++b)
-                            tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0, &full[s]);
+                            for (int b = 0; b < BN / 16; ++b)
+                                tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0, &full[s]);
+                        }
                     }
                 }
+                if (live) tile = (int)gridDim.x + atomicAdd(p.tile_counter, 1);
             }
+            live = (*abort_flag == 0);
             if (!live) {
                 // give loads already in flight a bounded time to land before the CTA retires
                 for (int s = 0; s < STAGES; ++s)
@@ -290,11 +315,21 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t smem_base = smem_u32(smem);
 
     uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (;;) {
+        // the first stage of a tile tells which tile it is
+        {
+            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+            if (*abort_flag || !mbar_wait(&full[s], ph)) {
+                *abort_flag = 1;
+                atomicExch(p.err, 102);
+                return;
+            }
+        }
+        const int tile = tile_slot[it % STAGES];
+        if (tile < 0) return;
         int tm, tn;
         tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
-        if (tile_skipped(p.tri, m0, n0, BM, BN)) continue;
 
         double acc[MT][NT][4];
 #pragma unroll
@@ -306,7 +341,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
         for (int kc = 0; kc < kt; ++kc, ++it) {
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-            if (*abort_flag || !mbar_wait(&full[s], ph)) {
+            if (kc > 0 && (*abort_flag || !mbar_wait(&full[s], ph))) {
                 *abort_flag = 1;
                 atomicExch(p.err, 102);
                 return;
@@ -466,7 +501,7 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
         ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, p.n, p.k, p.ldb, 16, kBK);
     if (!ok) return -1;   // caller falls back to the ldg kernel
 
-    constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * 128 + 2 * STAGES * 8 + 16 + 1024;
+    constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * 128 + 2 * STAGES * 8 + 16 + 4 * STAGES + 1024;
     auto kern = dgemm_tma_kernel<BM, BN, WARPS_M, WARPS_N, MAJOR_A, MAJOR_B, STAGES, CTAS_PER_SM>;
     static bool attr_done[kMaxDevices] = {};
     const int dev = current_device();
@@ -476,7 +511,13 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
-    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, p);
+    // tile counter: one of 60 words next to the error word, taken round-robin so that launches
+    // in flight on different streams do not share one
+    static std::atomic<unsigned> rr{0};
+    GemmParams q = p;
+    q.tile_counter = p.err + 1 + (rr.fetch_add(1, std::memory_order_relaxed) % 60);
+    ULMB_CUDA(cudaMemsetAsync(q.tile_counter, 0, sizeof(int), st));
+    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, q);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
     return ULMB200_OK;
@@ -552,7 +593,7 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     GemmParams p;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
-    p.tiles_m = p.tiles_n = 0; p.tri = tri;
+    p.tiles_m = p.tiles_n = 0; p.tri = tri; p.tile_counter = nullptr;
     p.err = err_word ? err_word : device_error_word();
     if (!p.err) return set_status(ULMB200_CUDA_ERROR);
 
