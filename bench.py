@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--k", type=int, default=16384)
     ap.add_argument("--kp", type=int, default=4096, help="K-panel of the A broadcast (N > 1)")
     ap.add_argument("--kp-first", type=int, default=1024, help="short first panel (N > 1)")
+    ap.add_argument("--nccl-ctas", type=int, default=8, help="CTAs NCCL may use = SMs the GEMM leaves free")
+    ap.add_argument("--reserve-panels", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--extra", action="store_true", help="also time 16384^3 on one GPU (N = 1)")
@@ -175,6 +177,11 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # keep NCCL's kernels small: they run beside a GEMM grid that leaves them exactly this room
+        os.environ.setdefault("NCCL_MAX_CTAS", str(a.nccl_ctas))
+        os.environ.setdefault("NCCL_MIN_CTAS", "1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"       # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     if a.gpus != world and rank == 0:
         print(f"note: --gpus {a.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
@@ -199,7 +206,8 @@ def main():
     if rank == 0:
         peak_tf = max(ulm.peak_probe(2, 4000)[0], ulm.peak_probe(2, 20000)[0])
 
-    eng = ShardedDgemm(m, n, k, kp=a.kp, first=a.kp_first)
+    eng = ShardedDgemm(m, n, k, kp=a.kp, first=a.kp_first, reserve_sms=a.nccl_ctas,
+                       reserve_panels=a.reserve_panels)
 
     def barrier():
         torch.cuda.synchronize()

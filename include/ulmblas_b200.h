@@ -209,6 +209,12 @@ int ulmb200_abs_f64(void *stream, double *d, int64_t ld, int64_t rows, int64_t c
  * 7 packed fma.rn.f32x2.         */
 int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms);
 
+/* The persistent DGEMM grid normally takes every SM.  A caller that runs a collective
+ * (e.g. the NCCL broadcast of the next A panel) beside it can ask the following DGEMM
+ * launches to leave `sms` SMs free so that the collective's kernels are never starved;
+ * 0 restores the default.  Process-wide.                                               */
+void ulmb200_set_sm_reserve(int sms);
+
 /* Number of kernels this library has launched in this process so far.        */
 int64_t ulmb200_launch_count(void);
 

@@ -61,6 +61,8 @@ lib.ulmb200_host_fill_f32.argtypes = [_vp, _i64, _i64, _i64, _u64, _u32, _i64, _
 lib.ulmb200_host_fill_f32.restype = None
 lib.ulmb200_abs_f64.argtypes = [_vp, _vp, _i64, _i64, _i64]
 lib.ulmb200_peak_probe.argtypes = [_int, _int, _pd, _pd]
+lib.ulmb200_set_sm_reserve.argtypes = [_int]
+lib.ulmb200_set_sm_reserve.restype = None
 lib.ulmb200_set_pin_host.argtypes = [_int]
 lib.ulmb200_set_pin_host.restype = None
 for _name in ("dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "cblas_dgemm", "cblas_sgemm", "cblas_dtrsm",
@@ -201,6 +203,11 @@ def host_fill(a, seed, mat, row0=0, col0=0, dist=0, scale=1.0):
     else:
         raise TypeError("float64 or float32 only")
     return a
+
+
+def set_sm_reserve(sms):
+    """Leave `sms` SMs free in the following persistent DGEMM launches (0 = use them all)."""
+    lib.ulmb200_set_sm_reserve(int(sms))
 
 
 def peak_probe(which, iters=2000):

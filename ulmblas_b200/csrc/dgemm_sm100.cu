@@ -472,6 +472,9 @@ __global__ void dscal_matrix_kernel(double *C, int64_t ldc, int64_t m, int64_t n
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
+// SMs the persistent grid leaves free (for a collective's kernels running beside it)
+static std::atomic<int> g_sm_reserve{0};
+
 int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri)
 {
     if (beta == 1.0 || m <= 0 || n <= 0) return ULMB200_OK;
@@ -510,7 +513,9 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
         attr_done[dev] = true;
     }
     const int tiles = p.tiles_m * p.tiles_n;
-    const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
+    int sms = sm_count() - g_sm_reserve.load(std::memory_order_relaxed);
+    if (sms < 1) sms = 1;
+    const int grid = tiles < sms * ctas_per_sm ? tiles : sms * ctas_per_sm;
     // tile counter: one of 60 words next to the error word, taken round-robin so that launches
     // in flight on different streams do not share one
     static std::atomic<unsigned> rr{0};
@@ -613,6 +618,11 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
 }
 
 }  // namespace ulmb200
+
+extern "C" void ulmb200_set_sm_reserve(int sms)
+{
+    ulmb200::g_sm_reserve.store(sms < 0 ? 0 : sms, std::memory_order_relaxed);
+}
 
 extern "C" int ulmb200_dgemm(void *stream, int transA, int transB, int64_t m, int64_t n, int64_t k,
                              double alpha, const double *dA, int64_t ldA, const double *dB,

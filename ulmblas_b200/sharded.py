@@ -104,7 +104,7 @@ class ShardedDgemm:
     Cr : (nr, m)  this rank's column block of C  (column-major m x nr, ld = m)
     """
 
-    def __init__(self, m, n, k, kp=4096, first=1024, group=None, root=0):
+    def __init__(self, m, n, k, kp=4096, first=1024, group=None, root=0, reserve_sms=8, reserve_panels=2):
         import torch
         import torch.distributed as dist
         from . import api
@@ -118,6 +118,11 @@ class ShardedDgemm:
         # when set to a list, run() appends (start_event, end_event, flops) per GEMM launch,
         # recorded on the launching stream
         self.kernel_events = None
+        # While panels are still travelling, the GEMMs leave a few SMs free so that NCCL's
+        # kernels can always be scheduled next to the persistent grid (bench.py caps NCCL at
+        # the same number of CTAs); later GEMMs take the whole GPU again.
+        self.reserve_sms = reserve_sms if self.world > 1 else 0
+        self.reserve_panels = reserve_panels
 
     def run(self, alpha, A, Br, beta, Cr):
         torch, dist, api, p = self.torch, self.dist, self.api, self.plan
@@ -134,7 +139,11 @@ class ShardedDgemm:
             with torch.cuda.stream(self.comm):
                 return dist.broadcast(h, src=self.root, group=self.group, async_op=True)
 
+        launched = [0]
+
         def gemm(h, l0, l1, beta_l, w):
+            api.set_sm_reserve(self.reserve_sms if launched[0] < self.reserve_panels else 0)
+            launched[0] += 1
             with torch.cuda.stream(self.compute):
                 if w is not None:
                     w.wait()                         # compute stream waits for the panel, host does not
@@ -150,6 +159,7 @@ class ShardedDgemm:
                     self.kernel_events.append((ev[0], ev[1], 2.0 * p.m * nr * (l1 - l0)))
 
         run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
+        api.set_sm_reserve(0)
         cur.wait_stream(self.compute)
         cur.wait_stream(self.comm)
         return j0, j1
