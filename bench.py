@@ -26,6 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SEED = 99
+DRAM_BYTES_PER_FLOP = 67.398e9 / (2.0 * 16384 ** 3)     # measured, see profiles/dgemm_tma_kernel_dram_16384.md
 UNIT = "GFLOP/s"
 METRIC = "DGEMM GFLOP/s (2mnk/t)"
 
@@ -180,8 +181,7 @@ def main():
         # keep NCCL's kernels small: they run beside a GEMM grid that leaves them exactly this room
         os.environ.setdefault("NCCL_MAX_CTAS", str(a.nccl_ctas))
         os.environ.setdefault("NCCL_MIN_CTAS", "1")
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"       # keep stdout to the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     if a.gpus != world and rank == 0:
         print(f"note: --gpus {a.gpus} but WORLD_SIZE={world}; using {world}", file=sys.stderr)
@@ -287,7 +287,12 @@ def main():
                        "parallelism": f"column blocks x{world}", "l2": "operands (>= 8 GB per GPU) exceed L2"},
             "roofline": {"bound": "tensor", "achieved": ach_tf, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (ach_tf / peak_tf) if (ach_tf and peak_tf) else None,
-                         "traffic": None,
+                         # dram__bytes_read+write of one launch, ncu capture at 16384^3 (67.40 GB for
+                         # 8.796 TFLOP, profiles/dgemm_tma_kernel_dram_16384.md) scaled by flops: the
+                         # traffic is (waves x panels per wave), proportional to m*n*k
+                         "traffic": DRAM_BYTES_PER_FLOP * (sum(kflops) / max(len(kflops), 1)) if kflops else None,
+                         "traffic_unit": "bytes per launch (scaled from a smaller ncu capture)",
+                         "algorithmic_bytes": 8.0 * (m * k + k * nr + m * nr) if world == 1 else None,
                          "peak_source": "FP64 DMMA (mma.sync m16n8k8.f64) register-only probe run on this GPU "
                                         "just before the timed region; MEASURED_PEAKS.json holds no FP64 figure",
                          "kernel": "dgemm_tma_kernel<128,128>", "launches_timed": len(kdur),

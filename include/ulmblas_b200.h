@@ -72,6 +72,21 @@ void dsyrk_(const char *upLo, const char *trans, const int *n, const int *k,
             const double *alpha, const double *A, const int *ldA,
             const double *beta, double *C, const int *ldC);
 
+/* replaces F77BLAS(dsymm), interfaces/blas/F77/symm.cc:87-150; xerbla_ codes {1,2,3,4,7,9,12} */
+void dsymm_(const char *side, const char *upLo, const int *m, const int *n,
+            const double *alpha, const double *A, const int *ldA,
+            const double *B, const int *ldB, const double *beta, double *C, const int *ldC);
+
+/* replaces F77BLAS(dtrmm), interfaces/blas/F77/trmm.cc:123-230; codes {1,2,3,4,5,6,9,11}    */
+void dtrmm_(const char *side, const char *upLo, const char *transA, const char *diag,
+            const int *m, const int *n, const double *alpha,
+            const double *A, const int *ldA, double *B, const int *ldB);
+
+/* replaces F77BLAS(dsyr2k), interfaces/blas/F77/syr2k.cc:92-170; codes {1,2,3,4,7,9,12}     */
+void dsyr2k_(const char *upLo, const char *trans, const int *n, const int *k,
+             const double *alpha, const double *A, const int *ldA,
+             const double *B, const int *ldB, const double *beta, double *C, const int *ldC);
+
 /* replaces F77BLAS(xerbla), interfaces/blas/F77/xerbla.cc:6-10.  Weak symbol:
  * a test harness may supply its own, exactly as the Netlib testers do.       */
 void xerbla_(const char rout[6], const int *info);
@@ -178,6 +193,20 @@ int ulmb200_dtrsm_noalloc(void *stream, int side, int lower, int transA, int uni
 int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int64_t k,
                   double alpha, const double *dA, int64_t ldA,
                   double beta, double *dC, int64_t ldC);
+
+/* The other gemm clients of the reference's Level 3 (same conventions as above).
+ * ulmb200_dsymm  replaces ulmBLAS::sylmm / syumm   (ulmblas/level3/sylmm.tcc, syumm.tcc)
+ * ulmb200_dtrmm  replaces ulmBLAS::trlmm / trumm   (ulmblas/level3/trlmm.tcc, trumm.tcc)
+ * ulmb200_dsyr2k replaces ulmBLAS::sylr2k / syur2k (ulmblas/level3/sylr2k.tcc, syur2k.tcc)  */
+int ulmb200_dsymm(void *stream, int side, int lower, int64_t m, int64_t n, double alpha,
+                  const double *dA, int64_t ldA, const double *dB, int64_t ldB,
+                  double beta, double *dC, int64_t ldC);
+int ulmb200_dtrmm(void *stream, int side, int lower, int transA, int unit,
+                  int64_t m, int64_t n, double alpha,
+                  const double *dA, int64_t ldA, double *dB, int64_t ldB);
+int ulmb200_dsyr2k(void *stream, int lower, int trans, int64_t n, int64_t k, double alpha,
+                   const double *dA, int64_t ldA, const double *dB, int64_t ldB,
+                   double beta, double *dC, int64_t ldC);
 
 /* Deterministic test/bench matrices: element (i,j) of matrix `mat` under
  * `seed` is a pure function of (seed, mat, i, j), identical on host and device,

@@ -156,6 +156,40 @@ class Ref:
             _p(Cm), r(ldc or _ld(Cm), _int))
 
 
+def _ref_extra(self):
+    r = self._r
+
+    def dsymm(side, uplo, m, n, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+        self.lib.dsymm_(C.c_char_p(_c(side)), C.c_char_p(_c(uplo)), r(m, _int), r(n, _int), r(alpha, _dbl),
+                        _p(A), r(lda or _ld(A), _int), _p(B), r(ldb or _ld(B), _int), r(beta, _dbl), _p(Cm),
+                        r(ldc or _ld(Cm), _int))
+
+    def dtrmm(side, uplo, ta, diag, m, n, alpha, A, B, lda=None, ldb=None):
+        self.lib.dtrmm_(C.c_char_p(_c(side)), C.c_char_p(_c(uplo)), C.c_char_p(_c(ta)), C.c_char_p(_c(diag)),
+                        r(m, _int), r(n, _int), r(alpha, _dbl), _p(A), r(lda or _ld(A), _int), _p(B),
+                        r(ldb or _ld(B), _int))
+
+    def dsyr2k(uplo, trans, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+        self.lib.dsyr2k_(C.c_char_p(_c(uplo)), C.c_char_p(_c(trans)), r(n, _int), r(k, _int), r(alpha, _dbl),
+                         _p(A), r(lda or _ld(A), _int), _p(B), r(ldb or _ld(B), _int), r(beta, _dbl), _p(Cm),
+                         r(ldc or _ld(Cm), _int))
+
+    return dsymm, dtrmm, dsyr2k
+
+
+def _ref_getattr(self, name):
+    """dsymm / dtrmm / dsyr2k of the compiled reference (interfaces/blas/F77/symm.cc:87,
+    trmm.cc:123, syr2k.cc:92), bound on first use."""
+    if name in ("dsymm", "dtrmm", "dsyr2k"):
+        fns = dict(zip(("dsymm", "dtrmm", "dsyr2k"), _ref_extra(self)))
+        self.__dict__.update(fns)
+        return fns[name]
+    raise AttributeError(name)
+
+
+Ref.__getattr__ = _ref_getattr
+
+
 def fmat(rows, cols, ld=None, dtype=np.float64, fill=None):
     """Column-major rows x cols view on top of an ld x cols allocation (padding = ``fill``)."""
     ld = max(ld or rows, rows, 1)

@@ -65,7 +65,10 @@ lib.ulmb200_set_sm_reserve.argtypes = [_int]
 lib.ulmb200_set_sm_reserve.restype = None
 lib.ulmb200_set_pin_host.argtypes = [_int]
 lib.ulmb200_set_pin_host.restype = None
-for _name in ("dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "cblas_dgemm", "cblas_sgemm", "cblas_dtrsm",
+lib.ulmb200_dsymm.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
+lib.ulmb200_dtrmm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
+lib.ulmb200_dsyr2k.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
+for _name in ("dsymm_", "dtrmm_", "dsyr2k_", "dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "cblas_dgemm", "cblas_sgemm", "cblas_dtrsm",
               "cblas_dsyrk", "ulmblas_dgemm", "ulmblas_sgemm", "ulmblas_dtrsm", "ulmblas_dsyrk"):
     getattr(lib, _name).restype = None
 lib.cblas_dgemm.argtypes = [_int, _int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int, _dbl, _vp, _int]
@@ -151,6 +154,27 @@ def dsyrk(uplo, trans, n, k, alpha, A, beta, Cm, lda=None, ldc=None):
     """One triangle of C <- alpha*op(A)*op(A)^T + beta*C through ``dsyrk_``."""
     lib.dsyrk_(_cp(_c(uplo)), _cp(_c(trans)), _ri(n), _ri(k), C.byref(_dbl(alpha)), _p(A),
                _ri(lda or _ld(A)), C.byref(_dbl(beta)), _p(Cm), _ri(ldc or _ld(Cm)))
+    return last_status()
+
+
+def dsymm(side, uplo, m, n, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+    """C <- alpha*A*B + beta*C (side 'L') or alpha*B*A + beta*C ('R'), A symmetric, through ``dsymm_``."""
+    lib.dsymm_(_cp(_c(side)), _cp(_c(uplo)), _ri(m), _ri(n), C.byref(_dbl(alpha)), _p(A), _ri(lda or _ld(A)),
+               _p(B), _ri(ldb or _ld(B)), C.byref(_dbl(beta)), _p(Cm), _ri(ldc or _ld(Cm)))
+    return last_status()
+
+
+def dtrmm(side, uplo, transA, diag, m, n, alpha, A, B, lda=None, ldb=None):
+    """B <- alpha*op(A)*B or alpha*B*op(A), A triangular, through ``dtrmm_``."""
+    lib.dtrmm_(_cp(_c(side)), _cp(_c(uplo)), _cp(_c(transA)), _cp(_c(diag)), _ri(m), _ri(n),
+               C.byref(_dbl(alpha)), _p(A), _ri(lda or _ld(A)), _p(B), _ri(ldb or _ld(B)))
+    return last_status()
+
+
+def dsyr2k(uplo, trans, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+    """One triangle of C <- alpha*(op(A)*op(B)^T + op(B)*op(A)^T) + beta*C through ``dsyr2k_``."""
+    lib.dsyr2k_(_cp(_c(uplo)), _cp(_c(trans)), _ri(n), _ri(k), C.byref(_dbl(alpha)), _p(A), _ri(lda or _ld(A)),
+                _p(B), _ri(ldb or _ld(B)), C.byref(_dbl(beta)), _p(Cm), _ri(ldc or _ld(Cm)))
     return last_status()
 
 

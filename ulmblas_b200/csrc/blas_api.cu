@@ -27,6 +27,13 @@ int dsyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, do
                  const double *A, int64_t lda, double beta, double *C, int64_t ldc);
 int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                  double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
+int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                 double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
+int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, double alpha, const double *A,
+                 int64_t lda, const double *B, int64_t ldb, double beta, double *C, int64_t ldc);
+int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
+                  const double *A, int64_t lda, const double *B, int64_t ldb, double beta, double *C,
+                  int64_t ldc);
 
 static int g_pin_host = 0;
 
@@ -285,6 +292,89 @@ static int dtrsm_any(int side, int lower, int transA, int unit, int64_t m, int64
     return set_status(finish(s));
 }
 
+// One staged operand: device pointers pass through, host matrices are copied into a cached
+// device buffer (slot) before the call and, when `back`, copied out after it.
+struct Staged {
+    const double *host = nullptr;
+    double *dev = nullptr;
+    int64_t ldh = 0, ldd = 0, rows = 0, cols = 0;
+    bool staged = false;
+};
+
+static int stage_in(Staged &o, const double *p, int64_t ld, int64_t rows, int64_t cols, int slot, bool copy,
+                    cudaStream_t st)
+{
+    o.host = p; o.ldh = ld; o.rows = rows; o.cols = cols;
+    if (on_device(p) || rows <= 0 || cols <= 0) { o.dev = const_cast<double *>(p); o.ldd = ld; return ULMB200_OK; }
+    o.ldd = round_up(rows, 2);
+    o.dev = static_cast<double *>(device_scratch(slot, sizeof(double) * (size_t)(o.ldd * cols)));
+    if (!o.dev) return ULMB200_CUDA_ERROR;
+    o.staged = true;
+    if (copy) return check_cuda(copy_in(o.dev, o.ldd, p, ld, rows, cols, st), "copy in", __FILE__, __LINE__);
+    return ULMB200_OK;
+}
+
+static int stage_out(const Staged &o, cudaStream_t st)
+{
+    if (!o.staged) return ULMB200_OK;
+    return check_cuda(copy_out(const_cast<double *>(o.host), o.ldh, o.dev, o.ldd, o.rows, o.cols, st), "copy out",
+                      __FILE__, __LINE__);
+}
+
+static int dtrmm_any(int side, int lower, int transA, int unit, int64_t m, int64_t n, double alpha,
+                     const double *A, int64_t lda, double *B, int64_t ldb)
+{
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t dim = side == 0 ? m : n;
+    Staged a, b;
+    int st = stage_in(a, A, lda, dim, dim, 0, true, s->run);
+    if (st == ULMB200_OK) st = stage_in(b, B, ldb, m, n, 2, true, s->run);
+    if (st == ULMB200_OK) st = dtrmm_device(s->run, side, lower, transA, unit, m, n, alpha, a.dev, a.ldd, b.dev, b.ldd);
+    if (st == ULMB200_OK) st = stage_out(b, s->run);
+    const int fin = finish(s);
+    return set_status(st != ULMB200_OK ? st : fin);
+}
+
+static int dsymm_any(int side, int lower, int64_t m, int64_t n, double alpha, const double *A, int64_t lda,
+                     const double *B, int64_t ldb, double beta, double *C, int64_t ldc)
+{
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t na = side == 0 ? m : n;
+    Staged a, b, c;
+    int st = stage_in(a, A, lda, na, na, 0, true, s->run);
+    if (st == ULMB200_OK) st = stage_in(b, B, ldb, m, n, 1, true, s->run);
+    if (st == ULMB200_OK) st = stage_in(c, C, ldc, m, n, 2, beta != 0.0, s->run);
+    if (st == ULMB200_OK) st = dsymm_device(s->run, side, lower, m, n, alpha, a.dev, a.ldd, b.dev, b.ldd, beta, c.dev, c.ldd);
+    if (st == ULMB200_OK) st = stage_out(c, s->run);
+    const int fin = finish(s);
+    return set_status(st != ULMB200_OK ? st : fin);
+}
+
+static int dsyr2k_any(int lower, int trans, int64_t n, int64_t k, double alpha, const double *A, int64_t lda,
+                      const double *B, int64_t ldb, double beta, double *C, int64_t ldc)
+{
+    if (n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t rows = trans ? k : n, cols = trans ? n : k;
+    Staged a, b, c;
+    int st = stage_in(a, A, lda, rows, cols, 0, true, s->run);
+    if (st == ULMB200_OK) st = stage_in(b, B, ldb, rows, cols, 1, true, s->run);
+    // the whole square travels both ways; the kernels only touch the requested triangle
+    if (st == ULMB200_OK) st = stage_in(c, C, ldc, n, n, 2, true, s->run);
+    if (st == ULMB200_OK) st = dsyr2k_device(s->run, lower, trans, n, k, alpha, a.dev, a.ldd, b.dev, b.ldd, beta, c.dev, c.ldd);
+    if (st == ULMB200_OK) st = stage_out(c, s->run);
+    const int fin = finish(s);
+    return set_status(st != ULMB200_OK ? st : fin);
+}
+
 // ---- argument decoding shared by the shims ---------------------------------
 static inline int up(const char *c) { return std::toupper((unsigned char)*c); }
 static inline bool is_trans(const char *c) { int u = up(c); return u == 'T' || u == 'C'; }
@@ -395,6 +485,75 @@ void dsyrk_(const char *upLo, const char *trans, const int *n, const int *k, con
         return;
     }
     dsyrk_any(up(upLo) == 'L', is_trans(trans), *n, *k, *alpha, A, *ldA, *beta, C, *ldC);
+}
+
+// replaces F77BLAS(dsymm), interfaces/blas/F77/symm.cc:87-150
+void dsymm_(const char *side, const char *upLo, const int *m, const int *n, const double *alpha,
+            const double *A, const int *ldA, const double *B, const int *ldB, const double *beta,
+            double *C, const int *ldC)
+{
+    const bool left = up(side) == 'L';
+    const int rowsA = left ? *m : *n;
+    int info = 0;
+    if (up(side) != 'L' && up(side) != 'R') info = 1;
+    else if (up(upLo) != 'L' && up(upLo) != 'U') info = 2;
+    else if (*m < 0) info = 3;
+    else if (*n < 0) info = 4;
+    else if (*ldA < std::max(1, rowsA)) info = 7;
+    else if (*ldB < std::max(1, *m)) info = 9;
+    else if (*ldC < std::max(1, *m)) info = 12;
+    if (info != 0) {
+        xerbla_("DSYMM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    dsymm_any(left ? 0 : 1, up(upLo) == 'L', *m, *n, *alpha, A, *ldA, B, *ldB, *beta, C, *ldC);
+}
+
+// replaces F77BLAS(dtrmm), interfaces/blas/F77/trmm.cc:123-230
+void dtrmm_(const char *side, const char *upLo, const char *transA, const char *diag, const int *m,
+            const int *n, const double *alpha, const double *A, const int *ldA, double *B,
+            const int *ldB)
+{
+    const bool left = up(side) == 'L';
+    const int rowsA = left ? *m : *n;
+    int info = 0;
+    if (up(side) != 'L' && up(side) != 'R') info = 1;
+    else if (up(upLo) != 'L' && up(upLo) != 'U') info = 2;
+    else if (!valid_trans(transA)) info = 3;
+    else if (up(diag) != 'U' && up(diag) != 'N') info = 4;
+    else if (*m < 0) info = 5;
+    else if (*n < 0) info = 6;
+    else if (*ldA < std::max(1, rowsA)) info = 9;
+    else if (*ldB < std::max(1, *m)) info = 11;
+    if (info != 0) {
+        xerbla_("DTRMM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    dtrmm_any(left ? 0 : 1, up(upLo) == 'L', is_trans(transA), up(diag) == 'U', *m, *n, *alpha, A, *ldA, B, *ldB);
+}
+
+// replaces F77BLAS(dsyr2k), interfaces/blas/F77/syr2k.cc:92-170
+void dsyr2k_(const char *upLo, const char *trans, const int *n, const int *k, const double *alpha,
+             const double *A, const int *ldA, const double *B, const int *ldB, const double *beta,
+             double *C, const int *ldC)
+{
+    const int rows = is_trans(trans) ? *k : *n;
+    int info = 0;
+    if (up(upLo) != 'L' && up(upLo) != 'U') info = 1;
+    else if (!valid_trans(trans)) info = 2;
+    else if (*n < 0) info = 3;
+    else if (*k < 0) info = 4;
+    else if (*ldA < std::max(1, rows)) info = 7;
+    else if (*ldB < std::max(1, rows)) info = 9;
+    else if (*ldC < std::max(1, *n)) info = 12;
+    if (info != 0) {
+        xerbla_("DSYR2K", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    dsyr2k_any(up(upLo) == 'L', is_trans(trans), *n, *k, *alpha, A, *ldA, B, *ldB, *beta, C, *ldC);
 }
 
 // ------------------------------- CBLAS ---------------------------------------

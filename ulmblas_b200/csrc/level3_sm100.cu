@@ -233,6 +233,168 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
     return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, A, lda, B, ldb, inv, W));
 }
 
+// ---------------------------------------------------------------------------
+// syr2k:  triangle of  C <- alpha*(op(A)*op(B)^T + op(B)*op(A)^T) + beta*C
+// (ulmblas/level3/syur2k.tcc:18-127, sylr2k.tcc: two passes of the gemm macro-kernel
+// per block; here two passes of the device GEMM with the triangle predicate).
+// ---------------------------------------------------------------------------
+int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
+                  const double *A, int64_t lda, const double *B, int64_t ldb, double beta, double *C,
+                  int64_t ldc)
+{
+    if (n < 0 || k < 0) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t rows = trans ? k : n;
+    if (lda < (rows > 1 ? rows : 1) || ldb < (rows > 1 ? rows : 1) || ldc < (n > 1 ? n : 1))
+        return set_status(ULMB200_BAD_ARGUMENT);
+    if (n == 0 || ((alpha == 0.0 || k == 0) && beta == 1.0)) return set_status(ULMB200_OK);   // syur2k.tcc:47-49
+    const int tri = lower ? 2 : 1;
+    const int ta = trans ? 1 : 0, tb = trans ? 0 : 1;
+    int s = dgemm_device(st, tri, ta, tb, n, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+    if (s != ULMB200_OK || alpha == 0.0 || k == 0) return s;
+    return dgemm_device(st, tri, ta, tb, n, n, k, alpha, B, ldb, A, lda, 1.0, C, ldc);
+}
+
+// ---------------------------------------------------------------------------
+// symm:  C <- alpha*A*B + beta*C (left) or alpha*B*A + beta*C (right), A symmetric with one
+// triangle stored (ulmblas/level3/sylmm.tcc:18-100, syumm.tcc; pack/sy?pack.tcc mirrors the
+// stored triangle while packing).  Here the mirror image is written once into scratch and the
+// product is one device GEMM.
+// ---------------------------------------------------------------------------
+__global__ void symmetrize_kernel(const double *A, int64_t lda, int64_t n, int lower, double *S, int64_t lds)
+{
+    const int64_t total = n * n;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = e % n, j = e / n;
+        const bool stored = lower ? (i >= j) : (i <= j);
+        S[i + j * lds] = stored ? A[i + j * lda] : A[j + i * lda];
+    }
+}
+
+int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, double alpha, const double *A,
+                 int64_t lda, const double *B, int64_t ldb, double beta, double *C, int64_t ldc)
+{
+    if (m < 0 || n < 0 || (side != 0 && side != 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t na = side == 0 ? m : n;
+    if (lda < (na > 1 ? na : 1) || ldb < (m > 1 ? m : 1) || ldc < (m > 1 ? m : 1))
+        return set_status(ULMB200_BAD_ARGUMENT);
+    if (m == 0 || n == 0 || (alpha == 0.0 && beta == 1.0)) return set_status(ULMB200_OK);     // sylmm.tcc:47-49
+    if (int s0 = ensure_device()) return set_status(s0);
+    if (alpha == 0.0) return set_status(scale_matrix_device(st, C, ldc, m, n, beta, 0));
+    const int64_t lds = (na + 1) / 2 * 2;
+    double *S = static_cast<double *>(device_scratch(6, sizeof(double) * (size_t)(lds * na)));
+    if (!S) return set_status(ULMB200_CUDA_ERROR);
+    int64_t blocks = (na * na + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    symmetrize_kernel<<<(int)blocks, 256, 0, st>>>(A, lda, na, lower, S, lds);
+    count_launch();
+    if (int e = check_cuda(cudaGetLastError(), "symmetrize_kernel", __FILE__, __LINE__)) return e;
+    if (side == 0) return dgemm_device(st, 0, 0, 0, m, n, m, alpha, S, lds, B, ldb, beta, C, ldc);
+    return dgemm_device(st, 0, 0, 0, m, n, n, alpha, B, ldb, S, lds, beta, C, ldc);
+}
+
+// ---------------------------------------------------------------------------
+// trmm:  B <- alpha*op(A)*B (left) or alpha*B*op(A) (right), A triangular
+// (ulmblas/level3/trlmm.tcc:18-88, trumm.tcc; pack/tr?pack.tcc zero-fills the other
+// triangle while packing).  Same recursion as the solver above: the off-diagonal blocks
+// are plain GEMM updates on rows/columns of B not yet overwritten, the 128x128 diagonal
+// blocks are multiplied from zero-filled copies and go through the leaf tile.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kNB)
+trclean_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *out)
+{
+    const int blk = blockIdx.x, j = threadIdx.x;
+    const int64_t r0 = (int64_t)blk * kNB;
+    const int len = (int)((dim - r0) < kNB ? (dim - r0) : kNB);
+    const double *Ab = A + r0 + r0 * lda;
+    double *o = out + (int64_t)blk * kNB * kNB;
+    for (int i = 0; i < kNB; ++i) {
+        // element (j, i): threads run down a column, coalesced
+        double v = 0.0;
+        if (i < len && j < len) {
+            if (i == j) v = unit ? 1.0 : Ab[j + (int64_t)i * lda];
+            else if (lower ? (j > i) : (j < i)) v = Ab[j + (int64_t)i * lda];
+        }
+        o[j + i * kNB] = v;
+    }
+}
+
+static void mul_left(TrsmCtx &c, double alpha, int64_t r0, int64_t len)
+{
+    if (c.status != ULMB200_OK) return;
+    if (len <= kNB) {
+        const double *tb = c.inv + (r0 / kNB) * kNB * kNB;
+        gemm_chk(c, c.trans, 0, len, c.n, len, alpha, tb, kNB, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
+        launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
+        return;
+    }
+    const int64_t l1 = ((len / 2 + kNB - 1) / kNB) * kNB, l2 = len - l1;
+    if (c.eff_lower) {
+        mul_left(c, alpha, r0 + l1, l2);               // B2 <- a*T22*B2
+        gemm_chk(c, c.trans, 0, l2, c.n, l1, alpha, opA_block(c, r0 + l1, r0), c.lda, c.B + r0, c.ldb, 1.0,
+                 c.B + r0 + l1, c.ldb);                // B2 += a*T21*B1 (B1 still the input)
+        mul_left(c, alpha, r0, l1);
+    } else {
+        mul_left(c, alpha, r0, l1);                    // B1 <- a*T11*B1
+        gemm_chk(c, c.trans, 0, l1, c.n, l2, alpha, opA_block(c, r0, r0 + l1), c.lda, c.B + r0 + l1, c.ldb,
+                 1.0, c.B + r0, c.ldb);                // B1 += a*T12*B2 (B2 still the input)
+        mul_left(c, alpha, r0 + l1, l2);
+    }
+}
+
+static void mul_right(TrsmCtx &c, double alpha, int64_t c0, int64_t len)
+{
+    if (c.status != ULMB200_OK) return;
+    if (len <= kNB) {
+        const double *tb = c.inv + (c0 / kNB) * kNB * kNB;
+        gemm_chk(c, 0, c.trans, c.m, len, len, alpha, c.B + c0 * c.ldb, c.ldb, tb, kNB, 0.0, c.W, c.ldw);
+        launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
+        return;
+    }
+    const int64_t l1 = ((len / 2 + kNB - 1) / kNB) * kNB, l2 = len - l1;
+    if (c.eff_lower) {
+        mul_right(c, alpha, c0, l1);                   // B1 <- a*B1*T11
+        gemm_chk(c, 0, c.trans, c.m, l1, l2, alpha, c.B + (c0 + l1) * c.ldb, c.ldb, opA_block(c, c0 + l1, c0),
+                 c.lda, 1.0, c.B + c0 * c.ldb, c.ldb); // B1 += a*B2*T21 (B2 still the input)
+        mul_right(c, alpha, c0 + l1, l2);
+    } else {
+        mul_right(c, alpha, c0 + l1, l2);              // B2 <- a*B2*T22
+        gemm_chk(c, 0, c.trans, c.m, l2, l1, alpha, c.B + c0 * c.ldb, c.ldb, opA_block(c, c0, c0 + l1), c.lda,
+                 1.0, c.B + (c0 + l1) * c.ldb, c.ldb); // B2 += a*B1*T12 (B1 still the input)
+        mul_right(c, alpha, c0, l1);
+    }
+}
+
+int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                 double alpha, const double *A, int64_t lda, double *B, int64_t ldb)
+{
+    if (m < 0 || n < 0 || (side != 0 && side != 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t dim = (side == 0) ? m : n;
+    if (lda < (dim > 1 ? dim : 1) || ldb < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s = ensure_device()) return set_status(s);
+    if (alpha == 0.0) return set_status(scale_matrix_device(st, B, ldb, m, n, 0.0, 0));      // trlmm.tcc:46-49
+    const int64_t nblk = (dim + kNB - 1) / kNB;
+    double *blk = static_cast<double *>(device_scratch(3, (size_t)nblk * kNB * kNB * sizeof(double)));
+    const int64_t wel = (side == 0) ? (int64_t)kNB * n : m * (int64_t)kNB;
+    double *W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
+    if (!blk || !W) return set_status(ULMB200_CUDA_ERROR);
+    trclean_blocks_kernel<<<(int)nblk, kNB, 0, st>>>(A, lda, dim, lower, unit, blk);
+    count_launch();
+    if (int e = check_cuda(cudaGetLastError(), "trclean_blocks_kernel", __FILE__, __LINE__)) return e;
+    TrsmCtx c;
+    c.st = st; c.left = (side == 0); c.lower = lower; c.trans = transA;
+    c.eff_lower = (lower != 0) != (transA != 0);
+    c.m = m; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb;
+    c.inv = blk; c.W = W; c.ldw = c.left ? kNB : m;
+    c.err = nullptr;
+    c.status = ULMB200_OK;
+    if (c.left) mul_left(c, alpha, 0, m);
+    else        mul_right(c, alpha, 0, n);
+    return set_status(c.status);
+}
+
 }  // namespace ulmb200
 
 extern "C" int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int64_t k, double alpha,
@@ -240,6 +402,29 @@ extern "C" int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int6
 {
     return ulmb200::dsyrk_device(static_cast<cudaStream_t>(stream), lower, trans, n, k, alpha, dA, ldA,
                                  beta, dC, ldC);
+}
+
+extern "C" int ulmb200_dsyr2k(void *stream, int lower, int trans, int64_t n, int64_t k, double alpha,
+                              const double *dA, int64_t ldA, const double *dB, int64_t ldB, double beta,
+                              double *dC, int64_t ldC)
+{
+    return ulmb200::dsyr2k_device(static_cast<cudaStream_t>(stream), lower, trans, n, k, alpha, dA, ldA, dB,
+                                  ldB, beta, dC, ldC);
+}
+
+extern "C" int ulmb200_dsymm(void *stream, int side, int lower, int64_t m, int64_t n, double alpha,
+                             const double *dA, int64_t ldA, const double *dB, int64_t ldB, double beta,
+                             double *dC, int64_t ldC)
+{
+    return ulmb200::dsymm_device(static_cast<cudaStream_t>(stream), side, lower, m, n, alpha, dA, ldA, dB, ldB,
+                                 beta, dC, ldC);
+}
+
+extern "C" int ulmb200_dtrmm(void *stream, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                             double alpha, const double *dA, int64_t ldA, double *dB, int64_t ldB)
+{
+    return ulmb200::dtrmm_device(static_cast<cudaStream_t>(stream), side, lower, transA, unit, m, n, alpha, dA,
+                                 ldA, dB, ldB);
 }
 
 extern "C" int ulmb200_dtrsm(void *stream, int side, int lower, int transA, int unit, int64_t m,
