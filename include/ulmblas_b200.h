@@ -136,6 +136,25 @@ void ulmblas_dtrsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
 void ulmblas_dsyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k,
                    double alpha, const double *A, int ldA, double beta, double *C, int ldC);
 
+/* replace CBLAS(dsymm) / CBLAS(dtrmm) / CBLAS(dsyr2k) and their ULMBLAS() twins,
+ * interfaces/blas/C/symm.cc, trmm.cc, syr2k.cc                                */
+void cblas_dsymm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, int m, int n,
+                 double alpha, const double *A, int ldA, const double *B, int ldB,
+                 double beta, double *C, int ldC);
+void cblas_dtrmm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n,
+                 double alpha, const double *A, int ldA, double *B, int ldB);
+void cblas_dsyr2k(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans,
+                  int n, int k, double alpha, const double *A, int ldA,
+                  const double *B, int ldB, double beta, double *C, int ldC);
+void ulmblas_dsymm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, int m, int n, double alpha,
+                   const double *A, int ldA, const double *B, int ldB, double beta, double *C, int ldC);
+void ulmblas_dtrmm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE transA,
+                   enum CBLAS_DIAG diag, int m, int n, double alpha,
+                   const double *A, int ldA, double *B, int ldB);
+void ulmblas_dsyr2k(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k, double alpha,
+                    const double *A, int ldA, const double *B, int ldB, double beta, double *C, int ldC);
+
 /* replaces CBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-17 (weak)            */
 void cblas_xerbla(int info, const char *rout, const char *form, ...);
 /* interfaces/blas/C/cblas_globals.cc:3-4 (the Netlib C testers read these)   */
@@ -243,6 +262,11 @@ int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms);
  * launches to leave `sms` SMs free so that the collective's kernels are never starved;
  * 0 restores the default.  Process-wide.                                               */
 void ulmb200_set_sm_reserve(int sms);
+
+/* Failure-path self test: launches a kernel whose (short, bounded) wait can never be
+ * satisfied.  The kernel gives up, records it in the device error word and returns
+ * normally; the call reports ULMB200_KERNEL_FAULT and the context stays usable.       */
+int ulmb200_selftest_wait_timeout(void);
 
 /* Number of kernels this library has launched in this process so far.        */
 int64_t ulmb200_launch_count(void);

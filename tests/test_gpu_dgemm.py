@@ -177,3 +177,12 @@ def test_device_fill_matches_host_fill(ulm, torch_cuda):
     hf, _ = ulm.fmat(rows, cols, dtype=np.float32)
     ulm.host_fill(hf, 7, 0)
     assert np.array_equal(f.cpu().numpy().T[:rows, :], hf)
+
+
+def test_bounded_wait_reports_and_context_survives(ulm):
+    """Every mbarrier wait in the kernels is bounded; when one runs out the kernel records it and
+    returns.  Provoked here with a wait nothing can satisfy (no fault, no trap, no hang): the call
+    must report KERNEL_FAULT and the very next product must still be right."""
+    assert ulm.lib.ulmb200_selftest_wait_timeout() == ulm.KERNEL_FAULT
+    assert ulm.last_status() == ulm.KERNEL_FAULT
+    check_case(ulm, "N", "T", 150, 140, 70, 1.0, 0.0, 777)

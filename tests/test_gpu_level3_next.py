@@ -125,3 +125,34 @@ def test_dsyr2k_all_variants(ulm):
                 assert np.all(got[:n, :n][~mask] == ROGUE), "opposite triangle was written"
                 ratio = bound_ratio(np.where(mask, got[:n, :n], 0), np.where(mask, want, 0), gauge, 2 * k, EPS64)
                 assert ratio <= 1.0, (n, k, uplo, tr, alpha, beta, ratio)
+
+
+def test_cblas_row_major_symm_trmm_syr2k(ulm):
+    """Row-major CBLAS calls = the column-major routine on the transposed problem
+    (interfaces/blas/C/symm.cc, trmm.cc, syr2k.cc); checked against numpy on C-ordered arrays."""
+    rng = np.random.default_rng(5)
+    m, n, k = 40, 65, 23
+    A = rng.uniform(-1, 1, (m, m)); B = rng.uniform(-1, 1, (m, n)); C0 = rng.uniform(-1, 1, (m, n))
+    S = np.triu(A) + np.triu(A, 1).T
+    got = C0.copy()
+    ulm.lib.cblas_dsymm(ulm.CblasRowMajor, ulm.CblasLeft, ulm.CblasUpper, m, n, 0.5, A.ctypes.data, m,
+                        B.ctypes.data, n, 2.0, got.ctypes.data, n)
+    assert ulm.last_status() == ulm.OK
+    want = 0.5 * S @ B + 2.0 * C0
+    assert bound_ratio(got, want, 0.5 * np.abs(S) @ np.abs(B) + 2.0 * np.abs(C0), m, EPS64) <= 1.0
+    T = np.tril(A)
+    got = B.copy()
+    ulm.lib.cblas_dtrmm(ulm.CblasRowMajor, ulm.CblasLeft, ulm.CblasLower, ulm.CblasTrans, ulm.CblasNonUnit, m, n,
+                        1.5, A.ctypes.data, m, got.ctypes.data, n)
+    assert ulm.last_status() == ulm.OK
+    assert bound_ratio(got, 1.5 * T.T @ B, 1.5 * np.abs(T.T) @ np.abs(B), m, EPS64) <= 1.0
+    A2 = rng.uniform(-1, 1, (n, k)); B2 = rng.uniform(-1, 1, (n, k)); C2 = rng.uniform(-1, 1, (n, n))
+    got = C2.copy()
+    ulm.lib.cblas_dsyr2k(ulm.CblasRowMajor, ulm.CblasLower, ulm.CblasNoTrans, n, k, 1.0, A2.ctypes.data, k,
+                         B2.ctypes.data, k, 0.5, got.ctypes.data, n)
+    assert ulm.last_status() == ulm.OK
+    want = A2 @ B2.T + B2 @ A2.T + 0.5 * C2
+    low = np.tril(np.ones((n, n), bool))
+    gauge = np.abs(A2) @ np.abs(B2).T + np.abs(B2) @ np.abs(A2).T + 0.5 * np.abs(C2)
+    assert bound_ratio(np.where(low, got, 0), np.where(low, want, 0), gauge, 2 * k, EPS64) <= 1.0
+    assert np.array_equal(got[~low], C2[~low])

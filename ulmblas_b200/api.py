@@ -48,6 +48,7 @@ lib.ulmb200_last_status.restype = _int
 lib.ulmb200_status_string.restype = C.c_char_p
 lib.ulmb200_status_string.argtypes = [_int]
 lib.ulmb200_launch_count.restype = _i64
+lib.ulmb200_selftest_wait_timeout.restype = _int
 lib.ulmb200_dgemm.argtypes = [_vp, _int, _int, _i64, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_sgemm.argtypes = [_vp, _int, _int, _int, _i64, _i64, _i64, _flt, _vp, _i64, _vp, _i64, _flt, _vp, _i64]
 lib.ulmb200_dtrsm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
@@ -74,6 +75,11 @@ for _name in ("dsymm_", "dtrmm_", "dsyr2k_", "dgemm_", "sgemm_", "dtrsm_", "dsyr
 lib.cblas_dgemm.argtypes = [_int, _int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int, _dbl, _vp, _int]
 lib.cblas_sgemm.argtypes = [_int, _int, _int, _int, _int, _int, _flt, _vp, _int, _vp, _int, _flt, _vp, _int]
 lib.cblas_dtrsm.argtypes = [_int, _int, _int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int]
+lib.cblas_dsymm.argtypes = [_int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int, _dbl, _vp, _int]
+lib.cblas_dtrmm.argtypes = [_int, _int, _int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int]
+lib.cblas_dsyr2k.argtypes = [_int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int, _dbl, _vp, _int]
+for _name in ("cblas_dsymm", "cblas_dtrmm", "cblas_dsyr2k"):
+    getattr(lib, _name).restype = None
 lib.cblas_dsyrk.argtypes = [_int, _int, _int, _int, _int, _dbl, _vp, _int, _dbl, _vp, _int]
 
 CblasRowMajor, CblasColMajor = 101, 102

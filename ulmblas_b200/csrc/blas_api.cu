@@ -717,4 +717,119 @@ void cblas_dsyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSP
     }
 }
 
+// ---- CBLAS twins of the three further gemm clients -----------------------------------------
+
+void ulmblas_dsymm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, int m, int n, double alpha, const double *A,
+                   int ldA, const double *B, int ldB, double beta, double *C, int ldC)
+{
+    dsymm_any(side == CblasLeft ? 0 : 1, upLo == CblasLower, m, n, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
+// replaces CBLAS(dsymm), interfaces/blas/C/symm.cc
+void cblas_dsymm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, int m, int n,
+                 double alpha, const double *A, int ldA, const double *B, int ldB, double beta, double *C,
+                 int ldC)
+{
+    const int rowsA = (side == CblasLeft) ? m : n;
+    int info = 0;
+    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
+    else if (side != CblasLeft && side != CblasRight) info = 2;
+    else if (upLo != CblasLower && upLo != CblasUpper) info = 3;
+    else if (order == CblasColMajor) {
+        if (m < 0) info = 4;
+        else if (n < 0) info = 5;
+        else if (ldA < std::max(1, rowsA)) info = 8;
+        else if (ldB < std::max(1, m)) info = 10;
+        else if (ldC < std::max(1, m)) info = 13;
+    } else {
+        if (n < 0) info = 4;
+        else if (m < 0) info = 5;
+        else if (ldA < std::max(1, rowsA)) info = 8;
+        else if (ldB < std::max(1, n)) info = 10;
+        else if (ldC < std::max(1, n)) info = 13;
+    }
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_dsymm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) ulmblas_dsymm(side, upLo, m, n, alpha, A, ldA, B, ldB, beta, C, ldC);
+    else ulmblas_dsymm(side == CblasLeft ? CblasRight : CblasLeft, upLo == CblasUpper ? CblasLower : CblasUpper,
+                       n, m, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
+void ulmblas_dtrmm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE transA,
+                   enum CBLAS_DIAG diag, int m, int n, double alpha, const double *A, int ldA, double *B,
+                   int ldB)
+{
+    dtrmm_any(side == CblasLeft ? 0 : 1, upLo == CblasLower, !c_notrans(transA), diag == CblasUnit, m, n, alpha,
+              A, ldA, B, ldB);
+}
+
+// replaces CBLAS(dtrmm), interfaces/blas/C/trmm.cc
+void cblas_dtrmm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n, double alpha,
+                 const double *A, int ldA, double *B, int ldB)
+{
+    const int rowsA = (side == CblasLeft) ? m : n;
+    int info = 0;
+    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
+    else if (side != CblasLeft && side != CblasRight) info = 2;
+    else if (upLo != CblasLower && upLo != CblasUpper) info = 3;
+    else if (!c_valid_trans(transA)) info = 4;
+    else if (diag != CblasUnit && diag != CblasNonUnit) info = 5;
+    else if (order == CblasColMajor) {
+        if (m < 0) info = 6;
+        else if (n < 0) info = 7;
+        else if (ldA < std::max(1, rowsA)) info = 10;
+        else if (ldB < std::max(1, m)) info = 12;
+    } else {
+        if (n < 0) info = 6;
+        else if (m < 0) info = 7;
+        else if (ldA < std::max(1, rowsA)) info = 10;
+        else if (ldB < std::max(1, n)) info = 12;
+    }
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_dtrmm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) ulmblas_dtrmm(side, upLo, transA, diag, m, n, alpha, A, ldA, B, ldB);
+    else ulmblas_dtrmm(side == CblasLeft ? CblasRight : CblasLeft, upLo == CblasUpper ? CblasLower : CblasUpper,
+                       transA, diag, n, m, alpha, A, ldA, B, ldB);
+}
+
+void ulmblas_dsyr2k(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k, double alpha,
+                    const double *A, int ldA, const double *B, int ldB, double beta, double *C, int ldC)
+{
+    dsyr2k_any(upLo == CblasLower, !c_notrans(trans), n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
+// replaces CBLAS(dsyr2k), interfaces/blas/C/syr2k.cc
+void cblas_dsyr2k(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k,
+                  double alpha, const double *A, int ldA, const double *B, int ldB, double beta, double *C,
+                  int ldC)
+{
+    int rows;
+    if (order == CblasColMajor) rows = c_notrans(trans) ? n : k;
+    else                        rows = c_notrans(trans) ? k : n;
+    int info = 0;
+    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
+    else if (upLo != CblasLower && upLo != CblasUpper) info = 2;
+    else if (!c_valid_trans(trans)) info = 3;
+    else if (n < 0) info = 4;
+    else if (k < 0) info = 5;
+    else if (ldA < std::max(1, rows)) info = 8;
+    else if (ldB < std::max(1, rows)) info = 10;
+    else if (ldC < std::max(1, n)) info = 13;
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_dsyr2k", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) ulmblas_dsyr2k(upLo, trans, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+    else ulmblas_dsyr2k(upLo == CblasUpper ? CblasLower : CblasUpper, c_notrans(trans) ? CblasTrans : CblasNoTrans,
+                        n, k, alpha, B, ldB, A, ldA, beta, C, ldC);
+}
+
 }  // extern "C"

@@ -109,9 +109,38 @@ static int run_probe(int iters, int blocks, double *ms)
     return ULMB200_OK;
 }
 
+// A wait that nothing will ever satisfy, with a short poll limit: exercises the path every
+// bounded wait in the library takes when it gives up (error word written, normal return).
+__global__ void wait_probe_kernel(int *err, uint32_t limit)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+        bool ok = false;
+        for (uint32_t i = 0; i < limit && !ok; ++i) {
+            ok = mbar_try_wait(&bar, 0);
+            if (!ok) __nanosleep(64);
+        }
+        if (!ok) atomicExch(err, 301);
+    }
+}
+
 }  // namespace ulmb200
 
 using namespace ulmb200;
+
+extern "C" int ulmb200_selftest_wait_timeout(void)
+{
+    if (int s = ensure_device()) return set_status(s);
+    int *err = device_error_word();
+    if (!err) return set_status(ULMB200_CUDA_ERROR);
+    wait_probe_kernel<<<1, 32>>>(err, 20000);      // about a millisecond of polling
+    count_launch();
+    if (int e = check_cuda(cudaGetLastError(), "wait_probe_kernel", __FILE__, __LINE__)) return e;
+    if (int e = check_cuda(cudaDeviceSynchronize(), "synchronize", __FILE__, __LINE__)) return e;
+    return set_status(poll_device_error());        // ULMB200_KERNEL_FAULT is the expected answer
+}
 
 extern "C" int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms_out)
 {
