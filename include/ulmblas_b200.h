@@ -155,6 +155,12 @@ void ulmblas_dtrmm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, enum CBLAS_TRANSP
 void ulmblas_dsyr2k(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k, double alpha,
                     const double *A, int ldA, const double *B, int ldB, double beta, double *C, int ldC);
 
+/* replaces ULMLAPACK(dgetrf), interfaces/lapack/C/getrf.cc:6-19 (blocked LU with partial
+ * pivoting, ulmblas/lapack/getrf.tcc:30-73): the L and U factors overwrite A, piv[i] = 0-based row exchanged
+ * with row i, returns the 1-based index of the first zero pivot or 0.  CblasColMajor only
+ * (CblasRowMajor returns -1; the reference's row-major mode is consistent only for m == n).   */
+int ulmblas_dgetrf(enum CBLAS_ORDER order, int m, int n, double *A, int ldA, int *piv);
+
 /* replaces CBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-17 (weak)            */
 void cblas_xerbla(int info, const char *rout, const char *form, ...);
 /* interfaces/blas/C/cblas_globals.cc:3-4 (the Netlib C testers read these)   */
@@ -226,6 +232,10 @@ int ulmb200_dtrmm(void *stream, int side, int lower, int transA, int unit,
 int ulmb200_dsyr2k(void *stream, int lower, int trans, int64_t n, int64_t k, double alpha,
                    const double *dA, int64_t ldA, const double *dB, int64_t ldB,
                    double beta, double *dC, int64_t ldC);
+
+/* Blocked LU on device operands; d_piv (min(m,n) ints) and d_info (1 int) are device
+ * pointers written asynchronously.  Replaces ulmBLAS::getrf / getf2 / laswp.                */
+int ulmb200_dgetrf(void *stream, int64_t m, int64_t n, double *dA, int64_t ldA, int *d_piv, int *d_info);
 
 /* Deterministic test/bench matrices: element (i,j) of matrix `mat` under
  * `seed` is a pure function of (seed, mat, i, j), identical on host and device,

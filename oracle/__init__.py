@@ -96,7 +96,7 @@ class Port:
 
 
 def ref_path(variant=""):
-    name = {"": "libulmref.so", "tiny": "libulmref_tiny.so", "plain": "libulmref_plain.so", "cblas": "libulmref_cblas.so"}[variant]
+    name = {"": "libulmref.so", "tiny": "libulmref_tiny.so", "plain": "libulmref_plain.so", "lapack": "libulmref_lapack.so", "cblas": "libulmref_cblas.so"}[variant]
     return os.path.join(_HERE, "_ref", name)
 
 
@@ -188,6 +188,17 @@ def _ref_getattr(self, name):
 
 
 Ref.__getattr__ = _ref_getattr
+
+
+def ref_dgetrf(A, lda=None):
+    """ulmblas_dgetrf of the compiled reference (interfaces/lapack/C/getrf.cc:6-19), column-major,
+    in place on the numpy matrix A; returns (piv, info) with the reference's 0-based pivots."""
+    L = C.CDLL(ref_path("lapack"))
+    m, n = A.shape
+    piv = (C.c_int * max(1, min(m, n)))()
+    L.ulmblas_dgetrf.restype = _int
+    info = L.ulmblas_dgetrf(C.c_int(102), C.c_int(m), C.c_int(n), _p(A), C.c_int(lda or _ld(A)), piv)
+    return np.array(piv[:min(m, n)], dtype=np.int64), int(info)
 
 
 def fmat(rows, cols, ld=None, dtype=np.float64, fill=None):

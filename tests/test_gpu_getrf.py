@@ -1,0 +1,70 @@
+"""Blocked LU (ulmblas_dgetrf) on the GPU against the reference's own getrf
+(ulmblas/lapack/getrf.tcc), the in-tree caller of trlsm + gemm."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import EPS64, det_uniform, padded
+
+pytestmark = pytest.mark.gpu
+
+
+def apply_piv(A, piv):
+    P = A.copy()
+    for i, p in enumerate(piv):
+        if p != i:
+            P[[i, p]] = P[[p, i]]
+    return P
+
+
+def check_lu(ulm, m, n, seed, extra=3):
+    A0 = det_uniform(seed, m, n)
+    Av, Ab = padded(A0, m + extra)
+    got = Ab.copy(order="F")
+    piv, info = ulm.dgetrf(got[:m, :n], lda=m + extra)
+    assert ulm.last_status() == ulm.OK and info == 0
+    assert np.array_equal(got[m:, :], Ab[m:, :]), "padding rows written"
+    mn = min(m, n)
+    LU = got[:m, :n]
+    L = np.tril(LU, -1)[:, :mn] + np.eye(m, mn)
+    U = np.triu(LU)[:mn, :]
+    assert np.abs(np.tril(LU, -1)).max() <= 1.0 + 1e-12, "partial pivoting keeps |l_ij| <= 1"
+    # backward error of the factorisation: |P A - L U| <= c * mn * eps * |L||U|
+    resid = np.abs(apply_piv(A0, piv) - L @ U)
+    bound = 4.0 * mn * EPS64 * (np.abs(L) @ np.abs(U))
+    assert (resid <= bound + 1e-300).all(), (m, n, float((resid / np.maximum(bound, 1e-300)).max()))
+    if oracle.have_ref("lapack"):
+        want = Ab.copy(order="F")
+        rpiv, rinfo = oracle.ref_dgetrf(want[:m, :n], lda=m + extra)
+        assert rinfo == 0
+        # same pivot sequence (first-largest rule) and factors equal up to rounding
+        assert np.array_equal(piv, rpiv), (m, n)
+        scale = np.abs(L) @ np.abs(U)
+        assert (np.abs(LU - want[:m, :n]) <= 8.0 * mn * EPS64 * np.maximum(scale, 1.0)).all(), (m, n)
+
+
+def test_dgetrf_shapes(ulm):
+    for i, (m, n) in enumerate([(1, 1), (7, 5), (5, 7), (31, 31), (130, 130), (300, 200), (200, 300),
+                                (513, 513), (1100, 700)]):
+        check_lu(ulm, m, n, 70000 + i)
+
+
+def test_dgetrf_2048_and_zero_pivot(ulm):
+    check_lu(ulm, 2048, 2048, 71000, extra=0)
+    # an exactly singular matrix: column 2 is zero -> info = 3 (1-based), as the reference reports
+    A = det_uniform(71001, 6, 6)
+    A[:, 2] = 0.0
+    W = A.copy(order="F")
+    piv, info = ulm.dgetrf(W)
+    assert info == 3
+    if oracle.have_ref("lapack"):
+        W2 = A.copy(order="F")
+        rpiv, rinfo = oracle.ref_dgetrf(W2)
+        assert rinfo == info and np.array_equal(piv, rpiv)
+
+
+def test_dgetrf_row_major_is_refused(ulm):
+    A = np.zeros((4, 4), order="F")
+    piv = np.zeros(4, dtype=np.int32)
+    assert ulm.lib.ulmblas_dgetrf(ulm.CblasRowMajor, 4, 4, A.ctypes.data, 4, piv.ctypes.data) == -1
+    assert ulm.last_status() == ulm.BAD_ARGUMENT

@@ -66,6 +66,9 @@ lib.ulmb200_set_sm_reserve.argtypes = [_int]
 lib.ulmb200_set_sm_reserve.restype = None
 lib.ulmb200_set_pin_host.argtypes = [_int]
 lib.ulmb200_set_pin_host.restype = None
+lib.ulmb200_dgetrf.argtypes = [_vp, _i64, _i64, _vp, _i64, _vp, _vp]
+lib.ulmblas_dgetrf.argtypes = [_int, _int, _int, _vp, _int, _vp]
+lib.ulmblas_dgetrf.restype = _int
 lib.ulmb200_dsymm.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_dtrmm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
 lib.ulmb200_dsyr2k.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
@@ -182,6 +185,15 @@ def dsyr2k(uplo, trans, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=Non
     lib.dsyr2k_(_cp(_c(uplo)), _cp(_c(trans)), _ri(n), _ri(k), C.byref(_dbl(alpha)), _p(A), _ri(lda or _ld(A)),
                 _p(B), _ri(ldb or _ld(B)), C.byref(_dbl(beta)), _p(Cm), _ri(ldc or _ld(Cm)))
     return last_status()
+
+
+def dgetrf(A, lda=None):
+    """LU with partial pivoting in place on a numpy column-major matrix through ``ulmblas_dgetrf``;
+    returns (piv, info) with the reference's 0-based pivots."""
+    m, n = A.shape
+    piv = np.zeros(max(1, min(m, n)), dtype=np.int32)
+    info = lib.ulmblas_dgetrf(CblasColMajor, m, n, _p(A), lda or _ld(A), piv.ctypes.data_as(_vp))
+    return piv[:min(m, n)].astype(np.int64), info
 
 
 # --------------------------------------------------------------------------- device-pointer calls

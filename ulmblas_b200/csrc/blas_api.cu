@@ -29,6 +29,7 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
                  double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
 int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                  double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
+int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda, int *d_piv, int *d_info);
 int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, double alpha, const double *A,
                  int64_t lda, const double *B, int64_t ldb, double beta, double *C, int64_t ldc);
 int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
@@ -830,6 +831,40 @@ void cblas_dsyr2k(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANS
     if (order == CblasColMajor) ulmblas_dsyr2k(upLo, trans, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
     else ulmblas_dsyr2k(upLo == CblasUpper ? CblasLower : CblasUpper, c_notrans(trans) ? CblasTrans : CblasNoTrans,
                         n, k, alpha, B, ldB, A, ldA, beta, C, ldC);
+}
+
+// replaces ULMLAPACK(dgetrf), interfaces/lapack/C/getrf.cc:6-19 -> ulmBLAS::getrf
+// (ulmblas/lapack/getrf.tcc:30-73).  Column-major only: for CblasRowMajor the reference runs
+// getrf(n, m, A, ldA, 1), which addresses the array consistently only when m == n; that mode is
+// refused here (return value -1) rather than imitated.  piv holds 0-based row indices, the
+// return value is the 1-based index of the first zero pivot or 0.
+int ulmblas_dgetrf(enum CBLAS_ORDER order, int m, int n, double *A, int ldA, int *piv)
+{
+    if (order != CblasColMajor || m < 0 || n < 0 || ldA < std::max(1, m)) {
+        int info = order != CblasColMajor ? 1 : (m < 0 ? 2 : (n < 0 ? 3 : 5));
+        cblas_xerbla(info, "ulmblas_dgetrf", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return -info;
+    }
+    if (m == 0 || n == 0) { set_status(ULMB200_OK); return 0; }
+    if (ensure_device() != ULMB200_OK) { set_status(ULMB200_NO_DEVICE); return -100; }
+    Streams *s = streams();
+    if (!s) { set_status(ULMB200_CUDA_ERROR); return -100; }
+    const int mn = std::min(m, n);
+    int *dints = static_cast<int *>(device_scratch(9, sizeof(int) * (size_t)(mn + 1)));
+    if (!dints) { set_status(ULMB200_CUDA_ERROR); return -100; }
+    Staged a;
+    int st = stage_in(a, A, ldA, m, n, 2, true, s->run);
+    if (st == ULMB200_OK) st = dgetrf_device(s->run, m, n, a.dev, a.ldd, dints, dints + mn);
+    if (st == ULMB200_OK) st = stage_out(a, s->run);
+    int info = 0;
+    if (st == ULMB200_OK)
+        st = check_cuda(cudaMemcpyAsync(piv, dints, sizeof(int) * mn, cudaMemcpyDeviceToHost, s->run), "piv", __FILE__, __LINE__);
+    if (st == ULMB200_OK)
+        st = check_cuda(cudaMemcpyAsync(&info, dints + mn, sizeof(int), cudaMemcpyDeviceToHost, s->run), "info", __FILE__, __LINE__);
+    const int fin = finish(s);
+    set_status(st != ULMB200_OK ? st : fin);
+    return (st == ULMB200_OK && fin == ULMB200_OK) ? info : -100;
 }
 
 }  // extern "C"
