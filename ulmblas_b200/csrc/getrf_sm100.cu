@@ -127,6 +127,124 @@ __global__ void __launch_bounds__(kLuThreads) getf2_panel_kernel(PanelArgs a)
     }
 }
 
+// The same panel factorisation with each CTA's rows held in shared memory (up to kLuSlabRows
+// rows x 128 columns), used whenever the panel is short enough for that.  One grid-wide barrier
+// per column: before it every CTA publishes its best candidate together with that row's
+// contents, and the owner of row c publishes row c; after it every CTA knows the pivot row's
+// contents without another exchange, the owners of the two rows overwrite their copies (the row
+// swap), and all update their rows at shared-memory speed.  Publication buffers alternate with
+// the column parity, so a CTA one column ahead never overwrites what a slower CTA still reads.
+constexpr int kLuSlabRows = 192;
+
+struct PanelSmemArgs {
+    PanelArgs p;
+    double *cand_rows;     // [2][G][kLuNB]
+    double *rowc;          // [2][kLuNB]
+    double *cval;          // [2][G]
+    int *cidx;             // [2][G]
+};
+
+__global__ void __launch_bounds__(kLuThreads) getf2_panel_smem_kernel(PanelSmemArgs q)
+{
+    cg::grid_group grid = cg::this_grid();
+    const PanelArgs &a = q.p;
+    extern __shared__ double lu_smem[];
+    __shared__ double sv[kLuThreads];
+    __shared__ int64_t si[kLuThreads];
+    __shared__ double s_row[kLuNB];
+    __shared__ double s_l[kLuSlabRows];
+
+    const int G = gridDim.x, b = blockIdx.x, t = threadIdx.x;
+    const int64_t slab = (a.m + G - 1) / G;
+    const int64_t lo = (int64_t)b * slab, hi = min(a.m, lo + slab);
+    const int nr = (int)max((int64_t)0, hi - lo);          // my rows (<= kLuSlabRows)
+    const int ldS = kLuSlabRows;
+    double *S = lu_smem;                                   // S[cc*ldS + r]
+
+    for (int e = t; e < nr * a.jb; e += kLuThreads) {
+        const int r = e % nr, cc = e / nr;
+        S[cc * ldS + r] = a.A[lo + r + (int64_t)cc * a.lda];
+    }
+    __syncthreads();
+
+    const int ncol = (int)min((int64_t)a.jb, a.m);
+    for (int c = 0; c < ncol; ++c) {
+        const int par = c & 1;
+        double *crow = q.cand_rows + ((size_t)par * G + b) * kLuNB;
+        // (1) my candidate among rows >= c, published with its row
+        double bv = -1.0;
+        int64_t bi = a.m;
+        for (int r = t; r < nr; r += kLuThreads) {
+            const int64_t gr = lo + r;
+            if (gr >= c) {
+                const double v = fabs(S[c * ldS + r]);
+                if (lu_better(v, gr, bv, bi)) { bv = v; bi = gr; }
+            }
+        }
+        lu_block_argmax(bv, bi, sv, si);
+        if (t == 0) { q.cval[par * G + b] = bv; q.cidx[par * G + b] = (int)bi; }
+        if (bi < a.m)
+            for (int cc = t; cc < a.jb; cc += kLuThreads) crow[cc] = S[cc * ldS + (int)(bi - lo)];
+        if (c >= lo && c < hi)
+            for (int cc = t; cc < a.jb; cc += kLuThreads) q.rowc[par * kLuNB + cc] = S[cc * ldS + (int)(c - lo)];
+        __threadfence();
+        grid.sync();
+
+        // (2) the pivot and its row
+        double pv = -1.0;
+        int64_t p = a.m;
+        for (int g = t; g < G; g += kLuThreads) {
+            const double v = q.cval[par * G + g];
+            const int64_t i = q.cidx[par * G + g];
+            if (lu_better(v, i, pv, p)) { pv = v; p = i; }
+        }
+        lu_block_argmax(pv, p, sv, si);
+        const bool singular = !(pv > 0.0);
+        if (singular) p = c;
+        if (b == 0 && t == 0) {
+            a.piv[a.row_off + c] = (int)(p + a.row_off);
+            if (singular) atomicCAS(a.info, 0, (int)(a.row_off + c + 1));
+        }
+        if (singular) continue;
+        const int w = (int)min((int64_t)G - 1, p / slab);                // CTA that owns row p
+        const double *prow = q.cand_rows + ((size_t)par * G + w) * kLuNB;
+        for (int cc = t; cc < a.jb; cc += kLuThreads) s_row[cc] = prow[cc];
+        if (p != c) {
+            // the exchange: row p takes the old row c, row c takes the pivot row
+            if (p >= lo && p < hi)
+                for (int cc = t; cc < a.jb; cc += kLuThreads) S[cc * ldS + (int)(p - lo)] = q.rowc[par * kLuNB + cc];
+            if (c >= lo && c < hi)
+                for (int cc = t; cc < a.jb; cc += kLuThreads) S[cc * ldS + (int)(c - lo)] = prow[cc];
+        }
+        __syncthreads();
+
+        // (3) multipliers, then the rank-1 update of my rows below c
+        const double piv = s_row[c];
+        const bool recip = fabs(piv) >= DBL_MIN;
+        const double rp = 1.0 / piv;
+        const int r_first = (int)max((int64_t)0, (int64_t)c + 1 - lo);   // first local row with global index > c
+        for (int r = r_first + t; r < nr; r += kLuThreads) {
+            const double x = S[c * ldS + r];
+            const double l = recip ? x * rp : x / piv;
+            S[c * ldS + r] = l;
+            s_l[r] = l;
+        }
+        __syncthreads();
+        const int na = nr - r_first, nc = a.jb - c - 1;
+        if (na > 0)
+            for (int e = t; e < na * nc; e += kLuThreads) {
+                const int r = r_first + e % na, cc = c + 1 + e / na;
+                S[cc * ldS + r] -= s_l[r] * s_row[cc];
+            }
+        __syncthreads();
+    }
+
+    for (int e = t; e < nr * a.jb; e += kLuThreads) {
+        const int r = e % nr, cc = e / nr;
+        a.A[lo + r + (int64_t)cc * a.lda] = S[cc * ldS + r];
+    }
+}
+
 // Rows k1..k2-1 of `ncols` columns are exchanged with rows piv[k1..k2-1], in order (laswp.tcc).
 __global__ void laswp_kernel(double *A, int64_t lda, int64_t ncols, int64_t k1, int64_t k2, const int *piv)
 {
@@ -165,10 +283,18 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
         ULMB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, getf2_panel_kernel, kLuThreads, 0));
         max_ctas[dev] = (per_sm > 0 ? 1 : 0) * sm_count();      // one CTA per SM is plenty
         if (max_ctas[dev] <= 0) return set_status(ULMB200_CUDA_ERROR);
+        ULMB_CUDA(cudaFuncSetAttribute(getf2_panel_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(sizeof(double) * kLuSlabRows * kLuNB)));
     }
-    double *cand_val = static_cast<double *>(device_scratch(8, 16 * (size_t)max_ctas[dev]));
+    // scratch: candidates (value, index) x 2 parities, candidate rows x 2 parities, row c x 2 parities
+    const size_t nG = (size_t)max_ctas[dev];
+    const size_t doubles = 2 * nG + 2 * nG * kLuNB + 2 * kLuNB + nG /* ints, 2 per double */;
+    double *cand_val = static_cast<double *>(device_scratch(8, sizeof(double) * doubles));
     if (!cand_val) return set_status(ULMB200_CUDA_ERROR);
-    int *cand_idx = reinterpret_cast<int *>(cand_val + max_ctas[dev]);
+    double *cand_rows = cand_val + 2 * nG;
+    double *rowc = cand_rows + 2 * nG * kLuNB;
+    int *cand_idx = reinterpret_cast<int *>(rowc + 2 * kLuNB);
+    constexpr size_t kSlabSmem = sizeof(double) * (size_t)kLuSlabRows * kLuNB;
 
     const int64_t mn = m < n ? m : n;
     for (int64_t j = 0; j < mn; j += kLuNB) {
@@ -176,12 +302,25 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
         PanelArgs a;
         a.A = A + j + j * lda; a.lda = lda; a.m = m - j; a.jb = jb; a.row_off = j;
         a.piv = d_piv; a.info = d_info; a.cand_val = cand_val; a.cand_idx = cand_idx;
-        int64_t G = (a.m + 4 * kLuThreads - 1) / (4 * kLuThreads);        // >= 1024 rows per CTA
-        if (G > max_ctas[dev]) G = max_ctas[dev];
-        if (G < 1) G = 1;
-        void *args[] = {&a};
-        ULMB_CUDA(cudaLaunchCooperativeKernel((const void *)getf2_panel_kernel, dim3((unsigned)G), dim3(kLuThreads),
-                                              args, 0, st));
+        // short panels live in shared memory (64..192 rows per CTA); taller ones work in global memory
+        int64_t Gs = (a.m + 63) / 64;
+        if (Gs > max_ctas[dev]) Gs = max_ctas[dev];
+        if (Gs < 1) Gs = 1;
+        if ((a.m + Gs - 1) / Gs <= kLuSlabRows) {
+            PanelSmemArgs q;
+            q.p = a;
+            q.cand_rows = cand_rows; q.rowc = rowc; q.cval = cand_val; q.cidx = cand_idx;
+            void *args[] = {&q};
+            ULMB_CUDA(cudaLaunchCooperativeKernel((const void *)getf2_panel_smem_kernel, dim3((unsigned)Gs),
+                                                  dim3(kLuThreads), args, kSlabSmem, st));
+        } else {
+            int64_t G = (a.m + 4 * kLuThreads - 1) / (4 * kLuThreads);        // >= 1024 rows per CTA
+            if (G > max_ctas[dev]) G = max_ctas[dev];
+            if (G < 1) G = 1;
+            void *args[] = {&a};
+            ULMB_CUDA(cudaLaunchCooperativeKernel((const void *)getf2_panel_kernel, dim3((unsigned)G),
+                                                  dim3(kLuThreads), args, 0, st));
+        }
         count_launch();
         // the same exchanges on the columns left and right of the panel (getrf.tcc:50-57)
         launch_laswp(st, A, lda, j, j, j + jb, d_piv);

@@ -140,31 +140,42 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
             sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, (int64_t)(kc + 1) * BK, p.k);
             sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, (int64_t)(kc + 1) * BK, p.k);
         }
-        const uint32_t a_s = smem_u32(As + cur * A_TILE + am);
-        const uint32_t b_s = smem_u32(Bs + cur * B_TILE + bn);
+        const float *a_t = As + cur * A_TILE + am;
+        const float *b_t = Bs + cur * B_TILE + bn;
+        // fragments of step kk+1 are fetched while step kk multiplies
+        uint64_t a2[2][8];
+        float4 bf[2][2];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(a_t + 32 * r);
+            a2[0][2 * r] = v.x; a2[0][2 * r + 1] = v.y;
+        }
+        bf[0][0] = *reinterpret_cast<const float4 *>(b_t);
+        bf[0][1] = *reinterpret_cast<const float4 *>(b_t + 16);
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
-            uint64_t a2[8], b2[8];
+            const int cb = kk & 1, nb = cb ^ 1;
+            if (kk + 1 < BK) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                asm volatile("ld.shared.v2.b64 {%0,%1}, [%2];"
-                             : "=l"(a2[2 * r]), "=l"(a2[2 * r + 1])
-                             : "r"(a_s + (kk * LDA_ + 32 * r) * 4));
+                for (int r = 0; r < 4; ++r) {
+                    const ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(a_t + (kk + 1) * LDA_ + 32 * r);
+                    a2[nb][2 * r] = v.x; a2[nb][2 * r + 1] = v.y;
+                }
+                bf[nb][0] = *reinterpret_cast<const float4 *>(b_t + (kk + 1) * LDB_);
+                bf[nb][1] = *reinterpret_cast<const float4 *>(b_t + (kk + 1) * LDB_ + 16);
+            }
+            uint64_t b2[8];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                float4 b;
-                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                             : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
-                             : "r"(b_s + (kk * LDB_ + 16 * c) * 4));
-                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 0]) : "f"(b.x));
-                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 1]) : "f"(b.y));
-                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 2]) : "f"(b.z));
-                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 3]) : "f"(b.w));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 0]) : "f"(bf[cb][c].x));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 1]) : "f"(bf[cb][c].y));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 2]) : "f"(bf[cb][c].z));
+                asm("mov.b64 %0, {%1,%1};" : "=l"(b2[4 * c + 3]) : "f"(bf[cb][c].w));
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ffma2(acc[i][j], a2[i], b2[j]);
+                for (int i = 0; i < 8; ++i) ffma2(acc[i][j], a2[cb][i], b2[j]);
         }
         if (kc + 1 < kt) {
             sg_store<BM, LDA_, TA>(As + (cur ^ 1) * A_TILE, ra);
