@@ -27,7 +27,7 @@ _vp = C.c_void_p
 
 def build(ref=True):
     """Compile the restatement and, if the reference tree is present, the reference."""
-    subprocess.run(["make", "-C", _HERE, "all" if ref else "port"], check=True,
+    subprocess.run(["make", "-j8", "-C", _HERE, "all" if ref else "port"], check=True,
                    stdout=subprocess.DEVNULL)
 
 

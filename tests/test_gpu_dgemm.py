@@ -186,3 +186,24 @@ def test_bounded_wait_reports_and_context_survives(ulm):
     assert ulm.lib.ulmb200_selftest_wait_timeout() == ulm.KERNEL_FAULT
     assert ulm.last_status() == ulm.KERNEL_FAULT
     check_case(ulm, "N", "T", 150, 140, 70, 1.0, 0.0, 777)
+
+
+def test_calls_from_several_host_threads(ulm):
+    """The reference is re-entrant (its scratch pool is mutex-guarded); so are the BLAS entry points
+    here: four threads calling dgemm_/dtrsm_ at once on their own data all get the right answer."""
+    import threading
+    errors = []
+
+    def worker(i):
+        try:
+            for rep in range(3):
+                check_case(ulm, "NT"[i % 2], "N", 300 + 17 * i, 200 + 5 * i, 150 + rep, 1.0 + i, 0.5, 9000 + 10 * i + rep)
+        except Exception as exc:        # noqa: BLE001 - reported below
+            errors.append((i, repr(exc)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors

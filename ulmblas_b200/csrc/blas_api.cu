@@ -17,6 +17,7 @@
 #include <cctype>
 #include <cstdarg>
 #include <cstring>
+#include <mutex>
 
 namespace ulmb200 {
 
@@ -37,6 +38,14 @@ int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, d
                   int64_t ldc);
 
 static int g_pin_host = 0;
+
+// The blocking BLAS entry points share the per-device staging and work buffers, so calls from
+// different host threads take turns (the reference guards its memory pool the same way,
+// ulmblas/auxiliary/memorypool.tcc:43,57).  Callers of the asynchronous ulmb200_* device ABI
+// order their own work: routines that use work buffers (dtrsm, dtrmm, dsymm, dgetrf, 3xTF32
+// sgemm) must not overlap on one device.
+static std::recursive_mutex g_call_mu;
+#define ULMB_SERIALISE std::lock_guard<std::recursive_mutex> ulmb_call_lock(g_call_mu)
 
 // ---- where does a pointer live? -------------------------------------------
 static bool on_device(const void *p)
@@ -137,6 +146,7 @@ template <typename T, typename Launch>
 static int gemm_any(Launch launch, int transA, int transB, int64_t m, int64_t n, int64_t k,
                     const T *A, int64_t lda, const T *B, int64_t ldb, bool read_c, T *C, int64_t ldc)
 {
+    ULMB_SERIALISE;
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
     const bool dA = on_device(A), dB = on_device(B), dC = on_device(C);
@@ -236,6 +246,7 @@ static int sgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, fl
 static int dsyrk_any(int lower, int trans, int64_t n, int64_t k, double alpha, const double *A,
                      int64_t lda, double beta, double *C, int64_t ldc)
 {
+    ULMB_SERIALISE;
     if (n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
     const bool dA = on_device(A), dC = on_device(C);
@@ -266,6 +277,7 @@ static int dsyrk_any(int lower, int trans, int64_t n, int64_t k, double alpha, c
 static int dtrsm_any(int side, int lower, int transA, int unit, int64_t m, int64_t n, double alpha,
                      const double *A, int64_t lda, double *B, int64_t ldb)
 {
+    ULMB_SERIALISE;
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
     const bool dA = on_device(A), dB = on_device(B);
@@ -325,6 +337,7 @@ static int stage_out(const Staged &o, cudaStream_t st)
 static int dtrmm_any(int side, int lower, int transA, int unit, int64_t m, int64_t n, double alpha,
                      const double *A, int64_t lda, double *B, int64_t ldb)
 {
+    ULMB_SERIALISE;
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
     Streams *s = streams();
@@ -342,6 +355,7 @@ static int dtrmm_any(int side, int lower, int transA, int unit, int64_t m, int64
 static int dsymm_any(int side, int lower, int64_t m, int64_t n, double alpha, const double *A, int64_t lda,
                      const double *B, int64_t ldb, double beta, double *C, int64_t ldc)
 {
+    ULMB_SERIALISE;
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
     Streams *s = streams();
@@ -360,6 +374,7 @@ static int dsymm_any(int side, int lower, int64_t m, int64_t n, double alpha, co
 static int dsyr2k_any(int lower, int trans, int64_t n, int64_t k, double alpha, const double *A, int64_t lda,
                       const double *B, int64_t ldb, double beta, double *C, int64_t ldc)
 {
+    ULMB_SERIALISE;
     if (n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
     Streams *s = streams();
@@ -840,6 +855,7 @@ void cblas_dsyr2k(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANS
 // return value is the 1-based index of the first zero pivot or 0.
 int ulmblas_dgetrf(enum CBLAS_ORDER order, int m, int n, double *A, int ldA, int *piv)
 {
+    ULMB_SERIALISE;
     if (order != CblasColMajor || m < 0 || n < 0 || ldA < std::max(1, m)) {
         int info = order != CblasColMajor ? 1 : (m < 0 ? 2 : (n < 0 ? 3 : 5));
         cblas_xerbla(info, "ulmblas_dgetrf", "");
