@@ -48,16 +48,31 @@ __device__ __forceinline__ bool lu_better(double v1, int64_t i1, double v2, int6
     return v1 > v2 || (v1 == v2 && i1 < i2);
 }
 
+// block-wide argmax: shuffles inside each warp, then one warp combines the 8 warp results
 __device__ __forceinline__ void lu_block_argmax(double &v, int64_t &i, double *sv, int64_t *si)
 {
-    const int t = threadIdx.x;
-    sv[t] = v; si[t] = i;
-    __syncthreads();
-    for (int s = kLuThreads / 2; s > 0; s >>= 1) {
-        if (t < s && lu_better(sv[t + s], si[t + s], sv[t], si[t])) { sv[t] = sv[t + s]; si[t] = si[t + s]; }
-        __syncthreads();
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const double ov = __shfl_down_sync(0xffffffffu, v, off);
+        const int64_t oi = __shfl_down_sync(0xffffffffu, i, off);
+        if (lu_better(ov, oi, v, i)) { v = ov; i = oi; }
     }
-    v = sv[0]; i = si[0];
+    if (lane == 0) { sv[warp] = v; si[warp] = i; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < kLuThreads / 32 ? sv[lane] : -2.0;
+        i = lane < kLuThreads / 32 ? si[lane] : INT64_MAX;
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) {
+            const double ov = __shfl_down_sync(0xffffffffu, v, off);
+            const int64_t oi = __shfl_down_sync(0xffffffffu, i, off);
+            if (lu_better(ov, oi, v, i)) { v = ov; i = oi; }
+        }
+        if (lane == 0) { sv[32] = v; si[32] = i; }
+    }
+    __syncthreads();
+    v = sv[32]; i = si[32];
     __syncthreads();
 }
 
@@ -303,7 +318,9 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
         a.A = A + j + j * lda; a.lda = lda; a.m = m - j; a.jb = jb; a.row_off = j;
         a.piv = d_piv; a.info = d_info; a.cand_val = cand_val; a.cand_idx = cand_idx;
         // short panels live in shared memory (64..192 rows per CTA); taller ones work in global memory
-        int64_t Gs = (a.m + 63) / 64;
+        static const int rows_per_cta = [] { const char *e = getenv("ULMB200_LU_ROWS"); int v = e ? atoi(e) : 0;
+                                             return (v >= 32 && v <= kLuSlabRows) ? v : 64; }();
+        int64_t Gs = (a.m + rows_per_cta - 1) / rows_per_cta;
         if (Gs > max_ctas[dev]) Gs = max_ctas[dev];
         if (Gs < 1) Gs = 1;
         if ((a.m + Gs - 1) / Gs <= kLuSlabRows) {
