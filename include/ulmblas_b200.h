@@ -160,6 +160,9 @@ void ulmblas_dsyr2k(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int
  * with row i, returns the 1-based index of the first zero pivot or 0.  CblasColMajor only
  * (CblasRowMajor returns -1; the reference's row-major mode is consistent only for m == n).   */
 int ulmblas_dgetrf(enum CBLAS_ORDER order, int m, int n, double *A, int ldA, int *piv);
+/* replaces ULMLAPACK(dlaswp), interfaces/lapack/C/laswp.cc (ulmblas/lapack/laswp.tcc): exchange rows
+ * i = k1..k2-1 of the n columns of A with rows piv[i*incPiv] (0-based; piv is host memory).   */
+void ulmblas_dlaswp(int n, double *A, int ldA, int k1, int k2, int *piv, int incPiv);
 
 /* replaces CBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-17 (weak)            */
 void cblas_xerbla(int info, const char *rout, const char *form, ...);

@@ -207,3 +207,18 @@ def test_calls_from_several_host_threads(ulm):
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_random_shapes_property(ulm):
+    """Randomised sweep (seeded): any shape up to 400, any transposition, any legal padding of the
+    leading dimensions (odd ones take the plain-load kernel, even ones the TMA kernel), random
+    alpha/beta including 0 and 1 -- always inside the bound, padding and inputs untouched."""
+    rng = np.random.default_rng(20261125)
+    for it in range(80):
+        m, n, k = (int(x) for x in rng.integers(1, 400, 3))
+        ta, tb = "NT"[rng.integers(2)], "NT"[rng.integers(2)]
+        alpha = float(rng.choice([0.0, 1.0, -1.0, 0.37, 2.5]))
+        beta = float(rng.choice([0.0, 1.0, -0.5, 1.3]))
+        ra, rb = (m if ta == "N" else k), (k if tb == "N" else n)
+        check_case(ulm, ta, tb, m, n, k, alpha, beta, 30000 + 3 * it, lda=ra + int(rng.integers(0, 5)),
+                   ldb=rb + int(rng.integers(0, 5)), ldc=m + int(rng.integers(0, 5)))

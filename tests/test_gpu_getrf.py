@@ -69,3 +69,26 @@ def test_dgetrf_row_major_is_refused(ulm):
     piv = np.zeros(4, dtype=np.int32)
     assert ulm.lib.ulmblas_dgetrf(ulm.CblasRowMajor, 4, 4, A.ctypes.data, 4, piv.ctypes.data) == -1
     assert ulm.last_status() == ulm.BAD_ARGUMENT
+
+
+def test_dlaswp_forward_and_backward(ulm):
+    """ulmblas_dlaswp against the row exchanges done in numpy; incPiv = -1 walks the rows backwards
+    and reads piv[-i] (ulmblas/lapack/laswp.tcc:22-24), which undoes a forward pass."""
+    rng = np.random.default_rng(9)
+    m, n, k1, k2 = 40, 300, 3, 29
+    A0 = det_uniform(72000, m, n)
+    piv = np.arange(m, dtype=np.int32)
+    piv[k1:k2] = rng.integers(k1, m, k2 - k1)
+    want = A0.copy()
+    for i in range(k1, k2):
+        want[[i, piv[i]]] = want[[piv[i], i]]
+    Av, Ab = padded(A0, m + 3)
+    ulm.lib.ulmblas_dlaswp(n, Av.ctypes.data, m + 3, k1, k2, piv.ctypes.data, 1)
+    assert ulm.last_status() == ulm.OK
+    assert np.array_equal(Av, want) and np.all(Ab[m:, :] == -1e10)
+    # backwards: the reference indexes piv[i*incPiv], i.e. piv[-i]; hand it a mirrored array
+    mirrored = np.zeros(2 * m, dtype=np.int32)
+    mirrored[m - np.arange(m)] = piv            # mirrored[m - i] = piv[i]
+    base = mirrored[m:]                         # base[-i] == piv[i]
+    ulm.lib.ulmblas_dlaswp(n, Av.ctypes.data, m + 3, k1, k2, base.ctypes.data, -1)
+    assert np.array_equal(Av, A0)

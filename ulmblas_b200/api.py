@@ -69,6 +69,8 @@ lib.ulmb200_set_pin_host.restype = None
 lib.ulmb200_dgetrf.argtypes = [_vp, _i64, _i64, _vp, _i64, _vp, _vp]
 lib.ulmblas_dgetrf.argtypes = [_int, _int, _int, _vp, _int, _vp]
 lib.ulmblas_dgetrf.restype = _int
+lib.ulmblas_dlaswp.argtypes = [_int, _vp, _int, _int, _int, _vp, _int]
+lib.ulmblas_dlaswp.restype = None
 lib.ulmb200_dsymm.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_dtrmm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
 lib.ulmb200_dsyr2k.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]

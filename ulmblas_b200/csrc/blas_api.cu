@@ -18,6 +18,7 @@
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace ulmb200 {
 
@@ -31,6 +32,7 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
 int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                  double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
 int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda, int *d_piv, int *d_info);
+int dlaswp_pairs_device(cudaStream_t st, double *A, int64_t lda, int64_t ncols, const int *d_pairs, int npairs);
 int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, double alpha, const double *A,
                  int64_t lda, const double *B, int64_t ldb, double beta, double *C, int64_t ldc);
 int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
@@ -881,6 +883,37 @@ int ulmblas_dgetrf(enum CBLAS_ORDER order, int m, int n, double *A, int ldA, int
     const int fin = finish(s);
     set_status(st != ULMB200_OK ? st : fin);
     return (st == ULMB200_OK && fin == ULMB200_OK) ? info : -100;
+}
+
+// replaces ULMLAPACK(dlaswp), interfaces/lapack/C/laswp.cc -> ulmBLAS::laswp (ulmblas/lapack/laswp.tcc):
+// rows i = k1 .. k2-1 of the n columns of A are exchanged with rows piv[i*incPiv], in increasing
+// order of i for incPiv > 0 and decreasing for incPiv < 0.  piv is read on the host.
+void ulmblas_dlaswp(int n, double *A, int ldA, int k1, int k2, int *piv, int incPiv)
+{
+    ULMB_SERIALISE;
+    if (incPiv == 0 || n <= 0 || k2 <= k1) { set_status(ULMB200_OK); return; }
+    if (ensure_device() != ULMB200_OK) { set_status(ULMB200_NO_DEVICE); return; }
+    Streams *s = streams();
+    if (!s) { set_status(ULMB200_CUDA_ERROR); return; }
+    std::vector<int> pairs;
+    int rows = k2;
+    const int inc = incPiv > 0 ? 1 : -1;
+    for (int i = incPiv > 0 ? k1 : k2 - 1; incPiv > 0 ? i < k2 : i >= k1; i += inc) {
+        const int ip = piv[(long)i * incPiv];
+        pairs.push_back(i); pairs.push_back(ip);
+        rows = std::max(rows, ip + 1);
+    }
+    int *dp = static_cast<int *>(device_scratch(10, sizeof(int) * pairs.size()));
+    if (!dp) { set_status(ULMB200_CUDA_ERROR); return; }
+    Staged a;
+    int st = stage_in(a, A, ldA, rows, n, 2, true, s->run);
+    if (st == ULMB200_OK)
+        st = check_cuda(cudaMemcpyAsync(dp, pairs.data(), sizeof(int) * pairs.size(), cudaMemcpyHostToDevice, s->run),
+                        "pairs", __FILE__, __LINE__);
+    if (st == ULMB200_OK) st = dlaswp_pairs_device(s->run, a.dev, a.ldd, n, dp, (int)(pairs.size() / 2));
+    if (st == ULMB200_OK) st = stage_out(a, s->run);
+    const int fin = finish(s);      // also keeps `pairs` alive until the copy has been consumed
+    set_status(st != ULMB200_OK ? st : fin);
 }
 
 }  // extern "C"

@@ -273,6 +273,30 @@ __global__ void laswp_kernel(double *A, int64_t lda, int64_t ncols, int64_t k1, 
     }
 }
 
+// Row exchanges given as (row, other row) pairs in the order they are to be applied.
+__global__ void laswp_pairs_kernel(double *A, int64_t lda, int64_t ncols, const int *pairs, int npairs)
+{
+    for (int64_t col = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; col < ncols;
+         col += (int64_t)gridDim.x * blockDim.x) {
+        double *c = A + col * lda;
+        for (int q = 0; q < npairs; ++q) {
+            const int i = pairs[2 * q], p = pairs[2 * q + 1];
+            if (p != i) { const double tmp = c[i]; c[i] = c[p]; c[p] = tmp; }
+        }
+    }
+}
+
+int dlaswp_pairs_device(cudaStream_t st, double *A, int64_t lda, int64_t ncols, const int *d_pairs, int npairs)
+{
+    if (ncols <= 0 || npairs <= 0) return ULMB200_OK;
+    int64_t blocks = (ncols + 127) / 128;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    laswp_pairs_kernel<<<(int)blocks, 128, 0, st>>>(A, lda, ncols, d_pairs, npairs);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "laswp_pairs_kernel", __FILE__, __LINE__);
+}
+
 static void launch_laswp(cudaStream_t st, double *A, int64_t lda, int64_t ncols, int64_t k1, int64_t k2,
                          const int *piv)
 {

@@ -1,6 +1,7 @@
 """Device-resident timings of every routine of the library on one GPU, as a table.
 
     python -m ulmblas_b200.perf_report [--quick]
+    python -m ulmblas_b200.perf_report --modes 4096     # one DGEMM per transposition mode
 
 CUDA events on the launching stream, 2 warm-ups, median of 5 (3 for the largest cases).  Rates
 are algorithmic flops / time: GEMM 2mnk, SYRK n(n+1)k, SYR2K 2n(n+1)k, SYMM 2m^2n, TRSM/TRMM m^2n
@@ -38,7 +39,19 @@ def _buf(rows, cols, dtype, seed, mat, dist=0, scale=1.0):
     return t
 
 
+def modes(sz):
+    """One DGEMM per transposition mode (NN, TN, NT, TT) at sz^3: the run to put under a profiler."""
+    s = torch.cuda.current_stream().cuda_stream
+    A = _buf(sz, sz, torch.float64, 1, 0); B = _buf(sz, sz, torch.float64, 1, 1); C = _buf(sz, sz, torch.float64, 1, 2)
+    for ta, tb in ((0, 0), (1, 0), (0, 1), (1, 1)):
+        ms = _time(lambda: u.dev_dgemm(ta, tb, sz, sz, sz, 1.0, A.data_ptr(), sz, B.data_ptr(), sz, 0.0,
+                                       C.data_ptr(), sz, stream=s), 1)
+        print(f"dgemm {'NT'[ta]}{'NT'[tb]} {sz}^3: {ms:.3f} ms {2.0 * sz ** 3 / ms * 1e-9:.2f} TFLOP/s")
+
+
 def main():
+    if "--modes" in sys.argv:
+        return modes(int(sys.argv[sys.argv.index("--modes") + 1]))
     quick = "--quick" in sys.argv
     s = torch.cuda.current_stream().cuda_stream
     rows = []
