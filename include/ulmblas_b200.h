@@ -87,6 +87,15 @@ void dsyr2k_(const char *upLo, const char *trans, const int *n, const int *k,
              const double *alpha, const double *A, const int *ldA,
              const double *B, const int *ldB, const double *beta, double *C, const int *ldC);
 
+/* replace F77BLAS(strsm) / F77BLAS(ssyrk), interfaces/blas/F77/trsm.cc, syrk.cc: float operands,
+ * arithmetic in double as in the reference (it widens alpha/beta to double there)               */
+void strsm_(const char *side, const char *upLo, const char *transA, const char *diag,
+            const int *m, const int *n, const float *alpha,
+            const float *A, const int *ldA, float *B, const int *ldB);
+void ssyrk_(const char *upLo, const char *trans, const int *n, const int *k,
+            const float *alpha, const float *A, const int *ldA,
+            const float *beta, float *C, const int *ldC);
+
 /* replaces F77BLAS(xerbla), interfaces/blas/F77/xerbla.cc:6-10.  Weak symbol:
  * a test harness may supply its own, exactly as the Netlib testers do.       */
 void xerbla_(const char rout[6], const int *info);
@@ -239,6 +248,14 @@ int ulmb200_dsyr2k(void *stream, int lower, int trans, int64_t n, int64_t k, dou
 /* Blocked LU on device operands; d_piv (min(m,n) ints) and d_info (1 int) are device
  * pointers written asynchronously.  Replaces ulmBLAS::getrf / getf2 / laswp.                */
 int ulmb200_dgetrf(void *stream, int64_t m, int64_t n, double *dA, int64_t ldA, int *d_piv, int *d_info);
+
+/* Single-precision SYRK / TRSM on device operands: widened to FP64 scratch, computed by the FP64
+ * kernels, rounded once (the reference's ssyrk_/strsm_ also compute in double).                  */
+int ulmb200_ssyrk(void *stream, int lower, int trans, int64_t n, int64_t k, float alpha,
+                  const float *dA, int64_t ldA, float beta, float *dC, int64_t ldC);
+int ulmb200_strsm(void *stream, int side, int lower, int transA, int unit,
+                  int64_t m, int64_t n, float alpha,
+                  const float *dA, int64_t ldA, float *dB, int64_t ldB);
 
 /* Deterministic test/bench matrices: element (i,j) of matrix `mat` under
  * `seed` is a pure function of (seed, mat, i, j), identical on host and device,

@@ -174,14 +174,23 @@ def _ref_extra(self):
                          _p(A), r(lda or _ld(A), _int), _p(B), r(ldb or _ld(B), _int), r(beta, _dbl), _p(Cm),
                          r(ldc or _ld(Cm), _int))
 
-    return dsymm, dtrmm, dsyr2k
+    def ssyrk(uplo, trans, n, k, alpha, A, beta, Cm, lda=None, ldc=None):
+        self.lib.ssyrk_(C.c_char_p(_c(uplo)), C.c_char_p(_c(trans)), r(n, _int), r(k, _int), r(alpha, _flt),
+                        _p(A), r(lda or _ld(A), _int), r(beta, _flt), _p(Cm), r(ldc or _ld(Cm), _int))
+
+    def strsm(side, uplo, ta, diag, m, n, alpha, A, B, lda=None, ldb=None):
+        self.lib.strsm_(C.c_char_p(_c(side)), C.c_char_p(_c(uplo)), C.c_char_p(_c(ta)), C.c_char_p(_c(diag)),
+                        r(m, _int), r(n, _int), r(alpha, _flt), _p(A), r(lda or _ld(A), _int), _p(B),
+                        r(ldb or _ld(B), _int))
+
+    return dsymm, dtrmm, dsyr2k, ssyrk, strsm
 
 
 def _ref_getattr(self, name):
-    """dsymm / dtrmm / dsyr2k of the compiled reference (interfaces/blas/F77/symm.cc:87,
+    """dsymm / dtrmm / dsyr2k / ssyrk / strsm of the compiled reference (interfaces/blas/F77/symm.cc:87,
     trmm.cc:123, syr2k.cc:92), bound on first use."""
-    if name in ("dsymm", "dtrmm", "dsyr2k"):
-        fns = dict(zip(("dsymm", "dtrmm", "dsyr2k"), _ref_extra(self)))
+    if name in ("dsymm", "dtrmm", "dsyr2k", "ssyrk", "strsm"):
+        fns = dict(zip(("dsymm", "dtrmm", "dsyr2k", "ssyrk", "strsm"), _ref_extra(self)))
         self.__dict__.update(fns)
         return fns[name]
     raise AttributeError(name)

@@ -156,3 +156,58 @@ def test_cblas_row_major_symm_trmm_syr2k(ulm):
     gauge = np.abs(A2) @ np.abs(B2).T + np.abs(B2) @ np.abs(A2).T + 0.5 * np.abs(C2)
     assert bound_ratio(np.where(low, got, 0), np.where(low, want, 0), gauge, 2 * k, EPS64) <= 1.0
     assert np.array_equal(got[~low], C2[~low])
+
+
+def test_single_precision_syrk_and_trsm(ulm):
+    """ssyrk_ / strsm_: float operands, double arithmetic -- as in the reference, whose shims widen
+    alpha and beta to double (interfaces/blas/F77/syrk.cc:30-32, trsm.cc:32).  Checked against the
+    compiled reference (portable build) and the fp32 componentwise bound."""
+    from helpers import EPS32
+    R = ref("plain")
+    seed = 80000
+    for (n, k) in [(7, 3), (130, 70), (300, 401)]:
+        for uplo, tr in itertools.product("UL", "NT"):
+            seed += 2
+            ra, ca = (n, k) if tr == "N" else (k, n)
+            A = det_uniform(seed, ra, ca, np.float32)
+            Cv, Cb = padded(det_uniform(seed + 1, n, n, np.float32), n + 3)
+            mask = tri_mask(n, uplo)
+            Cb[:n, :n][~mask] = ROGUE
+            oA = op(A.astype(np.float64), tr)
+            C0 = np.where(mask, Cb[:n, :n], 0.0).astype(np.float64)
+            want = 0.7 * (oA @ oA.T) + 1.3 * C0
+            gauge = 0.7 * (np.abs(oA) @ np.abs(oA).T) + 1.3 * np.abs(C0)
+            if R is not None:
+                w2 = Cb.copy(order="F")
+                R.ssyrk(uplo, tr, n, k, 0.7, A, 1.3, w2[:n, :n], ldc=n + 3)
+                want = w2[:n, :n]
+            got = Cb.copy(order="F")
+            assert ulm.ssyrk(uplo, tr, n, k, 0.7, A, 1.3, got[:n, :n], ldc=n + 3) == ulm.OK
+            assert np.array_equal(got[n:, :], Cb[n:, :]) and np.all(got[:n, :n][~mask] == np.float32(ROGUE))
+            assert bound_ratio(np.where(mask, got[:n, :n], 0), np.where(mask, want, 0), gauge, k, EPS32) <= 1.0
+    for (m, n) in [(7, 5), (130, 70), (300, 129)]:
+        for side, uplo, tr, diag in itertools.product("LR", "UL", "NT", "NU"):
+            seed += 2
+            na = m if side == "L" else n
+            A = det_uniform(seed, na, na).astype(np.float64)
+            d = np.diag(A).copy()
+            A = A / na
+            A[np.arange(na), np.arange(na)] = 1.5 + 0.25 * d
+            Af = np.asfortranarray(A.astype(np.float32))
+            Af[~tri_mask(na, uplo)] = ROGUE
+            Bv, Bb = padded(det_uniform(seed + 1, m, n, np.float32), m + 1)
+            T = np.where(tri_mask(na, uplo), Af, 0).astype(np.float64)
+            if diag == "U":
+                T = T - np.diag(np.diag(T)) + np.eye(na)
+            T = op(T, tr)
+            got = Bb.copy(order="F")
+            assert ulm.strsm(side, uplo, tr, diag, m, n, 0.5, Af, got[:m, :n], ldb=m + 1) == ulm.OK
+            X = got[:m, :n].astype(np.float64)
+            assert np.isfinite(X).all() and np.array_equal(got[m:, :], Bb[m:, :])
+            lhs = T @ X if side == "L" else X @ T
+            gauge = (np.abs(T) @ np.abs(X) if side == "L" else np.abs(X) @ np.abs(T)) + 0.5 * np.abs(Bv)
+            assert bound_ratio(lhs, 0.5 * Bv.astype(np.float64), gauge, na, EPS32) <= 1.0, (side, uplo, tr, diag, m, n)
+            if R is not None:
+                w2 = Bb.copy(order="F")
+                R.strsm(side, uplo, tr, diag, m, n, 0.5, Af, w2[:m, :n], ldb=m + 1)
+                assert np.abs(X - w2[:m, :n]).max() <= 2e-5 * max(1.0, np.abs(X).max())

@@ -74,7 +74,9 @@ lib.ulmblas_dlaswp.restype = None
 lib.ulmb200_dsymm.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_dtrmm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
 lib.ulmb200_dsyr2k.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
-for _name in ("dsymm_", "dtrmm_", "dsyr2k_", "dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "cblas_dgemm", "cblas_sgemm", "cblas_dtrsm",
+lib.ulmb200_ssyrk.argtypes = [_vp, _int, _int, _i64, _i64, _flt, _vp, _i64, _flt, _vp, _i64]
+lib.ulmb200_strsm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _flt, _vp, _i64, _vp, _i64]
+for _name in ("strsm_", "ssyrk_", "dsymm_", "dtrmm_", "dsyr2k_", "dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "cblas_dgemm", "cblas_sgemm", "cblas_dtrsm",
               "cblas_dsyrk", "ulmblas_dgemm", "ulmblas_sgemm", "ulmblas_dtrsm", "ulmblas_dsyrk"):
     getattr(lib, _name).restype = None
 lib.cblas_dgemm.argtypes = [_int, _int, _int, _int, _int, _int, _dbl, _vp, _int, _vp, _int, _dbl, _vp, _int]
@@ -165,6 +167,20 @@ def dsyrk(uplo, trans, n, k, alpha, A, beta, Cm, lda=None, ldc=None):
     """One triangle of C <- alpha*op(A)*op(A)^T + beta*C through ``dsyrk_``."""
     lib.dsyrk_(_cp(_c(uplo)), _cp(_c(trans)), _ri(n), _ri(k), C.byref(_dbl(alpha)), _p(A),
                _ri(lda or _ld(A)), C.byref(_dbl(beta)), _p(Cm), _ri(ldc or _ld(Cm)))
+    return last_status()
+
+
+def ssyrk(uplo, trans, n, k, alpha, A, beta, Cm, lda=None, ldc=None):
+    """Single-precision SYRK through ``ssyrk_`` (float32 arrays)."""
+    lib.ssyrk_(_cp(_c(uplo)), _cp(_c(trans)), _ri(n), _ri(k), C.byref(_flt(alpha)), _p(A),
+               _ri(lda or _ld(A)), C.byref(_flt(beta)), _p(Cm), _ri(ldc or _ld(Cm)))
+    return last_status()
+
+
+def strsm(side, uplo, transA, diag, m, n, alpha, A, B, lda=None, ldb=None):
+    """Single-precision TRSM through ``strsm_`` (float32 arrays)."""
+    lib.strsm_(_cp(_c(side)), _cp(_c(uplo)), _cp(_c(transA)), _cp(_c(diag)), _ri(m), _ri(n),
+               C.byref(_flt(alpha)), _p(A), _ri(lda or _ld(A)), _p(B), _ri(ldb or _ld(B)))
     return last_status()
 
 

@@ -32,6 +32,10 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
 int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                  double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
 int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda, int *d_piv, int *d_info);
+int ssyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, float alpha, const float *A,
+                 int64_t lda, float beta, float *C, int64_t ldc);
+int strsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n, float alpha,
+                 const float *A, int64_t lda, float *B, int64_t ldb);
 int dlaswp_pairs_device(cudaStream_t st, double *A, int64_t lda, int64_t ncols, const int *d_pairs, int npairs);
 int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, double alpha, const double *A,
                  int64_t lda, const double *B, int64_t ldb, double beta, double *C, int64_t ldc);
@@ -309,31 +313,71 @@ static int dtrsm_any(int side, int lower, int transA, int unit, int64_t m, int64
 
 // One staged operand: device pointers pass through, host matrices are copied into a cached
 // device buffer (slot) before the call and, when `back`, copied out after it.
-struct Staged {
-    const double *host = nullptr;
-    double *dev = nullptr;
+template <typename T>
+struct StagedT {
+    const T *host = nullptr;
+    T *dev = nullptr;
     int64_t ldh = 0, ldd = 0, rows = 0, cols = 0;
     bool staged = false;
 };
+typedef StagedT<double> Staged;
 
-static int stage_in(Staged &o, const double *p, int64_t ld, int64_t rows, int64_t cols, int slot, bool copy,
+template <typename T>
+static int stage_in(StagedT<T> &o, const T *p, int64_t ld, int64_t rows, int64_t cols, int slot, bool copy,
                     cudaStream_t st)
 {
     o.host = p; o.ldh = ld; o.rows = rows; o.cols = cols;
-    if (on_device(p) || rows <= 0 || cols <= 0) { o.dev = const_cast<double *>(p); o.ldd = ld; return ULMB200_OK; }
-    o.ldd = round_up(rows, 2);
-    o.dev = static_cast<double *>(device_scratch(slot, sizeof(double) * (size_t)(o.ldd * cols)));
+    if (on_device(p) || rows <= 0 || cols <= 0) { o.dev = const_cast<T *>(p); o.ldd = ld; return ULMB200_OK; }
+    o.ldd = round_up(rows, 4);
+    o.dev = static_cast<T *>(device_scratch(slot, sizeof(T) * (size_t)(o.ldd * cols)));
     if (!o.dev) return ULMB200_CUDA_ERROR;
     o.staged = true;
     if (copy) return check_cuda(copy_in(o.dev, o.ldd, p, ld, rows, cols, st), "copy in", __FILE__, __LINE__);
     return ULMB200_OK;
 }
 
-static int stage_out(const Staged &o, cudaStream_t st)
+template <typename T>
+static int stage_out(const StagedT<T> &o, cudaStream_t st)
 {
     if (!o.staged) return ULMB200_OK;
-    return check_cuda(copy_out(const_cast<double *>(o.host), o.ldh, o.dev, o.ldd, o.rows, o.cols, st), "copy out",
+    return check_cuda(copy_out(const_cast<T *>(o.host), o.ldh, o.dev, o.ldd, o.rows, o.cols, st), "copy out",
                       __FILE__, __LINE__);
+}
+
+static int ssyrk_any(int lower, int trans, int64_t n, int64_t k, float alpha, const float *A, int64_t lda,
+                     float beta, float *C, int64_t ldc)
+{
+    ULMB_SERIALISE;
+    if (n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t rows = trans ? k : n, cols = trans ? n : k;
+    StagedT<float> a, c;
+    int st = stage_in(a, A, lda, rows, cols, 0, true, s->run);
+    if (st == ULMB200_OK) st = stage_in(c, C, ldc, n, n, 2, true, s->run);
+    if (st == ULMB200_OK) st = ssyrk_device(s->run, lower, trans, n, k, alpha, a.dev, a.ldd, beta, c.dev, c.ldd);
+    if (st == ULMB200_OK) st = stage_out(c, s->run);
+    const int fin = finish(s);
+    return set_status(st != ULMB200_OK ? st : fin);
+}
+
+static int strsm_any(int side, int lower, int transA, int unit, int64_t m, int64_t n, float alpha,
+                     const float *A, int64_t lda, float *B, int64_t ldb)
+{
+    ULMB_SERIALISE;
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const int64_t dim = side == 0 ? m : n;
+    StagedT<float> a, b;
+    int st = stage_in(a, A, lda, dim, dim, 0, true, s->run);
+    if (st == ULMB200_OK) st = stage_in(b, B, ldb, m, n, 2, true, s->run);
+    if (st == ULMB200_OK) st = strsm_device(s->run, side, lower, transA, unit, m, n, alpha, a.dev, a.ldd, b.dev, b.ldd);
+    if (st == ULMB200_OK) st = stage_out(b, s->run);
+    const int fin = finish(s);
+    return set_status(st != ULMB200_OK ? st : fin);
 }
 
 static int dtrmm_any(int side, int lower, int transA, int unit, int64_t m, int64_t n, double alpha,
@@ -572,6 +616,49 @@ void dsyr2k_(const char *upLo, const char *trans, const int *n, const int *k, co
         return;
     }
     dsyr2k_any(up(upLo) == 'L', is_trans(trans), *n, *k, *alpha, A, *ldA, B, *ldB, *beta, C, *ldC);
+}
+
+// replaces F77BLAS(strsm), interfaces/blas/F77/trsm.cc (float operands, double arithmetic)
+void strsm_(const char *side, const char *upLo, const char *transA, const char *diag, const int *m,
+            const int *n, const float *alpha, const float *A, const int *ldA, float *B, const int *ldB)
+{
+    const bool left = up(side) == 'L';
+    const int rowsA = left ? *m : *n;
+    int info = 0;
+    if (up(side) != 'L' && up(side) != 'R') info = 1;
+    else if (up(upLo) != 'L' && up(upLo) != 'U') info = 2;
+    else if (!valid_trans(transA)) info = 3;
+    else if (up(diag) != 'U' && up(diag) != 'N') info = 4;
+    else if (*m < 0) info = 5;
+    else if (*n < 0) info = 6;
+    else if (*ldA < std::max(1, rowsA)) info = 9;
+    else if (*ldB < std::max(1, *m)) info = 11;
+    if (info != 0) {
+        xerbla_("STRSM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    strsm_any(left ? 0 : 1, up(upLo) == 'L', is_trans(transA), up(diag) == 'U', *m, *n, *alpha, A, *ldA, B, *ldB);
+}
+
+// replaces F77BLAS(ssyrk), interfaces/blas/F77/syrk.cc (float operands, double arithmetic)
+void ssyrk_(const char *upLo, const char *trans, const int *n, const int *k, const float *alpha,
+            const float *A, const int *ldA, const float *beta, float *C, const int *ldC)
+{
+    const int rowsA = is_trans(trans) ? *k : *n;
+    int info = 0;
+    if (up(upLo) != 'L' && up(upLo) != 'U') info = 1;
+    else if (!valid_trans(trans)) info = 2;
+    else if (*n < 0) info = 3;
+    else if (*k < 0) info = 4;
+    else if (*ldA < std::max(1, rowsA)) info = 7;
+    else if (*ldC < std::max(1, *n)) info = 10;
+    if (info != 0) {
+        xerbla_("SSYRK ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    ssyrk_any(up(upLo) == 'L', is_trans(trans), *n, *k, *alpha, A, *ldA, *beta, C, *ldC);
 }
 
 // ------------------------------- CBLAS ---------------------------------------

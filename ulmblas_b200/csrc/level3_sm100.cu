@@ -395,6 +395,90 @@ int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
     return set_status(c.status);
 }
 
+// ---------------------------------------------------------------------------
+// Single-precision syrk / trsm.  The reference widens alpha (and beta) to double in these
+// shims, so its ssyrk_ / strsm_ compute in double and round to float at the end of each
+// block (interfaces/blas/F77/syrk.cc:30-32, trsm.cc:32).  Same here: the float operands are
+// widened into scratch, the FP64 kernels above do the work, and the result is rounded once
+// on the way back (only the requested triangle of C is written).
+// ---------------------------------------------------------------------------
+__global__ void widen_kernel(const float *X, int64_t ldx, int64_t rows, int64_t cols, double *D, int64_t ldd)
+{
+    const int64_t total = rows * cols;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = e % rows, j = e / rows;
+        D[i + j * ldd] = (double)X[i + j * ldx];
+    }
+}
+
+// tri: 0 all, 1 upper (i <= j), 2 lower (i >= j)
+__global__ void narrow_kernel(const double *D, int64_t ldd, int64_t rows, int64_t cols, float *X, int64_t ldx, int tri)
+{
+    const int64_t total = rows * cols;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = e % rows, j = e / rows;
+        if (tri == 1 && i > j) continue;
+        if (tri == 2 && i < j) continue;
+        X[i + j * ldx] = (float)D[i + j * ldd];
+    }
+}
+
+static int grid_for(int64_t total)
+{
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    return (int)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+int ssyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, float alpha, const float *A,
+                 int64_t lda, float beta, float *C, int64_t ldc)
+{
+    if (n < 0 || k < 0) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t rowsA = trans ? k : n, colsA = trans ? n : k;
+    if (lda < (rowsA > 1 ? rowsA : 1) || ldc < (n > 1 ? n : 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    if (n == 0 || ((alpha == 0.0f || k == 0) && beta == 1.0f)) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    const int64_t lda_d = (rowsA + 1) / 2 * 2, ldc_d = (n + 1) / 2 * 2;
+    double *buf = static_cast<double *>(device_scratch(11, sizeof(double) * (size_t)(lda_d * (colsA > 0 ? colsA : 1) + ldc_d * n)));
+    if (!buf) return set_status(ULMB200_CUDA_ERROR);
+    double *Ad = buf, *Cd = buf + lda_d * (colsA > 0 ? colsA : 1);
+    if (rowsA > 0 && colsA > 0) { widen_kernel<<<grid_for(rowsA * colsA), 256, 0, st>>>(A, lda, rowsA, colsA, Ad, lda_d); count_launch(); }
+    // the unreferenced triangle of C is widened too but never converted back
+    widen_kernel<<<grid_for(n * n), 256, 0, st>>>(C, ldc, n, n, Cd, ldc_d);
+    count_launch();
+    int s = dsyrk_device(st, lower, trans, n, k, (double)alpha, Ad, lda_d, (double)beta, Cd, ldc_d);
+    if (s != ULMB200_OK) return s;
+    narrow_kernel<<<grid_for(n * n), 256, 0, st>>>(Cd, ldc_d, n, n, C, ldc, lower ? 2 : 1);
+    count_launch();
+    return set_status(check_cuda(cudaGetLastError(), "ssyrk", __FILE__, __LINE__));
+}
+
+int strsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n, float alpha,
+                 const float *A, int64_t lda, float *B, int64_t ldb)
+{
+    if (m < 0 || n < 0 || (side != 0 && side != 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    const int64_t dim = (side == 0) ? m : n;
+    if (lda < (dim > 1 ? dim : 1) || ldb < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    const int64_t lda_d = (dim + 1) / 2 * 2, ldb_d = (m + 1) / 2 * 2;
+    double *buf = static_cast<double *>(device_scratch(11, sizeof(double) * (size_t)(lda_d * dim + ldb_d * n)));
+    if (!buf) return set_status(ULMB200_CUDA_ERROR);
+    double *Ad = buf, *Bd = buf + lda_d * dim;
+    // the whole square is widened; the solver reads only the referenced triangle (rogue values in
+    // the other one convert to finite doubles or Inf/NaN that are never touched)
+    widen_kernel<<<grid_for(dim * dim), 256, 0, st>>>(A, lda, dim, dim, Ad, lda_d);
+    widen_kernel<<<grid_for(m * n), 256, 0, st>>>(B, ldb, m, n, Bd, ldb_d);
+    count_launch(2);
+    int s = dtrsm_device(st, side, lower, transA, unit, m, n, (double)alpha, Ad, lda_d, Bd, ldb_d);
+    if (s != ULMB200_OK) return s;
+    narrow_kernel<<<grid_for(m * n), 256, 0, st>>>(Bd, ldb_d, m, n, B, ldb, 0);
+    count_launch();
+    return set_status(check_cuda(cudaGetLastError(), "strsm", __FILE__, __LINE__));
+}
+
 }  // namespace ulmb200
 
 extern "C" int ulmb200_dsyrk(void *stream, int lower, int trans, int64_t n, int64_t k, double alpha,
@@ -425,6 +509,19 @@ extern "C" int ulmb200_dtrmm(void *stream, int side, int lower, int transA, int 
 {
     return ulmb200::dtrmm_device(static_cast<cudaStream_t>(stream), side, lower, transA, unit, m, n, alpha, dA,
                                  ldA, dB, ldB);
+}
+
+extern "C" int ulmb200_ssyrk(void *stream, int lower, int trans, int64_t n, int64_t k, float alpha,
+                             const float *dA, int64_t ldA, float beta, float *dC, int64_t ldC)
+{
+    return ulmb200::ssyrk_device(static_cast<cudaStream_t>(stream), lower, trans, n, k, alpha, dA, ldA, beta, dC, ldC);
+}
+
+extern "C" int ulmb200_strsm(void *stream, int side, int lower, int transA, int unit, int64_t m, int64_t n,
+                             float alpha, const float *dA, int64_t ldA, float *dB, int64_t ldB)
+{
+    return ulmb200::strsm_device(static_cast<cudaStream_t>(stream), side, lower, transA, unit, m, n, alpha, dA, ldA,
+                                 dB, ldB);
 }
 
 extern "C" int ulmb200_dtrsm(void *stream, int side, int lower, int transA, int unit, int64_t m,
