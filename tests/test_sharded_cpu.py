@@ -105,3 +105,148 @@ def test_two_gloo_ranks_compute_their_column_blocks(tmp_path):
     for p, (o, e) in zip(procs, outs):
         assert p.returncode == 0, e[-2000:]
     assert "OK" in outs[0][0]
+
+
+# ---------------------------------------------------------------------------
+# sharded triangular solve
+# ---------------------------------------------------------------------------
+from ulmblas_b200.sharded import run_trsm_panels, trsm_panel_widths, trsm_steps  # noqa: E402
+
+
+def _triangle(rng, na, lower, unit):
+    """(the triangle the solve means, what is stored: other triangle rogue, diagonal kept)."""
+    full = rng.uniform(-1, 1, (na, na)) / na + np.diag(rng.uniform(1, 2, na))
+    T = np.tril(full) if lower else np.triu(full)
+    rogue = np.triu(np.full((na, na), 7e9), 1) if lower else np.tril(np.full((na, na), 7e9), -1)
+    stored = T + rogue
+    if unit:
+        T = T.copy()
+        np.fill_diagonal(T, 1.0)
+    return T, stored
+
+
+def _numpy_doubles(X, stored, right, lower, trans, unit):
+    """Test doubles for the device TRSM / GEMM calls of one rank, acting on X in place."""
+    def solve(h, s, w):
+        if w is not None:
+            w.wait()
+        J = slice(s.j0, s.j1)
+        D = np.tril(stored[J, J]) if lower else np.triu(stored[J, J])
+        if unit:
+            D = D.copy()
+            np.fill_diagonal(D, 1.0)
+        Dop = D.T if trans else D
+        if right:
+            X[:, J] = np.linalg.solve(Dop.T, X[:, J].T).T
+        else:
+            X[J, :] = np.linalg.solve(Dop, X[J, :])
+
+    def update(h, s, w):
+        if w is not None:
+            w.wait()
+        J, R = slice(s.j0, s.j1), slice(s.r0, s.r1)
+        Ar = stored[R, J]
+        if not right and not trans:
+            X[R, :] -= Ar @ X[J, :]
+        elif not right:
+            X[J, :] -= Ar.T @ X[R, :]
+        elif not trans:
+            X[:, J] -= X[:, R] @ Ar
+        else:
+            X[:, R] -= X[:, J] @ Ar.T
+    return solve, update
+
+
+def test_trsm_steps_order_and_ranges():
+    # left, lower, no trans: forward, rest below the block, solve first
+    st = trsm_steps(False, True, False, 10, 4)
+    assert [(s.j0, s.j1, s.r0, s.r1, s.update_first) for s in st] == [
+        (0, 4, 4, 10, False), (4, 8, 8, 10, False), (8, 10, 10, 10, False)]
+    # left, lower, trans: effectively upper -> backward, update first
+    st = trsm_steps(False, True, True, 10, 4)
+    assert [(s.j0, s.j1, s.r0, s.r1, s.update_first) for s in st] == [
+        (8, 10, 10, 10, True), (4, 8, 8, 10, True), (0, 4, 4, 10, True)]
+    # right, upper, no trans: forward, rest above, update first
+    st = trsm_steps(True, False, False, 10, 4)
+    assert [(s.j0, s.j1, s.r0, s.r1, s.update_first) for s in st] == [
+        (0, 4, 0, 0, True), (4, 8, 0, 4, True), (8, 10, 0, 8, True)]
+    # growing panels, measured from the end the walk starts at
+    assert trsm_panel_widths(20, 2, grow=True) == [2, 2, 4, 8, 4]
+    assert trsm_panel_widths(5, 2) == [2, 2, 1]
+    st = trsm_steps(False, False, False, 20, 2, grow=True)          # left, upper: backward
+    assert [(s.j0, s.j1) for s in st] == [(18, 20), (16, 18), (12, 16), (4, 12), (0, 4)]
+    st = trsm_steps(False, False, False, 21, 2, grow=True)          # ragged piece first
+    assert [(s.j0, s.j1) for s in st] == [(20, 21), (18, 20), (16, 18), (12, 16), (4, 12), (0, 4)]
+    assert all((s.r0, s.r1) == (0, s.j0) for s in st)
+    assert trsm_steps(False, True, False, 0, 4) == []
+    assert len(trsm_steps(True, True, True, 5, 100)) == 1
+
+
+def test_trsm_panel_walk_all_sixteen_cases():
+    rng = np.random.default_rng(5)
+    for right in (False, True):
+        for lower in (False, True):
+            for trans in (False, True):
+                for unit in (False, True):
+                    na, other, kp = 37, 11, 8
+                    T, stored = _triangle(rng, na, lower, unit)
+                    op = T.T if trans else T
+                    B = rng.uniform(-1, 1, (other, na)) if right else rng.uniform(-1, 1, (na, other))
+                    X = B.copy()
+                    solve, update = _numpy_doubles(X, stored, right, lower, trans, unit)
+                    run_trsm_panels(trsm_steps(right, lower, trans, na, kp, grow=unit), 1, lambda a, b: None, None, solve, update)
+                    want = np.linalg.solve(op.T, B.T).T if right else np.linalg.solve(op, B)
+                    assert np.abs(X - want).max() < 1e-12, (right, lower, trans, unit)
+
+
+_TRSM_WORKER = r"""
+import os, sys
+sys.path.insert(0, %(root)r); sys.path.insert(0, os.path.join(%(root)r, "tests"))
+import numpy as np, torch, torch.distributed as dist
+from ulmblas_b200.sharded import column_block, row_block, run_trsm_panels, trsm_steps
+from test_sharded_cpu import _triangle, _numpy_doubles
+rank, world = int(sys.argv[1]), int(sys.argv[2])
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=sys.argv[3], RANK=str(rank), WORLD_SIZE=str(world))
+dist.init_process_group("gloo", rank=rank, world_size=world)
+na, other, kp = 150, 300, 64
+for right, lower, trans, unit in ((False, True, False, False), (False, False, True, True), (True, False, False, False), (True, True, True, False)):
+    rng = np.random.default_rng(11)                       # same stream on both ranks
+    T, stored = _triangle(rng, na, lower, unit)
+    op = T.T if trans else T
+    B = rng.uniform(-1, 1, (other, na)) if right else rng.uniform(-1, 1, (na, other))
+    b0, b1 = (row_block if right else column_block)(other, world, rank)
+    X = (B[b0:b1, :] if right else B[:, b0:b1]).copy()
+    # column-major A as a (na, na) tensor whose row j is column j; only rank 0 holds data at first
+    A = torch.from_numpy(np.ascontiguousarray(stored.T)) if rank == 0 else torch.zeros((na, na), dtype=torch.float64)
+    order = []
+    def A_panel(j0, j1): return A[j0:j1, :]
+    def recv(h, j0, j1):
+        order.append((j0, j1))
+        return dist.broadcast(h, src=0, async_op=True)
+    local = A.numpy().T                                    # view: fills in as panels arrive
+    solve, update = _numpy_doubles(X, local, right, lower, trans, unit)
+    steps = trsm_steps(right, lower, trans, na, 16, grow=True)
+    run_trsm_panels(steps, world, A_panel, recv, solve, update)
+    assert order == [(s.j0, s.j1) for s in steps]
+    want = np.linalg.solve(op.T, B.T).T if right else np.linalg.solve(op, B)
+    want = want[b0:b1, :] if right else want[:, b0:b1]
+    assert np.abs(X - want).max() < 1e-11, ("rank %%d" %% rank, right, lower, trans, unit)
+    assert np.array_equal(A.numpy().T, stored), "A did not arrive intact"
+if rank == 0:
+    print("OK")
+dist.destroy_process_group()
+"""
+
+
+def test_two_gloo_ranks_solve_their_blocks(tmp_path):
+    import socket
+    import subprocess
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    script = tmp_path / "trsm_worker.py"
+    script.write_text(_TRSM_WORKER % dict(root=ROOT))
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", str(port)], stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-2000:]
+    assert "OK" in outs[0][0]

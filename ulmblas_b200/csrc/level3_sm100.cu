@@ -39,39 +39,110 @@ int dsyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, do
 // ---------------------------------------------------------------------------
 constexpr int kNB = 128;          // diagonal block size
 
-// Inverse of one triangular diagonal block per CTA.  T(i,p) = A[i*sr + p*sc]
-// addresses the block as a LOWER triangular matrix (an upper-stored block is
-// read transposed); X = T^-1 is built row by row,
-//     x(i,:) = (e_i - sum_{p<i} T(i,p) x(p,:)) / T(i,i),
-// thread j owning column j.  The result is written as the inverse of the block
-// as stored (so transposed back for upper), the other triangle zero-filled.
-__global__ void __launch_bounds__(kNB)
+// Inverse of one triangular diagonal block per CTA, in place in shared memory.
+// The block is viewed as a LOWER triangular matrix L (an upper-stored block is read
+// transposed and its inverse written transposed back), padded to kNB x kNB with an identity.
+//   1. eight 16 x 16 diagonal blocks are inverted by one warp each, row by row:
+//          x(i,:) = (e_i - sum_{p<i} L(i,p) x(p,:)) / L(i,i),   lane j owning column j;
+//   2. three doubling levels (s = 16, 32, 64) complete [[A,0],[C,B]]^-1 = [[A',0],[-B' C A', B']]
+//      with two small products per pair, all 256 threads sharing the outputs:
+//          W = C A'   then   C <- -B' W.
+// The zeros above the diagonal are kept in shared memory, so the products need no triangle logic.
+constexpr int kTrtriThreads = 256;
+constexpr int kTrtriLeaf = 16;
+
+__global__ void __launch_bounds__(kTrtriThreads)
 trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *inv)
 {
-    extern __shared__ double X[];           // X[p*kNB + j]
+    extern __shared__ double trtri_smem[];
+    double *M = trtri_smem;                   // M[p*kNB + i] = L(i, p)
+    double *W = trtri_smem + kNB * kNB;       // 64 * 64 doubles
     const int blk = blockIdx.x;
     const int64_t r0 = (int64_t)blk * kNB;
     const int len = (int)((dim - r0) < kNB ? (dim - r0) : kNB);
     const double *Ab = A + r0 + r0 * lda;
-    const int64_t sr = lower ? 1 : lda, sc = lower ? lda : 1;
-    const int j = threadIdx.x;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 
-    for (int i = 0; i < len; ++i) {
-        double s = (i == j) ? 1.0 : 0.0;
-        // columns j > i stay zero; rows p < j of column j are zero, start at p = j
-        if (j <= i) {
-            for (int p = j; p < i; ++p) s -= __ldg(Ab + i * sr + p * sc) * X[p * kNB + j];
-            if (!unit) s /= __ldg(Ab + i * sr + i * sc);
+    // the lower view: strictly upper part zero, identity beyond len; the stored block is walked
+    // column by column, and its unreferenced triangle is never read
+    for (int e = t; e < kNB * kNB; e += kTrtriThreads) {
+        const int a = e % kNB, b = e / kNB;               // stored element (a, b) of the block
+        const int i = lower ? a : b, p = lower ? b : a;   // its place in the lower view
+        double v = 0.0;
+        if (i >= p) {
+            if (i < len) v = (unit && i == p) ? 1.0 : __ldg(Ab + a + (int64_t)b * lda);
+            else if (i == p) v = 1.0;
         }
-        X[i * kNB + j] = s;
+        M[p * kNB + i] = v;
     }
     __syncthreads();
-    // write the full kNB x kNB block (zeros outside len x len and outside the triangle)
+
+    // 1. leaves
+    {
+        const int b0 = warp * kTrtriLeaf;
+        const int j = lane & (kTrtriLeaf - 1);
+        for (int i = 0; i < kTrtriLeaf; ++i) {
+            const double trow = M[(b0 + j) * kNB + b0 + i];      // L(i, j) of the leaf (zero for j > i)
+            __syncwarp();
+            double s = (i == j) ? 1.0 : 0.0;
+            for (int p = 0; p < i; ++p) {
+                const double tp = __shfl_sync(0xffffffffu, trow, p);
+                s -= tp * M[(b0 + j) * kNB + b0 + p];            // x(p, j); zero for j > p
+            }
+            const double d = __shfl_sync(0xffffffffu, trow, i);
+            if (!unit) s /= d;
+            if (j > i) s = 0.0;
+            __syncwarp();
+            if (lane < kTrtriLeaf) M[(b0 + j) * kNB + b0 + i] = s;
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+
+    // 2. doubling: per pair 4 s threads, thread = (row i, column group g of 4); a thread walks its
+    // columns g, g+4, ... four at a time so that four independent sums are in flight
+    for (int s = kTrtriLeaf; s < kNB; s *= 2) {
+        const int pairs = kNB / (2 * s);
+        const int tpp = kTrtriThreads / pairs;                 // = 4 s
+        const int q = t / tpp, tt = t % tpp;
+        const int i = tt % s, g = tt / s;                      // g in 0..3
+        const int o = q * 2 * s;
+        const double *Ainv = M + o * kNB + o;                  // (r, c) at [c*kNB + r]
+        const double *Binv = M + (o + s) * kNB + (o + s);
+        double *Cb = M + o * kNB + (o + s);
+        double *Wq = W + q * s * s;                            // (r, c) at [c*s + r]
+        // W = C A'      (A'(p, j) = 0 for p < j)
+        for (int j0 = g; j0 < s; j0 += 16) {
+            double acc[4] = {0.0, 0.0, 0.0, 0.0};
+            for (int p = j0; p < s; ++p) {
+                const double c = Cb[p * kNB + i];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] += c * Ainv[(j0 + 4 * u) * kNB + p];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) Wq[(j0 + 4 * u) * s + i] = acc[u];
+        }
+        __syncthreads();
+        // C <- -B' W    (B'(i, p) = 0 for p > i)
+        for (int j0 = g; j0 < s; j0 += 16) {
+            double acc[4] = {0.0, 0.0, 0.0, 0.0};
+            for (int p = 0; p <= i; ++p) {
+                const double bv = Binv[p * kNB + i];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] += bv * Wq[(j0 + 4 * u) * s + p];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) Cb[(j0 + 4 * u) * kNB + i] = -acc[u];
+        }
+        __syncthreads();
+    }
+
+    // the full kNB x kNB block goes out (zeros outside len x len and outside the triangle)
     double *out = inv + (int64_t)blk * kNB * kNB;
-    for (int i = 0; i < kNB; ++i) {
-        // element (i, j) of the lower-view inverse
-        double v = (i < len && j < len && j <= i) ? X[i * kNB + j] : 0.0;
-        if (lower) out[i + j * kNB] = v;      // coalescing is irrelevant at this size
+    for (int e = t; e < kNB * kNB; e += kTrtriThreads) {
+        const int i = e % kNB, j = e / kNB;           // lower view (i, j)
+        const double v = (i < len && j < len && j <= i) ? M[j * kNB + i] : 0.0;
+        if (lower) out[i + j * kNB] = v;
         else       out[j + i * kNB] = v;
     }
 }
@@ -196,12 +267,12 @@ int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int uni
     const int nblk = (int)((dim + kNB - 1) / kNB);
     static bool attr_done[kMaxDevices] = {};
     const int dev = current_device();
-    const int smem = kNB * kNB * (int)sizeof(double);
+    const int smem = (kNB * kNB + 64 * 64) * (int)sizeof(double);
     if (!attr_done[dev]) {
         ULMB_CUDA(cudaFuncSetAttribute(trtri_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done[dev] = true;
     }
-    trtri_blocks_kernel<<<nblk, kNB, smem, st>>>(A, lda, dim, lower, unit, inv);
+    trtri_blocks_kernel<<<nblk, kTrtriThreads, smem, st>>>(A, lda, dim, lower, unit, inv);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
 

@@ -2,6 +2,8 @@
 
     python -m ulmblas_b200.perf_report [--quick]
     python -m ulmblas_b200.perf_report --modes 4096     # one DGEMM per transposition mode
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        -m ulmblas_b200.perf_report --sharded-trsm 8192  # DTRSM LLNN split over N GPUs
 
 CUDA events on the launching stream, 2 warm-ups, median of 5 (3 for the largest cases).  Rates
 are algorithmic flops / time: GEMM 2mnk, SYRK n(n+1)k, SYR2K 2n(n+1)k, SYMM 2m^2n, TRSM/TRMM m^2n
@@ -49,7 +51,62 @@ def modes(sz):
         print(f"dgemm {'NT'[ta]}{'NT'[tb]} {sz}^3: {ms:.3f} ms {2.0 * sz ** 3 / ms * 1e-9:.2f} TFLOP/s")
 
 
+def sharded_trsm(m):
+    """DTRSM left/lower/no-trans/non-unit, m x m, B split by column blocks over the ranks of the
+    job; A starts on rank 0 only.  Prints the whole-job rate (m^2 n / max-over-ranks device time)
+    and each rank's largest deviation from the one-call solve of its block."""
+    import os
+    import torch.distributed as dist
+    from .sharded import ShardedDtrsm
+    os.environ.setdefault("NCCL_MAX_CTAS", "8")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if "RANK" in os.environ:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    op = ShardedDtrsm(False, True, False, False, m, m)
+    j0, j1 = op.block
+    nr = j1 - j0
+    A = torch.zeros((m, m), dtype=torch.float64, device="cuda")
+    if rank == 0:
+        u.dev_fill_f64(A.data_ptr(), m, m, m, 3, 0, dist=1, scale=1.0 / m)
+    B0 = torch.empty((max(nr, 1), m), dtype=torch.float64, device="cuda")
+    u.dev_fill_f64(B0.data_ptr(), m, m, nr, 3, 1, col0=j0)
+    X = B0.clone()
+    ts = []
+    for it in range(5):
+        X.copy_(B0)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        op.run(1.0, A, X)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if it >= 2:
+            ts.append(float(t.item()))
+    ref = B0.clone()                                      # A has arrived on every rank by now
+    u.dev_dtrsm(0, 1, 0, 0, m, nr, 1.0, A.data_ptr(), m, ref.data_ptr(), m,
+                stream=torch.cuda.current_stream().cuda_stream)
+    dev = torch.tensor([float((X - ref).abs().max().item()) if nr else 0.0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(dev, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = statistics.median(ts)
+        print(f"dtrsm LLNN m=n={m} on {world} GPU(s): {ms:.3f} ms {float(m) ** 3 / ms * 1e-9:.2f} TFLOP/s "
+              f"(whole job, A broadcast inside the timed region), max |X - X_one_call| = {dev.item():.3e}")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
 def main():
+    if "--sharded-trsm" in sys.argv:
+        return sharded_trsm(int(sys.argv[sys.argv.index("--sharded-trsm") + 1]))
     if "--modes" in sys.argv:
         return modes(int(sys.argv[sys.argv.index("--modes") + 1]))
     quick = "--quick" in sys.argv

@@ -1,4 +1,4 @@
-"""Large DGEMM split over the GPUs of one box by column blocks of C.
+"""Large DGEMM (and, further down, DTRSM) split over the GPUs of one box by column blocks of C.
 
     C[:, J_r] <- alpha * A * B[:, J_r] + beta * C[:, J_r]        on rank r
 
@@ -163,3 +163,219 @@ class ShardedDgemm:
         cur.wait_stream(self.compute)
         cur.wait_stream(self.comm)
         return j0, j1
+
+
+# ---------------------------------------------------------------------------
+# Triangular solve split over the GPUs
+# ---------------------------------------------------------------------------
+# op(A) X = alpha B (left) has independent columns of B, X op(A) = alpha B (right) independent
+# rows: rank r keeps a column block (left) or a row block (right) of B and overwrites it with
+# its part of X.  Only A travels.  The solve walks A by column panels J -- contiguous in
+# column-major storage, so each is one broadcast -- and every one of the eight
+# side/uplo/trans cases needs exactly column panel J at step J:
+#
+#   left,  no trans   solve X_J with A[J,J];  then  B[rest,:] -= A[rest,J]   X_J      (right-looking)
+#   left,  trans      B[J,:] -= A[rest,J]^T X_rest;  then solve X_J with A[J,J]^T     (left-looking)
+#   right, no trans   B[:,J] -= X_rest A[rest,J];    then solve X_J with A[J,J]       (left-looking)
+#   right, trans      solve X_J with A[J,J]^T; then B[:,rest] -= X_J A[rest,J]^T      (right-looking)
+#
+# with rest = the rows of the panel below J when A is stored lower, above J when stored upper.
+# The reference reaches the same eight cases by swapping strides in front of two drivers
+# (interfaces/blas/F77/trsm.cc:183-227) and blocks each by MC (ulmblas/level3/trlsm.tcc:66-88).
+
+@dataclass
+class TrsmStep:
+    j0: int
+    j1: int
+    r0: int            # rest = [r0, r1)
+    r1: int
+    update_first: bool  # left-looking: the update precedes the solve of the block
+
+
+def trsm_panel_widths(na, kp, grow=False):
+    """Widths of the panels in the order they are processed.  With `grow` the walk starts with two
+    panels of kp and doubles from there (kp, kp, 2kp, 4kp, ...): the first panel, whose transfer
+    nothing can hide, stays small, while later steps are large enough to run at full rate."""
+    out, left, w, count = [], na, max(1, kp), 0
+    while left > 0:
+        take = min(w, left)
+        out.append(take)
+        left -= take
+        count += 1
+        if grow and count >= 2:
+            w *= 2
+    return out
+
+
+def trsm_steps(right, lower, trans, na, kp, grow=False):
+    """Ordered steps of the panelled solve with a triangle of order `na` and first panel width `kp`."""
+    if na <= 0:
+        return []
+    eff_lower = bool(lower) != bool(trans)
+    forward = eff_lower if not right else (not eff_lower)
+    update_first = bool(trans) if not right else (not bool(trans))
+    out, pos = [], (0 if forward else na)
+    kp = max(1, min(kp, na))
+    widths = trsm_panel_widths(na, kp, grow)
+    if not forward and na % kp:
+        # a backward walk takes the ragged piece first, so that every boundary stays a multiple of kp
+        widths = [na % kp] + trsm_panel_widths(na - na % kp, kp, grow)
+    for w in widths:
+        j0, j1 = (pos, pos + w) if forward else (pos - w, pos)
+        pos = j1 if forward else j0
+        r0, r1 = (j1, na) if lower else (0, j0)
+        out.append(TrsmStep(j0, j1, r0, r1, update_first))
+    return out
+
+
+def row_block(m, world, rank, align=ALIGN):
+    """Row blocks of the right-side solve: same cut as the column blocks."""
+    return column_block(m, world, rank, align)
+
+
+def run_trsm_panels(steps, world, A_panel, recv_panel, solve, update):
+    """Drive one sharded solve.
+
+    A_panel(j0, j1)        -> handle of the local buffer that holds / will hold A[:, j0:j1]
+    recv_panel(h, j0, j1)  -> makes that panel present on this rank; returns a waitable or None
+    solve(h, step, waitable)   -> queues the solve of block J with the panel's diagonal block
+    update(h, step, waitable)  -> queues the update that uses A[rest, J]   (skipped when rest is empty)
+    The first of the two that a step queues gets the panel's waitable, the second gets None.
+    All broadcasts are queued before the first arithmetic, in the order the steps need them.
+    """
+    pending = []
+    for s in steps:
+        h = A_panel(s.j0, s.j1)
+        w = recv_panel(h, s.j0, s.j1) if world > 1 else None
+        pending.append((h, s, w))
+    for (h, s, w) in pending:
+        have_rest = s.r1 > s.r0
+        if s.update_first and have_rest:
+            update(h, s, w)
+            solve(h, s, None)
+        else:
+            solve(h, s, w)
+            if have_rest:
+                update(h, s, None)
+
+
+class ShardedDtrsm:
+    """Device-resident sharded DTRSM on torch CUDA buffers (column-major, as the BLAS sees them).
+
+    A  : torch.float64 tensor of shape (na, na) on every rank (column-major, ld = na; element
+         (i, j) at A[j, i]); only the root's copy needs to hold data before ``run``.
+    Bl : left  side: (nr, m) this rank's column block of B (column-major m x nr, ld = m)
+         right side: (n, mr) this rank's row block of B    (column-major mr x n, ld = mr)
+    """
+
+    def __init__(self, right, lower, trans, unit, m, n, kp=512, grow=True, group=None, root=0,
+                 reserve_sms=8, force_panels=False):
+        import torch
+        import torch.distributed as dist
+        from . import api
+        self.torch, self.dist, self.api = torch, dist, api
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.group, self.root = group, root
+        self.right, self.lower, self.trans, self.unit = bool(right), bool(lower), bool(trans), bool(unit)
+        self.m, self.n = m, n
+        self.na = n if right else m
+        self.block = row_block(m, self.world, self.rank) if right else column_block(n, self.world, self.rank)
+        # one GPU has nothing to wait for: one call, unless a test asks for the panelled walk
+        self.panelled = self.world > 1 or force_panels
+        self.steps = trsm_steps(right, lower, trans, self.na, kp, grow) if self.panelled else []
+        self.compute = torch.cuda.Stream()
+        self.comm = torch.cuda.Stream()
+        self.reserve_sms = reserve_sms if self.world > 1 else 0
+
+    def run(self, alpha, A, Bl):
+        torch, dist, api = self.torch, self.dist, self.api
+        b0, b1 = self.block
+        nb = b1 - b0                                  # my columns (left) or rows (right)
+        na = self.na
+        ldb = na if not self.right else max(nb, 1)
+        cur = torch.cuda.current_stream()
+        self.compute.wait_stream(cur)
+        self.comm.wait_stream(cur)
+        cs = self.compute.cuda_stream
+        pB = Bl.data_ptr()
+        side = 1 if self.right else 0
+
+        if not self.panelled:
+            if nb > 0:
+                with torch.cuda.stream(self.compute):
+                    if self.right:
+                        api.dev_dtrsm(1, self.lower, self.trans, self.unit, nb, na, alpha, A.data_ptr(), na, pB, ldb, stream=cs)
+                    else:
+                        api.dev_dtrsm(0, self.lower, self.trans, self.unit, na, nb, alpha, A.data_ptr(), na, pB, ldb, stream=cs)
+            cur.wait_stream(self.compute)
+            return b0, b1
+
+        if nb > 0 and alpha != 1.0:
+            # B <- alpha B once, then every step works with alpha = 1 (a product with k = 0 only scales)
+            rows, cols = (nb, na) if self.right else (na, nb)
+            with torch.cuda.stream(self.compute):
+                api.dev_dgemm(0, 0, rows, cols, 0, 0.0, pB, max(rows, 1), pB, 1, alpha, pB, ldb, stream=cs)
+
+        def A_panel(j0, j1):
+            return A[j0:j1, :]
+
+        def recv_panel(h, j0, j1):
+            with torch.cuda.stream(self.comm):
+                return dist.broadcast(h, src=self.root, group=self.group, async_op=True)
+
+        done = [0]
+        nsteps = len(self.steps)
+
+        def reserve():
+            # leave SMs to the transport while panels are still on their way (first half of the walk)
+            api.set_sm_reserve(self.reserve_sms if 2 * done[0] < nsteps else 0)
+
+        def el(i, j, base, ld):                        # address of element (i, j)
+            return base + 8 * (i + j * ld)
+
+        pA = A.data_ptr()
+
+        def solve(h, s, w):
+            with torch.cuda.stream(self.compute):
+                if w is not None:
+                    w.wait()
+                if nb == 0:
+                    return
+                reserve()
+                jb = s.j1 - s.j0
+                if self.right:
+                    api.dev_dtrsm(1, self.lower, self.trans, self.unit, nb, jb, 1.0, el(s.j0, s.j0, pA, na), na,
+                                  el(0, s.j0, pB, ldb), ldb, stream=cs)
+                else:
+                    api.dev_dtrsm(0, self.lower, self.trans, self.unit, jb, nb, 1.0, el(s.j0, s.j0, pA, na), na,
+                                  el(s.j0, 0, pB, ldb), ldb, stream=cs)
+                done[0] += 1
+
+        def update(h, s, w):
+            with torch.cuda.stream(self.compute):
+                if w is not None:
+                    w.wait()
+                if nb == 0:
+                    return
+                reserve()
+                jb, nrest = s.j1 - s.j0, s.r1 - s.r0
+                a_rest = el(s.r0, s.j0, pA, na)                     # A[rest, J]
+                if not self.right and not self.trans:               # B[rest,:] -= A[rest,J] B[J,:]
+                    api.dev_dgemm(0, 0, nrest, nb, jb, -1.0, a_rest, na, el(s.j0, 0, pB, ldb), ldb, 1.0,
+                                  el(s.r0, 0, pB, ldb), ldb, stream=cs)
+                elif not self.right:                                # B[J,:] -= A[rest,J]^T B[rest,:]
+                    api.dev_dgemm(1, 0, jb, nb, nrest, -1.0, a_rest, na, el(s.r0, 0, pB, ldb), ldb, 1.0,
+                                  el(s.j0, 0, pB, ldb), ldb, stream=cs)
+                elif not self.trans:                                # B[:,J] -= B[:,rest] A[rest,J]
+                    api.dev_dgemm(0, 0, nb, jb, nrest, -1.0, el(0, s.r0, pB, ldb), ldb, a_rest, na, 1.0,
+                                  el(0, s.j0, pB, ldb), ldb, stream=cs)
+                else:                                               # B[:,rest] -= B[:,J] A[rest,J]^T
+                    api.dev_dgemm(0, 1, nb, nrest, jb, -1.0, el(0, s.j0, pB, ldb), ldb, a_rest, na, 1.0,
+                                  el(0, s.r0, pB, ldb), ldb, stream=cs)
+
+        run_trsm_panels(self.steps, self.world, A_panel, recv_panel, solve, update)
+        api.set_sm_reserve(0)
+        cur.wait_stream(self.compute)
+        cur.wait_stream(self.comm)
+        return b0, b1
