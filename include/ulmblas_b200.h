@@ -96,6 +96,16 @@ void ssyrk_(const char *upLo, const char *trans, const int *n, const int *k,
             const float *alpha, const float *A, const int *ldA,
             const float *beta, float *C, const int *ldC);
 
+/* replaces F77BLAS(zgemm), interfaces/blas/F77/gemm.cc:381-510: complex double, matrices as
+ * interleaved (re, im) pairs, leading dimensions in complex elements, alpha and beta as
+ * pointers to {re, im}.  trans: 'N', 'T', 'C' (conjugate transpose), 'R' (conjugate only,
+ * gemm.cc:401-402).  xerbla_ codes as dgemm_, name "ZGEMM ".                                    */
+void zgemm_(const char *transA, const char *transB,
+            const int *m, const int *n, const int *k,
+            const double *alpha, const double *A, const int *ldA,
+            const double *B, const int *ldB,
+            const double *beta, double *C, const int *ldC);
+
 /* replaces F77BLAS(xerbla), interfaces/blas/F77/xerbla.cc:6-10.  Weak symbol:
  * a test harness may supply its own, exactly as the Netlib testers do.       */
 void xerbla_(const char rout[6], const int *info);
@@ -145,6 +155,15 @@ void ulmblas_dtrsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
 void ulmblas_dsyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k,
                    double alpha, const double *A, int ldA, double beta, double *C, int ldC);
 
+/* replace CBLAS(zgemm) and ULMBLAS(zgemm), interfaces/blas/C/gemm.cc:584-677, :219-292;
+ * AtlasConj = conjugate without transposing                                            */
+void cblas_zgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                 int m, int n, int k, const double *alpha, const double *A, int ldA,
+                 const double *B, int ldB, const double *beta, double *C, int ldC);
+void ulmblas_zgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                   int m, int n, int k, const double *alpha, const double *A, int ldA,
+                   const double *B, int ldB, const double *beta, double *C, int ldC);
+
 /* replace CBLAS(dsymm) / CBLAS(dtrmm) / CBLAS(dsyr2k) and their ULMBLAS() twins,
  * interfaces/blas/C/symm.cc, trmm.cc, syr2k.cc                                */
 void cblas_dsymm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, int m, int n,
@@ -193,6 +212,16 @@ int ulmb200_dgemm(void *stream, int transA, int transB,
                   int64_t m, int64_t n, int64_t k, double alpha,
                   const double *dA, int64_t ldA, const double *dB, int64_t ldB,
                   double beta, double *dC, int64_t ldC);
+
+/* Complex double GEMM on the same tensor-core path: the operands are split into real and
+ * imaginary planes (work memory: 2(mk + kn + mn) doubles, cached per device), four real
+ * products follow, one pass folds alpha, beta and the result into C.  transX as above,
+ * conjX: 1 = conjugate op(X).  Replaces ulmBLAS::gemm<std::complex<double>>
+ * (ulmblas/level3/gemm.tcc:16-87 with conjugating pack, pack/gepack.tcc:21-33).        */
+int ulmb200_zgemm(void *stream, int transA, int conjA, int transB, int conjB,
+                  int64_t m, int64_t n, int64_t k, const double *alpha,
+                  const double *dA, int64_t ldA, const double *dB, int64_t ldB,
+                  const double *beta, double *dC, int64_t ldC);
 
 /* SGEMM.  mode 0: FP32 FMA pipes; mode 1: opt-in 3xTF32 on tcgen05 tensor
  * cores with FP32 accumulation in tensor memory.  Replaces the float

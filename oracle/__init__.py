@@ -57,6 +57,8 @@ class Port:
                                        _vp, _i64, _dbl, _vp, _i64]
         L.ulm_oracle_sgemm.argtypes = [_chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64,
                                        _vp, _i64, _flt, _vp, _i64]
+        L.ulm_oracle_zgemm.argtypes = [_chr, _chr, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64]
+        L.ulm_oracle_zgemm.restype = None
         L.ulm_oracle_dtrsm.argtypes = [_chr] * 4 + [_i64, _i64, _dbl, _vp, _i64, _vp, _i64]
         L.ulm_oracle_dsyrk.argtypes = [_chr, _chr, _i64, _i64, _dbl, _vp, _i64, _dbl, _vp, _i64]
         L.ulm_oracle_gemm_info.argtypes = [_chr, _chr] + [_int] * 6
@@ -66,8 +68,10 @@ class Port:
                   L.ulm_oracle_dsyrk, L.ulm_oracle_set_blocks):
             f.restype = None
 
-    def set_blocks(self, mc=384, kc=384, nc=4096):
+    def set_blocks(self, mc=384, kc=384, nc=4096, kc_z=192):
+        """Cache blocks of the real types and KC of complex double (defaults = the reference's)."""
         self.lib.ulm_oracle_set_blocks(mc, kc, nc)
+        self.lib.ulm_oracle_set_blocks_z(kc_z)
 
     def dgemm(self, ta, tb, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
         self.lib.ulm_oracle_dgemm(_c(ta), _c(tb), m, n, k, alpha, _p(A), lda or _ld(A),
@@ -76,6 +80,12 @@ class Port:
     def sgemm(self, ta, tb, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
         self.lib.ulm_oracle_sgemm(_c(ta), _c(tb), m, n, k, alpha, _p(A), lda or _ld(A),
                                   _p(B), ldb or _ld(B), beta, _p(Cm), ldc or _ld(Cm))
+
+    def zgemm(self, ta, tb, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+        """complex128 column-major arrays; alpha, beta Python complex."""
+        al, be = (_dbl * 2)(alpha.real, alpha.imag), (_dbl * 2)(beta.real, beta.imag)
+        self.lib.ulm_oracle_zgemm(_c(ta), _c(tb), m, n, k, al, _p(A), lda or _ld(A),
+                                  _p(B), ldb or _ld(B), be, _p(Cm), ldc or _ld(Cm))
 
     def dtrsm(self, side, uplo, ta, diag, m, n, alpha, A, B, lda=None, ldb=None):
         self.lib.ulm_oracle_dtrsm(_c(side), _c(uplo), _c(ta), _c(diag), m, n, alpha,
@@ -140,6 +150,15 @@ class Ref:
 
     def sgemm(self, ta, tb, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
         self._gemm("sgemm_", _flt, ta, tb, m, n, k, alpha, A, B, beta, Cm, lda, ldb, ldc)
+
+    def zgemm(self, ta, tb, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+        """zgemm_ (interfaces/blas/F77/gemm.cc:381): complex128 arrays, alpha/beta by reference as {re, im}."""
+        r = self._r
+        al, be = (_dbl * 2)(alpha.real, alpha.imag), (_dbl * 2)(beta.real, beta.imag)
+        self.shim.ulm_shim_gemm(
+            self._fn("zgemm_"), C.c_char_p(_c(ta)), C.c_char_p(_c(tb)), r(m, _int), r(n, _int),
+            r(k, _int), al, _p(A), r(lda or _ld(A), _int), _p(B),
+            r(ldb or _ld(B), _int), be, _p(Cm), r(ldc or _ld(Cm), _int))
 
     def dtrsm(self, side, uplo, ta, diag, m, n, alpha, A, B, lda=None, ldb=None):
         r = self._r

@@ -31,6 +31,7 @@
 #include <string.h>
 
 static int g_MC = 384, g_KC = 384, g_NC = 4096;
+static int g_KC_z = 192;   /* BlockSize<std::complex<double>>::KC, config/blocksize.h:41 */
 enum { MR = 4, NR = 4 };   /* BlockSizeUGemm<double>, ukernel/sse/ugemm.h:12-15 */
 
 void ulm_oracle_set_blocks(int mc, int kc, int nc)
@@ -38,6 +39,13 @@ void ulm_oracle_set_blocks(int mc, int kc, int nc)
     if (mc > 0) g_MC = mc;
     if (kc > 0) g_KC = kc;
     if (nc > 0) g_NC = nc;
+}
+
+/* KC of the complex double type: 192 by default; the reference's test builds give every
+ * type the same blocks (config/blocksize.h:11-21), so checks against them set it too.   */
+void ulm_oracle_set_blocks_z(int kc)
+{
+    if (kc > 0) g_KC_z = kc;
 }
 
 void ulm_oracle_get_blocks(int *mc, int *kc, int *nc)
@@ -449,4 +457,110 @@ void ulm_oracle_dsyrk(char uplo, char trans, int64_t n, int64_t k,
         syrk_d(!lower, n, k, alpha, A, 1, ldA, beta, C, 1, ldC);
     else
         syrk_d(lower, n, k, alpha, A, ldA, 1, beta, C, ldC, 1);
+}
+
+
+/* ---- zgemm --------------------------------------------------------------- */
+
+/* zgemm_ : interfaces/blas/F77/gemm.cc:381-510 -> ulmblas/level3/gemm.tcc:16-87 with
+ * T = std::complex<double>.  The complex type has no SSE kernel (ukernel/sse/ugemm.h:12-15
+ * covers double only), so every tile runs ukernel/ref/ugemm.tcc:10-67:
+ *   - K is cut into blocks of KC = 192 (config/blocksize.h:41), beta on the first block;
+ *   - AB += A*B per k with std::complex's product, i.e. four real products rounded
+ *     separately, one subtraction and one addition, then two additions into AB;
+ *   - C = 0 (beta == 0) or C *= beta, then C += AB (alpha == 1) or C += alpha*AB.
+ * Conjugation happens while packing (pack/gepack.tcc:21-33,84-96): op(A), op(B) are
+ * conjugated copies, which the dense split below reproduces by negating the imaginary
+ * plane.  Matrices are interleaved (re, im) pairs; leading dimensions count complex
+ * elements.                                                                          */
+static int is_conj(char c)
+{
+    c = (char)toupper((unsigned char)c);
+    return c == 'C' || c == 'R';
+}
+
+static void densify_z(int64_t rows, int64_t cols, const double *X, int64_t ir, int64_t ic,
+                      int conj, double **re_out, double **im_out)
+{
+    double *re = (double *)malloc(sizeof(double) * (size_t)(rows * cols + 1));
+    double *im = (double *)malloc(sizeof(double) * (size_t)(rows * cols + 1));
+    for (int64_t j = 0; j < cols; ++j)
+        for (int64_t i = 0; i < rows; ++i) {
+            const double *x = &X[2 * (i * ir + j * ic)];
+            re[i + j * rows] = x[0];
+            im[i + j * rows] = conj ? -x[1] : x[1];
+        }
+    *re_out = re;
+    *im_out = im;
+}
+
+void ulm_oracle_zgemm(char transA, char transB, int64_t m, int64_t n, int64_t k,
+                      const double *alpha, const double *A, int64_t ldA,
+                      const double *B, int64_t ldB,
+                      const double *beta, double *C, int64_t ldC)
+{
+    const int tA = is_trans(transA), tB = is_trans(transB);
+    const double ar = alpha[0], ai = alpha[1];
+    if (m <= 0 || n <= 0) return;
+    if ((ar == 0.0 && ai == 0.0) || k == 0) {            /* gemm.tcc:52-55 -> gescal */
+        const double br = beta[0], bi = beta[1];
+        if (br == 1.0 && bi == 0.0) return;
+        for (int64_t j = 0; j < n; ++j)
+            for (int64_t i = 0; i < m; ++i) {
+                double *c = &C[2 * (i + j * ldC)];
+                if (br == 0.0 && bi == 0.0) { c[0] = 0.0; c[1] = 0.0; }
+                else {
+                    const double cr = c[0], ci = c[1];
+                    c[0] = cr * br - ci * bi;
+                    c[1] = cr * bi + ci * br;
+                }
+            }
+        return;
+    }
+    double *Ar, *Ai, *Br, *Bi;
+    densify_z(m, k, A, tA ? ldA : 1, tA ? 1 : ldA, is_conj(transA), &Ar, &Ai);
+    densify_z(k, n, B, tB ? ldB : 1, tB ? 1 : ldB, is_conj(transB), &Br, &Bi);
+    double abr[STRIP], abi[STRIP];
+    const int64_t KC = g_KC_z;
+    const int alpha_one = (ar == 1.0 && ai == 0.0);
+    for (int64_t l0 = 0; l0 < k; l0 += KC) {
+        const int64_t kc = min64(KC, k - l0);
+        const int first = (l0 == 0);
+        const double br = first ? beta[0] : 1.0, bi = first ? beta[1] : 0.0;
+        for (int64_t j = 0; j < n; ++j) {
+            for (int64_t i0 = 0; i0 < m; i0 += STRIP) {
+                const int64_t len = min64(STRIP, m - i0);
+                for (int64_t i = 0; i < len; ++i) { abr[i] = 0.0; abi[i] = 0.0; }
+                for (int64_t l = 0; l < kc; ++l) {
+                    const double xr = Br[l0 + l + j * k], xi = Bi[l0 + l + j * k];
+                    const double *pr = Ar + i0 + (l0 + l) * m, *pi = Ai + i0 + (l0 + l) * m;
+#pragma omp simd
+                    for (int64_t i = 0; i < len; ++i) {
+                        const double t1 = pr[i] * xr, t2 = pi[i] * xi;
+                        const double t3 = pr[i] * xi, t4 = pi[i] * xr;
+                        abr[i] = abr[i] + (t1 - t2);
+                        abi[i] = abi[i] + (t3 + t4);
+                    }
+                }
+                for (int64_t i = 0; i < len; ++i) {
+                    double *c = &C[2 * ((i0 + i) + j * ldC)];
+                    double cr, ci;
+                    if (br == 0.0 && bi == 0.0) { cr = 0.0; ci = 0.0; }
+                    else {
+                        const double c0 = c[0], c1 = c[1];
+                        cr = c0 * br - c1 * bi;
+                        ci = c0 * bi + c1 * br;
+                    }
+                    double tr = abr[i], ti = abi[i];
+                    if (!alpha_one) {
+                        tr = ar * abr[i] - ai * abi[i];
+                        ti = ar * abi[i] + ai * abr[i];
+                    }
+                    c[0] = cr + tr;
+                    c[1] = ci + ti;
+                }
+            }
+        }
+    }
+    free(Ar); free(Ai); free(Br); free(Bi);
 }

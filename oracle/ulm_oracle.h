@@ -28,6 +28,8 @@ extern "C" {
  * 8/12/12 (test/F77/config/make.testcase01.inc); so can the oracle.       */
 void ulm_oracle_set_blocks(int mc, int kc, int nc);
 void ulm_oracle_get_blocks(int *mc, int *kc, int *nc);
+/* KC of std::complex<double> (192, blocksize.h:41; test builds: the common KC) */
+void ulm_oracle_set_blocks_z(int kc);
 
 /* dgemm_ : interfaces/blas/F77/gemm.cc:132-249 -> ulmblas/level3/gemm.tcc:16-87 */
 void ulm_oracle_dgemm(char transA, char transB, int64_t m, int64_t n, int64_t k,
@@ -42,6 +44,14 @@ void ulm_oracle_sgemm(char transA, char transB, int64_t m, int64_t n, int64_t k,
                       float alpha, const float *A, int64_t ldA,
                       const float *B, int64_t ldB,
                       float beta, float *C, int64_t ldC);
+
+/* zgemm_ : interfaces/blas/F77/gemm.cc:381-510.  Interleaved (re, im) doubles, leading
+ * dimensions in complex elements, alpha and beta as {re, im}; trans characters N, T,
+ * C (conjugate transpose) and R (conjugate, no transpose).                          */
+void ulm_oracle_zgemm(char transA, char transB, int64_t m, int64_t n, int64_t k,
+                      const double *alpha, const double *A, int64_t ldA,
+                      const double *B, int64_t ldB,
+                      const double *beta, double *C, int64_t ldC);
 
 /* dtrsm_ : interfaces/blas/F77/trsm.cc:121-228 -> ulmblas/level3/trlsm.tcc,
  * trusm.tcc.  All side/uplo/trans/diag combinations.                        */

@@ -114,5 +114,50 @@ def main():
           sum(int(d["nan_replaced"]) for d in fx.values()), "NaN entries replaced")
 
 
+def main_z():
+    """zgemm_ cases into their own file (seeds continue from a fixed base, independent of main())."""
+    sse, plain = oracle.Ref(""), oracle.Ref("plain")
+    _seed[0] = 9000
+    fx = {}
+    cases = [((5, 7, 3), "N", "N"), ((5, 7, 3), "C", "R"), ((33, 17, 401), "N", "N"), ((33, 17, 401), "T", "N"),
+             ((33, 17, 401), "N", "C"), ((33, 17, 401), "C", "T"), ((33, 17, 401), "R", "N"),
+             ((200, 9, 190), "C", "N"), ((200, 9, 190), "N", "T"), ((9, 200, 30), "T", "R")]
+    scal = [(1.0 + 0.0j, 0.0j), (0.7 - 0.3j, 1.3 + 0.2j)]
+    for idx, (((m, n, k), ta, tb), (al, be)) in enumerate(itertools.product(cases, scal)):
+        ra, ca = (k, m) if ta in "TC" else (m, k)
+        rb, cb = (n, k) if tb in "TC" else (k, n)
+        seeds = []
+        def zmat(r, c, ld):
+            re, _, s1 = mat(None, r, c, r)
+            im, _, s2 = mat(None, r, c, r)
+            seeds.append((s1, s2))
+            base = np.full((ld, c), -1e10 - 1e10j, dtype=np.complex128, order="F")
+            base[:r, :] = re + 1j * im
+            return base[:r, :], base
+        A, _ = zmat(ra, ca, ra + 3)
+        B, _ = zmat(rb, cb, rb + 1)
+        C0, Cb = zmat(m, n, m + 2)
+        c1, c2 = Cb.copy(order="F"), Cb.copy(order="F")
+        sse.zgemm(ta, tb, m, n, k, al, A, B, be, c1[:m, :n], lda=ra + 3, ldb=rb + 1, ldc=m + 2)
+        plain_kc = 192     # the portable-kernel build uses KC = 384 for every type: only k <= 384 agree in general
+        plain.zgemm(ta, tb, m, n, k, al, A, B, be, c2[:m, :n], lda=ra + 3, ldb=rb + 1, ldc=m + 2)
+        assert np.isfinite(c1.real).all() and np.isfinite(c1.imag).all()
+        if k <= plain_kc:
+            assert np.array_equal(c1.real, c2.real) and np.array_equal(c1.imag, c2.imag)
+        assert np.array_equal(c1[m:, :].real, Cb[m:, :].real), "padding rows written"
+        fx[f"zgemm_{idx}"] = dict(kind="zgemm", ta=ta, tb=tb, m=m, n=n, k=k, alpha_re=al.real, alpha_im=al.imag,
+                                  beta_re=be.real, beta_im=be.imag, seedA=seeds[0], seedB=seeds[1], seedC=seeds[2],
+                                  C_re=c1[:m, :n].real, C_im=c1[:m, :n].imag)
+    flat = {}
+    for name, d in fx.items():
+        for key, val in d.items():
+            flat[f"{name}/{key}"] = np.asarray(val)
+    path = os.path.join(OUT, "ulmblas_zgemm.npz")
+    np.savez_compressed(path, **flat)
+    print(path, os.path.getsize(path) // 1024, "KiB,", len(fx), "cases")
+
+
 if __name__ == "__main__":
-    main()
+    if "--zgemm-only" not in sys.argv:
+        main()
+    main_z()

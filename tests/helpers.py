@@ -90,9 +90,9 @@ def repair_nonfinite(out_ref, out_port):
 
 # --------------------------------------------------------------------------- golden fixtures
 
-def load_golden():
-    """tests/golden/ulmblas_level3.npz -> {case name: {field: value}} (made by make_golden.py)."""
-    z = np.load(os.path.join(ROOT, "tests", "golden", "ulmblas_level3.npz"))
+def load_golden(name="ulmblas_level3.npz"):
+    """tests/golden/<name> -> {case name: {field: value}} (made by make_golden.py)."""
+    z = np.load(os.path.join(ROOT, "tests", "golden", name))
     cases = {}
     for key in z.files:
         name, field = key.split("/")
@@ -110,6 +110,14 @@ def golden_inputs(c):
         A = det_uniform(c["seedA"], m if c["ta"] == "N" else k, k if c["ta"] == "N" else m, dt)
         B = det_uniform(c["seedB"], k if c["tb"] == "N" else n, n if c["tb"] == "N" else k, dt)
         return A, B, det_uniform(c["seedC"], m, n, dt)
+    if kind == "zgemm":
+        m, n, k = c["m"], c["n"], c["k"]
+        ra, ca = (k, m) if c["ta"] in "TC" else (m, k)
+        rb, cb = (n, k) if c["tb"] in "TC" else (k, n)
+
+        def z(seeds, r, cc):
+            return np.asfortranarray(det_uniform(int(seeds[0]), r, cc) + 1j * det_uniform(int(seeds[1]), r, cc))
+        return z(c["seedA"], ra, ca), z(c["seedB"], rb, cb), z(c["seedC"], m, n)
     if kind == "dsyrk":
         n, k = c["n"], c["k"]
         A = det_uniform(c["seedA"], n if c["trans"] == "N" else k, k if c["trans"] == "N" else n)

@@ -29,7 +29,8 @@ def test_library_exports_every_declared_symbol(ulm):
     funcs, data = declared_symbols()
     assert {"dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "xerbla_", "cblas_dgemm", "cblas_sgemm",
             "cblas_dtrsm", "cblas_dsyrk", "cblas_xerbla", "ulmblas_dgemm", "ulmb200_dgemm",
-            "ulmb200_sgemm", "ulmb200_dtrsm", "ulmb200_dsyrk"} <= set(funcs)
+            "ulmb200_sgemm", "ulmb200_dtrsm", "ulmb200_dsyrk", "zgemm_", "cblas_zgemm", "ulmblas_zgemm",
+            "ulmb200_zgemm"} <= set(funcs)
     for name in funcs:
         assert hasattr(ulm.lib, name), f"{name} is declared in include/ulmblas_b200.h but not exported"
     for name in data:
@@ -53,7 +54,7 @@ sys.path.insert(0, %(root)r)
 hook = C.CDLL(%(hook)r, mode=C.RTLD_GLOBAL)
 import ulmblas_b200.api as u
 import numpy as np
-A = np.zeros((8, 8), order="F"); out = []
+A = np.zeros((8, 8), order="F"); Z = np.zeros((8, 8), dtype=np.complex128, order="F"); out = []
 def rec():
     r = (C.c_int.in_dll(hook, "hook_info").value, C.c_char_p(C.addressof(C.c_char.in_dll(hook, "hook_name"))).value.decode(), u.last_status())
     C.c_int.in_dll(hook, "hook_info").value = 0
@@ -62,6 +63,7 @@ for args in %(gemm)r:
     ta, tb, m, n, k, lda, ldb, ldc = args
     u.dgemm(ta, tb, m, n, k, 1.0, A, A, 0.0, A, lda=lda, ldb=ldb, ldc=ldc); out.append(("dgemm",) + rec())
     u.sgemm(ta, tb, m, n, k, 1.0, A, A, 0.0, A, lda=lda, ldb=ldb, ldc=ldc); out.append(("sgemm",) + rec())
+    u.zgemm(ta, tb, m, n, k, 1.0, Z, Z, 0.0, Z, lda=lda, ldb=ldb, ldc=ldc); out.append(("zgemm",) + rec())
 for args in %(trsm)r:
     s, ul, t, d, m, n, lda, ldb = args
     u.dtrsm(s, ul, t, d, m, n, 1.0, A, A, lda=lda, ldb=ldb); out.append(("dtrsm",) + rec())
@@ -106,7 +108,7 @@ def test_bad_arguments_reach_a_caller_supplied_xerbla(ulm, tmp_path):
     it = iter(got)
     for a in GEMM_CASES:
         want = P.gemm_info(*a)
-        for routine, nm in (("dgemm", "DGEMM "), ("sgemm", "SGEMM ")):
+        for routine, nm in (("dgemm", "DGEMM "), ("sgemm", "SGEMM "), ("zgemm", "ZGEMM ")):
             r_, info, name, status = next(it)
             assert (r_, info, name, status) == (routine, want, nm, ulm.BAD_ARGUMENT), (a, info, name)
     for a in TRSM_CASES:

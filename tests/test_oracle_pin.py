@@ -170,3 +170,51 @@ def test_port_argument_checks_follow_the_reference_order():
     assert [P.syrk_info(*a) for a in [("X", "N", 1, 1, 1, 1), ("U", "X", 1, 1, 1, 1), ("U", "N", -1, 1, 1, 1),
                                       ("U", "N", 1, -1, 1, 1), ("U", "N", 3, 1, 2, 3), ("U", "T", 3, 5, 4, 3),
                                       ("U", "N", 3, 1, 3, 2)]] == [1, 2, 3, 4, 7, 7, 10]
+
+
+# ---------------------------------------------------------------------------
+# complex double GEMM
+# ---------------------------------------------------------------------------
+def _same_z(a, b):
+    return np.array_equal(a.real, b.real) and np.array_equal(a.imag, b.imag)
+
+
+def test_port_reproduces_reference_golden_zgemm():
+    """Outputs the compiled reference's zgemm_ produced (tests/golden/ulmblas_zgemm.npz), bit for bit."""
+    P = port()
+    P.set_blocks()
+    cases = load_golden("ulmblas_zgemm.npz")
+    assert len(cases) == 20
+    for name, c in cases.items():
+        A, B, C0 = golden_inputs(c)
+        got = C0.copy(order="F")
+        P.zgemm(c["ta"], c["tb"], c["m"], c["n"], c["k"], complex(c["alpha_re"], c["alpha_im"]), A, B,
+                complex(c["beta_re"], c["beta_im"]), got)
+        want = c["C_re"] + 1j * c["C_im"]
+        assert _same_z(got, want), name
+
+
+@needs_ref
+@pytest.mark.parametrize("variant,blocks", [("", (384, 384, 4096, 192)), ("plain", (384, 384, 4096, 384)),
+                                            ("tiny", (8, 12, 12, 12))])
+def test_port_equals_compiled_reference_zgemm(variant, blocks):
+    R, P = ref(variant), port()
+    P.set_blocks(*blocks)
+    try:
+        seed = 7000
+        for (m, n, k) in [(1, 1, 1), (5, 7, 3), (33, 21, 50), (70, 45, 401)]:
+            for ta, tb in itertools.product("NTCR", "NTCR"):
+                for al, be in [(1 + 0j, 0j), (0.7 - 0.3j, 1.3 + 0.2j)]:
+                    seed += 6
+                    ra, ca = (k, m) if ta in "TC" else (m, k)
+                    rb, cb = (n, k) if tb in "TC" else (k, n)
+                    A = np.asfortranarray(det_uniform(seed, ra + 2, ca) + 1j * det_uniform(seed + 1, ra + 2, ca))
+                    B = np.asfortranarray(det_uniform(seed + 2, rb + 1, cb) + 1j * det_uniform(seed + 3, rb + 1, cb))
+                    C0 = np.asfortranarray(det_uniform(seed + 4, m + 3, n) + 1j * det_uniform(seed + 5, m + 3, n))
+                    c1, c2 = C0.copy(order="F"), C0.copy(order="F")
+                    R.zgemm(ta, tb, m, n, k, al, A, B, be, c1, lda=ra + 2, ldb=rb + 1, ldc=m + 3)
+                    P.zgemm(ta, tb, m, n, k, al, A, B, be, c2, lda=ra + 2, ldb=rb + 1, ldc=m + 3)
+                    assert _same_z(c1, c2), (variant, m, n, k, ta, tb, al, be)
+                    assert _same_z(c2[m:, :], C0[m:, :]), "padding rows written"
+    finally:
+        P.set_blocks()

@@ -88,6 +88,11 @@ lib.cblas_dsyr2k.argtypes = [_int, _int, _int, _int, _int, _dbl, _vp, _int, _vp,
 for _name in ("cblas_dsymm", "cblas_dtrmm", "cblas_dsyr2k"):
     getattr(lib, _name).restype = None
 lib.cblas_dsyrk.argtypes = [_int, _int, _int, _int, _int, _dbl, _vp, _int, _dbl, _vp, _int]
+lib.ulmb200_zgemm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64]
+lib.cblas_zgemm.argtypes = [_int, _int, _int, _int, _int, _int, _vp, _vp, _int, _vp, _int, _vp, _vp, _int]
+lib.ulmblas_zgemm.argtypes = [_int, _int, _int, _int, _int, _vp, _vp, _int, _vp, _int, _vp, _vp, _int]
+for _name in ("zgemm_", "cblas_zgemm", "ulmblas_zgemm"):
+    getattr(lib, _name).restype = None
 
 CblasRowMajor, CblasColMajor = 101, 102
 CblasNoTrans, CblasTrans, CblasConjTrans, AtlasConj = 111, 112, 113, 114
@@ -146,6 +151,29 @@ def dgemm(transA, transB, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ld
                _p(A), _ri(lda or _ld(A)), _p(B), _ri(ldb or _ld(B)), C.byref(_dbl(beta)), _p(Cm),
                _ri(ldc or _ld(Cm)))
     return last_status()
+
+
+def _z2(z):
+    z = complex(z)
+    return (_dbl * 2)(z.real, z.imag)
+
+
+def zgemm(transA, transB, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):
+    """C <- alpha*op(A)*op(B) + beta*C through ``zgemm_`` (complex128 arrays; trans N, T, C or R)."""
+    lib.zgemm_(_cp(_c(transA)), _cp(_c(transB)), _ri(m), _ri(n), _ri(k), _z2(alpha),
+               _p(A), _ri(lda or _ld(A)), _p(B), _ri(ldb or _ld(B)), _z2(beta), _p(Cm),
+               _ri(ldc or _ld(Cm)))
+    return last_status()
+
+
+def cblas_zgemm(order, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, Cm, ldc):
+    lib.cblas_zgemm(order, transA, transB, m, n, k, _z2(alpha), _p(A), lda, _p(B), ldb, _z2(beta), _p(Cm), ldc)
+    return last_status()
+
+
+def dev_zgemm(transA, conjA, transB, conjB, m, n, k, alpha, dA, lda, dB, ldb, beta, dC, ldc, stream=0):
+    _check(lib.ulmb200_zgemm(stream, int(transA), int(conjA), int(transB), int(conjB), m, n, k, _z2(alpha),
+                             dA, lda, dB, ldb, _z2(beta), dC, ldc), "ulmb200_zgemm")
 
 
 def sgemm(transA, transB, m, n, k, alpha, A, B, beta, Cm, lda=None, ldb=None, ldc=None):

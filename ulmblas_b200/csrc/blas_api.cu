@@ -37,6 +37,9 @@ int ssyrk_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, fl
 int strsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n, float alpha,
                  const float *A, int64_t lda, float *B, int64_t ldb);
 int dlaswp_pairs_device(cudaStream_t st, double *A, int64_t lda, int64_t ncols, const int *d_pairs, int npairs);
+int zgemm_device(cudaStream_t st, int transA, int conjA, int transB, int conjB, int64_t m, int64_t n,
+                 int64_t k, const double *alpha, const double *A, int64_t lda, const double *B,
+                 int64_t ldb, const double *beta, double *C, int64_t ldc);
 int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, double alpha, const double *A,
                  int64_t lda, const double *B, int64_t ldb, double beta, double *C, int64_t ldc);
 int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, double alpha,
@@ -437,9 +440,44 @@ static int dsyr2k_any(int lower, int trans, int64_t n, int64_t k, double alpha, 
     return set_status(st != ULMB200_OK ? st : fin);
 }
 
+// Complex double GEMM with host or device operands (interleaved re/im, ld in complex elements).
+static int zgemm_any(int transA, int conjA, int transB, int conjB, int64_t m, int64_t n, int64_t k,
+                     const double *alpha, const double *A, int64_t lda, const double *B, int64_t ldb,
+                     const double *beta, double *C, int64_t ldc)
+{
+    ULMB_SERIALISE;
+    if (m == 0 || n == 0) return set_status(ULMB200_OK);
+    if (int s0 = ensure_device()) return set_status(s0);
+    Streams *s = streams();
+    if (!s) return set_status(ULMB200_CUDA_ERROR);
+    const bool scale_only = (alpha[0] == 0.0 && alpha[1] == 0.0) || k == 0;
+    const bool beta_zero = beta[0] == 0.0 && beta[1] == 0.0;
+    StagedT<double2> a, b, c;
+    int st = ULMB200_OK;
+    if (!scale_only) {
+        st = stage_in(a, reinterpret_cast<const double2 *>(A), lda, transA ? k : m, transA ? m : k, 0, true, s->run);
+        if (st == ULMB200_OK)
+            st = stage_in(b, reinterpret_cast<const double2 *>(B), ldb, transB ? n : k, transB ? k : n, 1, true, s->run);
+    } else {
+        a.dev = nullptr; a.ldd = std::max<int64_t>(1, transA ? k : m);
+        b.dev = nullptr; b.ldd = std::max<int64_t>(1, transB ? n : k);
+    }
+    if (st == ULMB200_OK)
+        st = stage_in(c, reinterpret_cast<const double2 *>(C), ldc, m, n, 2, !beta_zero, s->run);
+    if (st == ULMB200_OK)
+        st = zgemm_device(s->run, transA, conjA, transB, conjB, m, n, k, alpha,
+                          reinterpret_cast<const double *>(a.dev), a.ldd,
+                          reinterpret_cast<const double *>(b.dev), b.ldd, beta,
+                          reinterpret_cast<double *>(c.dev), c.ldd);
+    if (st == ULMB200_OK) st = stage_out(c, s->run);
+    const int fin = finish(s);
+    return set_status(st != ULMB200_OK ? st : fin);
+}
+
 // ---- argument decoding shared by the shims ---------------------------------
 static inline int up(const char *c) { return std::toupper((unsigned char)*c); }
 static inline bool is_trans(const char *c) { int u = up(c); return u == 'T' || u == 'C'; }
+static inline bool is_conj(const char *c) { int u = up(c); return u == 'C' || u == 'R'; }
 static inline bool valid_trans(const char *c) { int u = up(c); return u == 'N' || u == 'T' || u == 'C' || u == 'R'; }
 
 static int gemm_info(const char *ta, const char *tb, int m, int n, int k, int lda, int ldb, int ldc)
@@ -492,6 +530,21 @@ void dgemm_(const char *transA, const char *transB, const int *m, const int *n, 
         return;
     }
     dgemm_any(is_trans(transA), is_trans(transB), *m, *n, *k, *alpha, A, *ldA, B, *ldB, *beta, C, *ldC);
+}
+
+// interfaces/blas/F77/gemm.cc:381-510.  'C' = conjugate transpose, 'R' = conjugate only.
+void zgemm_(const char *transA, const char *transB, const int *m, const int *n, const int *k,
+            const double *alpha, const double *A, const int *ldA, const double *B, const int *ldB,
+            const double *beta, double *C, const int *ldC)
+{
+    int info = gemm_info(transA, transB, *m, *n, *k, *ldA, *ldB, *ldC);
+    if (info != 0) {
+        xerbla_("ZGEMM ", &info);
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    zgemm_any(is_trans(transA), is_conj(transA), is_trans(transB), is_conj(transB), *m, *n, *k, alpha, A,
+              *ldA, B, *ldB, beta, C, *ldC);
 }
 
 void sgemm_(const char *transA, const char *transB, const int *m, const int *n, const int *k,
@@ -683,6 +736,16 @@ void ulmblas_sgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB, int
     sgemm_any(!c_notrans(transA), !c_notrans(transB), m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
 }
 
+// interfaces/blas/C/gemm.cc:219-292
+void ulmblas_zgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB, int m, int n, int k,
+                   const double *alpha, const double *A, int ldA, const double *B, int ldB,
+                   const double *beta, double *C, int ldC)
+{
+    const bool conjA = (transA == AtlasConj || transA == CblasConjTrans);
+    const bool conjB = (transB == AtlasConj || transB == CblasConjTrans);
+    zgemm_any(!c_notrans(transA), conjA, !c_notrans(transB), conjB, m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
 // first-bad-argument code of CBLAS(dgemm)/CBLAS(sgemm), interfaces/blas/C/gemm.cc:426-466
 static int cblas_gemm_info(int order, int transA, int transB, int m, int n, int k, int ldA, int ldB, int ldC)
 {
@@ -728,6 +791,21 @@ void cblas_dgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS
     // row-major C = A*B is column-major C^T = B^T * A^T: swap the operands (gemm.cc:478-484)
     if (order == CblasColMajor) ulmblas_dgemm(transA, transB, m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
     else                        ulmblas_dgemm(transB, transA, n, m, k, alpha, B, ldB, A, ldA, beta, C, ldC);
+}
+
+// interfaces/blas/C/gemm.cc:584-677 (same codes and the same operand swap as the real types)
+void cblas_zgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
+                 int m, int n, int k, const double *alpha, const double *A, int ldA, const double *B,
+                 int ldB, const double *beta, double *C, int ldC)
+{
+    int info = cblas_gemm_info(order, transA, transB, m, n, k, ldA, ldB, ldC);
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_zgemm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) ulmblas_zgemm(transA, transB, m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC);
+    else                        ulmblas_zgemm(transB, transA, n, m, k, alpha, B, ldB, A, ldA, beta, C, ldC);
 }
 
 void cblas_sgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,

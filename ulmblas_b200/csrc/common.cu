@@ -37,8 +37,8 @@ struct DeviceState {
     int checked = 0;          // 0 unknown, 1 usable, -1 not usable
     int sms = 0;
     int *err_word = nullptr;
-    void *scratch[12] = {};
-    size_t scratch_bytes[12] = {};
+    void *scratch[16] = {};
+    size_t scratch_bytes[16] = {};
 };
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_mu;

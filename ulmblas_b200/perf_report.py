@@ -6,7 +6,7 @@
         -m ulmblas_b200.perf_report --sharded-trsm 8192  # DTRSM LLNN split over N GPUs
 
 CUDA events on the launching stream, 2 warm-ups, median of 5 (3 for the largest cases).  Rates
-are algorithmic flops / time: GEMM 2mnk, SYRK n(n+1)k, SYR2K 2n(n+1)k, SYMM 2m^2n, TRSM/TRMM m^2n
+are algorithmic flops / time: GEMM 2mnk (complex 8mnk), SYRK n(n+1)k, SYR2K 2n(n+1)k, SYMM 2m^2n, TRSM/TRMM m^2n
 (left), LU 2n^3/3.
 """
 import statistics
@@ -130,6 +130,13 @@ def main():
     A = _buf(3072, k, torch.float64, 11, 0); B = _buf(640, n, torch.float64, 11, 1); C = _buf(3008, n, torch.float64, 11, 2)
     ms = _time(lambda: u.dev_dgemm(0, 0, m, n, k, -0.7, A.data_ptr(), 3072, B.data_ptr(), 640, 1.3, C.data_ptr(), 3008, stream=s), 5)
     add("dgemm NN 3001x2047x513 (padded ld)", 2.0 * m * n * k, ms, "fp64 dmma")
+    zs = 2048 if quick else 4096
+    A = _buf(2 * zs, zs, torch.float64, 13, 0); B = _buf(2 * zs, zs, torch.float64, 13, 1); C = _buf(2 * zs, zs, torch.float64, 13, 2)
+    for ta, ca, nm in ((0, 0, "NN"), (1, 1, "CN")):
+        ms = _time(lambda: u.dev_zgemm(ta, ca, 0, 0, zs, zs, zs, 0.7 - 0.3j, A.data_ptr(), zs, B.data_ptr(), zs, 1.3 + 0.2j,
+                                       C.data_ptr(), zs, stream=s), 5)
+        add(f"zgemm {nm} {zs}^3 (8mnk flops)", 8.0 * zs ** 3, ms, "fp64 dmma")
+    del A, B, C
     for mode, name in ((0, "fp32"), (1, "3xtf32")):
         for sz in (4096,) if quick else (4096, 8192):
             A = _buf(sz, sz, torch.float32, 7, 0); B = _buf(sz, sz, torch.float32, 7, 1); C = _buf(sz, sz, torch.float32, 7, 2)
