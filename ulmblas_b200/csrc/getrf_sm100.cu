@@ -2,12 +2,12 @@
 // reference's trlsm + gemm (ulmblas/lapack/getrf.tcc:30-73, getf2.tcc:15-62,
 // laswp.tcc), kept right-looking with the reference's loop structure:
 //
-//   for each 128-column panel:   getf2 on the panel          -> getf2_panel_kernel
-//                                 row swaps left and right    -> laswp_kernel
+//   for each 128-column panel:   getf2 on the panel          -> getf2_cluster_kernel (+ lu_rank_update_kernel)
+//                                 row swaps left and right    -> lu_perm_list_kernel + laswp_gather_kernel
 //                                 A12 <- L11^-1 A12           -> device TRSM (unit lower)
 //                                 A22 <- A22 - A21 A12        -> device DGEMM
 //
-// The panel kernel is one cooperative launch: the CTAs split the panel's rows,
+// Panels too tall for the cluster kernel's shared memory fall back to one cooperative launch: the CTAs split the panel's rows,
 // and per column they (1) propose their largest entry, (2) after a grid-wide
 // barrier agree on the pivot (first largest, as iamax does) while CTA 0 swaps the
 // two rows inside the panel, (3) after a second barrier scale their part of the
@@ -19,6 +19,7 @@
 
 #include <cooperative_groups.h>
 #include <float.h>
+#include <limits.h>
 
 namespace cg = cooperative_groups;
 
@@ -74,6 +75,18 @@ __device__ __forceinline__ void lu_block_argmax(double &v, int64_t &i, double *s
     __syncthreads();
     v = sv[32]; i = si[32];
     __syncthreads();
+}
+
+// Warp-wide "first largest": every lane leaves with the largest v and, among the lanes that hold
+// it, the smallest index.  Five exchange steps on the value and one hardware reduction on the index.
+__device__ __forceinline__ void lu_warp_argmax(double &v, int &i)
+{
+    double m = v;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmax(m, __shfl_xor_sync(0xffffffffu, m, off));
+    const int cand = (v == m) ? i : INT_MAX;
+    i = __reduce_min_sync(0xffffffffu, cand);
+    v = m;
 }
 
 __global__ void __launch_bounds__(kLuThreads) getf2_panel_kernel(PanelArgs a)
@@ -260,15 +273,342 @@ __global__ void __launch_bounds__(kLuThreads) getf2_panel_smem_kernel(PanelSmemA
     }
 }
 
-// Rows k1..k2-1 of `ncols` columns are exchanged with rows piv[k1..k2-1], in order (laswp.tcc).
-__global__ void laswp_kernel(double *A, int64_t lda, int64_t ncols, int64_t k1, int64_t k2, const int *piv)
+// ---------------------------------------------------------------------------
+// Panel factorisation inside one thread-block cluster.
+//
+// A grid-wide barrier costs 1.2 us on this part, a cluster barrier 0.2 us, and a CTA can write
+// straight into the shared memory of the other CTAs of its cluster.  So the 128-column panel is cut
+// into sub-panels of up to 32 columns, and one cluster of 16 CTAs factors a sub-panel entirely out
+// of shared memory: CTA b keeps rows [b R, (b+1) R) of the sub-panel, and per column
+//   1. finds its best pivot candidate,
+//   2. writes the candidate (value, row index) into EVERY CTA's shared memory and parks the
+//      candidate's row (and row c, if it owns it) in its own,
+//   3. after one cluster barrier each CTA picks the pivot from its own copy of the 16 candidates and
+//      reads the pivot row out of the winner's shared memory; the owners exchange the two rows, all
+//      scale and update their rows.
+// When the sub-panel is done the cluster writes it back, applies its row exchanges to the other
+// columns of the 128-column panel (as one gather, no chain of dependent swaps) and solves
+// U12 = L11^-1 A12 for the columns to the right, so that the only other launch per sub-panel is the
+// rank-w update of those columns (lu_rank_update_kernel).
+// Publication buffers alternate with the column parity: a CTA can be at most one column ahead.
+// ---------------------------------------------------------------------------
+constexpr int kClu = 16;           // CTAs per cluster (non-portable size, allowed explicitly)
+constexpr int kCluW = 32;          // widest sub-panel
+
+struct CluArgs {
+    double *A;            // top-left element of the 128-column panel (row j, column j of the matrix)
+    int64_t lda;
+    int64_t m;            // rows of the panel
+    int nb;               // columns of the panel
+    int c0;               // first column (= first row) of the sub-panel inside the panel
+    int w;                // columns of the sub-panel
+    int64_t row_off;      // j: added to pivot indices and info
+    int *piv;
+    int *info;
+    int ldS;              // pitch of the shared-memory slab (odd, >= rows per CTA)
+    int R;                // rows per CTA
+};
+
+__global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
 {
-    for (int64_t col = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; col < ncols;
-         col += (int64_t)gridDim.x * blockDim.x) {
-        double *c = A + col * lda;
-        for (int64_t i = k1; i < k2; ++i) {
-            const int64_t p = piv[i];
-            if (p != i) { const double tmp = c[i]; c[i] = c[p]; c[p] = tmp; }
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ double lu_smem[];
+    __shared__ double sv[kLuThreads / 32];
+    __shared__ double pub_val[2][kClu];
+    __shared__ int pub_idx[2][kClu];
+    __shared__ double pub_row[2][kCluW];         // my candidate's row, read by the others when it wins
+    __shared__ double pub_rowc[2][kCluW];        // row c, parked by its owner
+    __shared__ double s_row[kCluW];
+    __shared__ double s_pivv[kCluW];             // pivot values (0 = column skipped as singular)
+    __shared__ int s_wi[kLuThreads / 32];
+    __shared__ int s_piv[kCluW];                 // pivot of column c as a sub-panel row index
+    __shared__ int s_dst[2 * kCluW], s_src[2 * kCluW], s_cnt, s_info;
+    __shared__ double s_L11[kCluW * kCluW];
+    __shared__ double s_buf[2 * kCluW][8];
+
+    const int b = (int)cluster.block_rank(), t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int64_t ms = a.m - a.c0;                               // rows of the sub-panel
+    const int R = a.R, ldS = a.ldS, w = a.w;
+    const int64_t lo = (int64_t)b * R, hi = min(ms, lo + R);
+    const int nr = (int)max((int64_t)0, hi - lo);
+    double *S = lu_smem;                                        // S[cc*ldS + r]
+    double *Asub = a.A + a.c0 + (int64_t)a.c0 * a.lda;          // sub-panel element (0, 0)
+
+    for (int cc = 0; cc < w; ++cc)
+        for (int r = t; r < nr; r += kLuThreads) S[cc * ldS + r] = Asub[lo + r + (int64_t)cc * a.lda];
+    if (t == 0) s_info = 0;
+    __syncthreads();
+
+    const int ncol = (int)min((int64_t)w, ms);
+    const int msi = (int)ms;                    // the slab bound keeps the sub-panel below 2^31 rows
+    for (int c = 0; c < ncol; ++c) {
+        const int par = c & 1;
+        // (1) candidate among my rows >= c: per lane, per warp, then every warp combines the 8 warp
+        // results itself (one block barrier, no broadcast step)
+        double bv = -1.0;
+        int bi = msi;
+        for (int r = t; r < nr; r += kLuThreads) {
+            const int gr = (int)lo + r;
+            if (gr >= c) {
+                const double v = fabs(S[c * ldS + r]);
+                if (v > bv) { bv = v; bi = gr; }          // rows ascend: the first maximum stays
+            }
+        }
+        lu_warp_argmax(bv, bi);
+        if (lane == 0) { sv[warp] = bv; s_wi[warp] = bi; }
+        __syncthreads();
+        bv = lane < kLuThreads / 32 ? sv[lane] : -2.0;
+        bi = lane < kLuThreads / 32 ? s_wi[lane] : INT_MAX;
+        lu_warp_argmax(bv, bi);
+        // (2) publish the candidate into every CTA of the cluster
+        if (t < kClu) {
+            *cluster.map_shared_rank(&pub_val[par][b], t) = bv;
+            *cluster.map_shared_rank(&pub_idx[par][b], t) = bi;
+        }
+        // the candidate's row and (its owner) row c are parked in this CTA's own shared memory; whoever
+        // needs them after the barrier reads them from here
+        if (bi < msi && t < w) pub_row[par][t] = S[t * ldS + (bi - (int)lo)];
+        if (c >= lo && c < hi && t < w) pub_rowc[par][t] = S[t * ldS + (int)(c - lo)];
+        cluster.sync();
+
+        // (3) the pivot: first largest of the 16 candidates, found by every warp on its own
+        double pv = lane < kClu ? pub_val[par][lane] : -2.0;
+        int p = lane < kClu ? pub_idx[par][lane] : INT_MAX;
+        lu_warp_argmax(pv, p);
+        const bool singular = !(pv > 0.0);
+        if (singular) p = c;
+        // pivots and a zero-pivot report stay in shared memory until the sub-panel is done: a global
+        // store here would have to drain before every cluster barrier's release
+        if (t == 0) {
+            s_piv[c] = p;
+            if (singular && s_info == 0) s_info = c + 1;
+        }
+        if (!singular) {
+            const int wr = min(kClu - 1, p / R);            // CTA that owns row p
+            const int oc = min(kClu - 1, c / R);            // CTA that owns row c
+            if (t < w) {
+                const double prow = *cluster.map_shared_rank(&pub_row[par][t], wr);
+                s_row[t] = prow;
+                if (t == c) {
+                    s_pivv[c] = prow;                       // the pivot value, for the final scaling
+                }
+                if (p != c) {
+                    if (p >= lo && p < hi) S[t * ldS + (p - (int)lo)] = *cluster.map_shared_rank(&pub_rowc[par][t], oc);
+                    if (c >= lo && c < hi) S[t * ldS + (int)(c - lo)] = prow;
+                }
+            }
+        } else if (t == 0) {
+            s_pivv[c] = 0.0;                                // marks "column not scaled"
+        }
+        __syncthreads();
+        if (!singular && c + 1 < w) {
+            const double piv = s_row[c];
+            const bool recip = fabs(piv) >= DBL_MIN;
+            const double rp = 1.0 / piv;
+            // rank-1 update of my rows below c, a thread per row.  Column c itself keeps the unscaled
+            // entries until the write-back (later exchanges move them with their rows; the scaling
+            // commutes with that), so nothing here writes what another thread reads.
+            const int r_first = (int)max((int64_t)0, (int64_t)c + 1 - lo);
+            for (int r = r_first + t; r < nr; r += kLuThreads) {
+                const double x = S[c * ldS + r];
+                const double l = recip ? x * rp : x / piv;
+                for (int cc = c + 1; cc < w; ++cc) S[cc * ldS + r] -= l * s_row[cc];
+            }
+        }
+        __syncthreads();
+    }
+
+    // the multipliers: column c of every row below the diagonal, scaled now
+    for (int cc = 0; cc < ncol; ++cc) {
+        const double piv = s_pivv[cc];
+        if (piv == 0.0) continue;
+        const bool recip = fabs(piv) >= DBL_MIN;
+        const double rp = 1.0 / piv;
+        const int r_first = (int)max((int64_t)0, (int64_t)cc + 1 - lo);
+        for (int r = r_first + t; r < nr; r += kLuThreads) {
+            const double x = S[cc * ldS + r];
+            S[cc * ldS + r] = recip ? x * rp : x / piv;
+        }
+    }
+    __syncthreads();
+
+    // the factored sub-panel goes back, with its pivots (matrix row indices) and the first zero pivot
+    if (b == 0) {
+        if (t < ncol) a.piv[a.row_off + a.c0 + t] = (int)(s_piv[t] + a.row_off + a.c0);
+        if (t == 0 && s_info != 0) atomicCAS(a.info, 0, (int)(a.row_off + a.c0 + s_info));
+    }
+    for (int cc = 0; cc < w; ++cc)
+        for (int r = t; r < nr; r += kLuThreads) Asub[lo + r + (int64_t)cc * a.lda] = S[cc * ldS + r];
+    __threadfence();
+    cluster.sync();
+
+    // its row exchanges as (destination row <- source row) pairs: replay them on a sparse index map
+    int *idx = reinterpret_cast<int *>(lu_smem);                 // the slab is no longer needed
+    if (t < ncol) { idx[t] = t; }
+    __syncthreads();
+    if (t < ncol) idx[s_piv[t]] = s_piv[t];
+    __syncthreads();
+    if (t == 0) {
+        for (int c = 0; c < ncol; ++c) {
+            const int p = s_piv[c];
+            const int tmp = idx[c]; idx[c] = idx[p]; idx[p] = tmp;
+        }
+        s_cnt = 0;
+    }
+    __syncthreads();
+    if (t < 2 * ncol) {
+        const int r = t < ncol ? t : s_piv[t - ncol];
+        bool first = idx[r] != r;
+        for (int q = 0; q < t && first; ++q) first = (q < ncol ? q : s_piv[q - ncol]) != r;
+        if (first) { const int slot = atomicAdd(&s_cnt, 1); s_dst[slot] = r; s_src[slot] = idx[r]; }
+    }
+    __syncthreads();
+    const int cnt = s_cnt;
+
+    // my columns of the panel outside the sub-panel: exchange rows, then (right of it) U12
+    for (int e = t; e < ncol * ncol; e += kLuThreads) {
+        const int i = e % ncol, q = e / ncol;
+        s_L11[q * kCluW + i] = Asub[i + (int64_t)q * a.lda];
+    }
+    __syncthreads();
+    const int nother = a.nb - w;
+    for (int base = b * 8; base < nother; base += kClu * 8) {
+        // up to 8 columns per pass; oc counts the columns outside the sub-panel
+        const int ncs = min(8, nother - base);
+        for (int e = t; e < cnt * ncs; e += kLuThreads) {
+            const int q = e % cnt, k = e / cnt;
+            const int oc = base + k, col = oc < a.c0 ? oc : oc + w;
+            s_buf[q][k] = a.A[a.c0 + s_src[q] + (int64_t)col * a.lda];
+        }
+        __syncthreads();
+        for (int e = t; e < cnt * ncs; e += kLuThreads) {
+            const int q = e % cnt, k = e / cnt;
+            const int oc = base + k, col = oc < a.c0 ? oc : oc + w;
+            a.A[a.c0 + s_dst[q] + (int64_t)col * a.lda] = s_buf[q][k];
+        }
+        __threadfence_block();
+        __syncthreads();
+        // U12: one warp per column right of the sub-panel, lane i holds element i
+        if (warp < ncs) {
+            const int oc = base + warp, col = oc < a.c0 ? oc : oc + w;
+            if (col >= a.c0 + w) {
+                double *x = a.A + a.c0 + (int64_t)col * a.lda;
+                double u = lane < ncol ? x[lane] : 0.0;
+                for (int q = 0; q + 1 < ncol; ++q) {
+                    const double uq = __shfl_sync(0xffffffffu, u, q);
+                    if (lane > q && lane < ncol) u -= s_L11[q * kCluW + lane] * uq;
+                }
+                if (lane < ncol) x[lane] = u;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// A22 <- A22 - L21 U12 inside the 128-column panel after a sub-panel: rows below the sub-panel's
+// diagonal block, columns right of it.  64 rows per CTA; U12 (w x ncr) sits in shared memory.
+struct RankArgs {
+    double *A;            // top-left of the panel
+    int64_t lda;
+    int64_t m;            // rows of the panel
+    int c0, w, ncr;       // sub-panel offset and width, columns right of it
+};
+
+__global__ void __launch_bounds__(kLuThreads) lu_rank_update_kernel(RankArgs a)
+{
+    __shared__ double U[kCluW][128 + 1];
+    const int t = threadIdx.x;
+    const double *U12 = a.A + a.c0 + (int64_t)(a.c0 + a.w) * a.lda;
+    for (int e = t; e < a.w * a.ncr; e += kLuThreads) {
+        const int k = e % a.w, cc = e / a.w;
+        U[k][cc] = U12[k + (int64_t)cc * a.lda];
+    }
+    __syncthreads();
+    const int64_t r = (int64_t)a.c0 + a.w + (int64_t)blockIdx.x * 64 + (t & 63);
+    if (r >= a.m) return;
+    double l[kCluW];
+#pragma unroll
+    for (int k = 0; k < kCluW; ++k) l[k] = k < a.w ? a.A[r + (int64_t)(a.c0 + k) * a.lda] : 0.0;
+    for (int cc = t >> 6; cc < a.ncr; cc += 4) {
+        double *x = a.A + r + (int64_t)(a.c0 + a.w + cc) * a.lda;
+        double acc = *x;
+#pragma unroll
+        for (int k = 0; k < kCluW; ++k) acc -= l[k] * U[k][cc];
+        *x = acc;
+    }
+}
+
+// The nb row exchanges of a panel (row k1+i <-> row piv[k1+i], in order) as one simultaneous
+// assignment: list = { count, dst[256], src[256] } with "row dst takes the old contents of row
+// src".  Slots 0..nb-1 stand for rows k1..k1+nb-1, slot nb+q for pivot row q when it lies below
+// the panel's diagonal block and q is its first occurrence; one thread replays the exchanges on
+// the slot contents, which is the only sequential part.
+constexpr int kPermMax = 2 * kLuNB;
+
+__global__ void __launch_bounds__(kLuThreads) lu_perm_list_kernel(const int *piv, int64_t k1, int nb, int *list)
+{
+    __shared__ int s_p[kLuNB], s_slot[kLuNB], s_cont[kPermMax], s_valid[kPermMax], s_cnt;
+    const int t = threadIdx.x;
+    if (t < nb) s_p[t] = piv[k1 + t] - (int)k1;             // relative to the panel's first row
+    if (t < kPermMax) { s_cont[t] = t; s_valid[t] = t < nb; }
+    if (t == 0) s_cnt = 0;
+    __syncthreads();
+    if (t < nb) {
+        const int p = s_p[t];
+        int slot = p;
+        if (p >= nb) {
+            int fo = t;
+            for (int q = 0; q < t; ++q) if (s_p[q] == p) { fo = q; break; }
+            slot = nb + fo;
+            if (fo == t) s_valid[slot] = 1;
+        }
+        s_slot[t] = slot;
+    }
+    __syncthreads();
+    if (t == 0)
+        for (int i = 0; i < nb; ++i) {
+            const int sb = s_slot[i];
+            const int tmp = s_cont[i]; s_cont[i] = s_cont[sb]; s_cont[sb] = tmp;
+        }
+    __syncthreads();
+    if (t < kPermMax && s_valid[t] && s_cont[t] != t) {
+        const int k = atomicAdd(&s_cnt, 1);
+        const int src_slot = s_cont[t];
+        list[1 + k] = t < nb ? t : s_p[t - nb];
+        list[1 + kPermMax + k] = src_slot < nb ? src_slot : s_p[src_slot - nb];
+    }
+    __syncthreads();
+    if (t == 0) list[0] = s_cnt;
+}
+
+// Applies such a list to columns [0, skip_from) and [skip_from + skip_count, ...) of A (ncols
+// columns in all, rows relative to row0).  One warp per column: every lane first reads its
+// sources, then writes its destinations, so no chain of dependent exchanges remains.
+__global__ void __launch_bounds__(kLuThreads) laswp_gather_kernel(double *A, int64_t lda, int64_t ncols,
+                                                                  int64_t skip_from, int64_t skip_count,
+                                                                  int64_t row0, const int *list)
+{
+    __shared__ int s_dst[kPermMax], s_src[kPermMax];
+    const int t = threadIdx.x, lane = t & 31;
+    const int cnt = list[0];
+    if (t < cnt) { s_dst[t] = list[1 + t]; s_src[t] = list[1 + kPermMax + t]; }
+    __syncthreads();
+    if (cnt == 0) return;
+    const int64_t warps = (int64_t)gridDim.x * (kLuThreads / 32);
+    for (int64_t oc = (int64_t)blockIdx.x * (kLuThreads / 32) + (t >> 5); oc < ncols; oc += warps) {
+        const int64_t col = oc < skip_from ? oc : oc + skip_count;
+        double *x = A + row0 + col * lda;
+        double v[kPermMax / 32];
+#pragma unroll
+        for (int u = 0; u < kPermMax / 32; ++u) {
+            const int q = lane + 32 * u;
+            v[u] = q < cnt ? x[s_src[q]] : 0.0;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < kPermMax / 32; ++u) {
+            const int q = lane + 32 * u;
+            if (q < cnt) x[s_dst[q]] = v[u];
         }
     }
 }
@@ -297,17 +637,6 @@ int dlaswp_pairs_device(cudaStream_t st, double *A, int64_t lda, int64_t ncols, 
     return check_cuda(cudaGetLastError(), "laswp_pairs_kernel", __FILE__, __LINE__);
 }
 
-static void launch_laswp(cudaStream_t st, double *A, int64_t lda, int64_t ncols, int64_t k1, int64_t k2,
-                         const int *piv)
-{
-    if (ncols <= 0) return;
-    int64_t blocks = (ncols + 127) / 128;
-    const int64_t cap = (int64_t)sm_count() * 8;
-    if (blocks > cap) blocks = cap;
-    laswp_kernel<<<(int)blocks, 128, 0, st>>>(A, lda, ncols, k1, k2, piv);
-    count_launch();
-}
-
 int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda, int *d_piv, int *d_info)
 {
     if (m < 0 || n < 0 || lda < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
@@ -325,6 +654,31 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
         ULMB_CUDA(cudaFuncSetAttribute(getf2_panel_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)(sizeof(double) * kLuSlabRows * kLuNB)));
     }
+    static int64_t cluster_smem_max[kMaxDevices] = {};
+    if (cluster_smem_max[dev] == 0) {
+        // what one CTA of a 16-CTA cluster may take next to the kernel's static shared memory
+        cudaFuncAttributes fa;
+        int optin = 0;
+        ULMB_CUDA(cudaFuncGetAttributes(&fa, getf2_cluster_kernel));
+        ULMB_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        int64_t room = (int64_t)optin - (int64_t)fa.sharedSizeBytes - 1024;
+        cluster_smem_max[dev] = -1;
+        if (room > 16384 &&
+            cudaFuncSetAttribute(getf2_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+            cudaFuncSetAttribute(getf2_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)room) == cudaSuccess) {
+            // the launch is only used if the device can actually co-schedule such a cluster
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(kClu); cfg.blockDim = dim3(kLuThreads); cfg.dynamicSmemBytes = (size_t)room;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = kClu; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            int ncl = 0;
+            if (cudaOccupancyMaxActiveClusters(&ncl, getf2_cluster_kernel, &cfg) == cudaSuccess && ncl >= 1)
+                cluster_smem_max[dev] = room;
+        }
+        cudaGetLastError();
+    }
     // scratch: candidates (value, index) x 2 parities, candidate rows x 2 parities, row c x 2 parities
     const size_t nG = (size_t)max_ctas[dev];
     const size_t doubles = 2 * nG + 2 * nG * kLuNB + 2 * kLuNB + nG /* ints, 2 per double */;
@@ -334,6 +688,8 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
     double *rowc = cand_rows + 2 * nG * kLuNB;
     int *cand_idx = reinterpret_cast<int *>(rowc + 2 * kLuNB);
     constexpr size_t kSlabSmem = sizeof(double) * (size_t)kLuSlabRows * kLuNB;
+    int *perm_list = static_cast<int *>(device_scratch(13, sizeof(int) * (1 + 2 * kPermMax)));
+    if (!perm_list) return set_status(ULMB200_CUDA_ERROR);
 
     const int64_t mn = m < n ? m : n;
     for (int64_t j = 0; j < mn; j += kLuNB) {
@@ -341,6 +697,47 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
         PanelArgs a;
         a.A = A + j + j * lda; a.lda = lda; a.m = m - j; a.jb = jb; a.row_off = j;
         a.piv = d_piv; a.info = d_info; a.cand_val = cand_val; a.cand_idx = cand_idx;
+        // Preferred: sub-panels of up to 32 columns, each factored by one 16-CTA cluster out of shared
+        // memory.  The slab (rows/16 x width doubles per CTA) has to fit; narrower sub-panels for taller
+        // panels, the cooperative kernels below beyond that.
+        static const int use_cluster = [] { const char *e = getenv("ULMB200_LU_CLUSTER"); return e ? atoi(e) : 1; }();
+        int wsub = kCluW;
+        auto slab_bytes = [&](int64_t rows, int wcols) {
+            const int64_t R = (rows + kClu - 1) / kClu;
+            const int64_t ld = R | 1;
+            const int64_t slab = (int64_t)wcols * ld * 8, map = rows * 4 + 64;
+            return slab > map ? slab : map;
+        };
+        while (wsub > 8 && slab_bytes(a.m, wsub) > cluster_smem_max[dev]) wsub /= 2;
+        if (use_cluster && cluster_smem_max[dev] > 0 && slab_bytes(a.m, wsub) <= cluster_smem_max[dev]) {
+            for (int c0 = 0; c0 < jb && c0 < a.m; c0 += wsub) {
+                CluArgs q;
+                q.A = a.A; q.lda = lda; q.m = a.m; q.nb = jb; q.c0 = c0; q.w = (jb - c0) < wsub ? (jb - c0) : wsub;
+                q.row_off = j; q.piv = d_piv; q.info = d_info;
+                const int64_t rows = a.m - c0;
+                q.R = (int)((rows + kClu - 1) / kClu);
+                q.ldS = q.R | 1;
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(kClu); cfg.blockDim = dim3(kLuThreads);
+                cfg.dynamicSmemBytes = (size_t)slab_bytes(rows, q.w);
+                cfg.stream = st;
+                cudaLaunchAttribute at[1];
+                at[0].id = cudaLaunchAttributeClusterDimension;
+                at[0].val.clusterDim.x = kClu; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+                cfg.attrs = at; cfg.numAttrs = 1;
+                ULMB_CUDA(cudaLaunchKernelEx(&cfg, getf2_cluster_kernel, q));
+                count_launch();
+                const int ncr = jb - c0 - q.w;
+                if (ncr > 0 && c0 + q.w < a.m) {
+                    RankArgs r;
+                    r.A = a.A; r.lda = lda; r.m = a.m; r.c0 = c0; r.w = q.w; r.ncr = ncr;
+                    const int64_t below = a.m - c0 - q.w;
+                    lu_rank_update_kernel<<<(unsigned)((below + 63) / 64), kLuThreads, 0, st>>>(r);
+                    count_launch();
+                }
+            }
+            ULMB_CUDA(cudaGetLastError());
+        } else {
         // short panels live in shared memory (64..192 rows per CTA); taller ones work in global memory
         static const int rows_per_cta = [] { const char *e = getenv("ULMB200_LU_ROWS"); int v = e ? atoi(e) : 0;
                                              return (v >= 32 && v <= kLuSlabRows) ? v : 64; }();
@@ -363,10 +760,22 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                                                   dim3(kLuThreads), args, 0, st));
         }
         count_launch();
-        // the same exchanges on the columns left and right of the panel (getrf.tcc:50-57)
-        launch_laswp(st, A, lda, j, j, j + jb, d_piv);
+        }
+        // the same exchanges on the columns left and right of the panel (getrf.tcc:50-57), as one
+        // gather over both column ranges
+        {
+            const int64_t others = n - jb;
+            if (others > 0) {
+                lu_perm_list_kernel<<<1, kLuThreads, 0, st>>>(d_piv, j, jb, perm_list);
+                count_launch();
+                int64_t blocks = (others + 7) / 8;
+                const int64_t cap = (int64_t)sm_count() * 8;
+                if (blocks > cap) blocks = cap;
+                laswp_gather_kernel<<<(unsigned)blocks, kLuThreads, 0, st>>>(A, lda, others, j, jb, j, perm_list);
+                count_launch();
+            }
+        }
         if (j + jb < n) {
-            launch_laswp(st, A + (j + jb) * lda, lda, n - j - jb, j, j + jb, d_piv);
             int s = dtrsm_device(st, 0, 1, 0, 1, jb, n - j - jb, 1.0, A + j + j * lda, lda, A + j + (j + jb) * lda, lda);
             if (s != ULMB200_OK) return set_status(s);
             if (j + jb < m) {
