@@ -23,6 +23,7 @@ int check_cuda(cudaError_t e, const char *what, const char *file, int line)
 {
     if (e == cudaSuccess) return ULMB200_OK;
     fprintf(stderr, "ulmblas_b200: %s failed: %s (%s:%d)\n", what, cudaGetErrorString(e), file, line);
+    cudaGetLastError();      // a launch error is reported once, not again by the next call
     return set_status(ULMB200_CUDA_ERROR);
 }
 

@@ -309,6 +309,84 @@ struct CluArgs {
     int R;                // rows per CTA
 };
 
+// What a cluster does once its sub-panel is factored and written back: the sub-panel's row
+// exchanges, as (destination row <- source row) pairs, applied to the other columns of the
+// 128-column panel, then U12 = L11^-1 A12 for the columns to its right.  `idx` is scratch shared
+// memory for (rows of the sub-panel) ints.
+struct CluShared {
+    int s_piv[kCluW];                 // pivot of column c as a sub-panel row index
+    int s_dst[2 * kCluW], s_src[2 * kCluW], s_cnt, s_info;
+    double s_L11[kCluW * kCluW];
+    double s_buf[2 * kCluW][8];
+};
+
+__device__ __forceinline__ void cluster_post_phase(const CluArgs &a, CluShared &sh, int *idx, int b, int ncol)
+{
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int w = a.w;
+    double *Asub = a.A + a.c0 + (int64_t)a.c0 * a.lda;
+    // its row exchanges as (destination row <- source row) pairs: replay them on a sparse index map
+    if (t < ncol) { idx[t] = t; }
+    __syncthreads();
+    if (t < ncol) idx[sh.s_piv[t]] = sh.s_piv[t];
+    __syncthreads();
+    if (t == 0) {
+        for (int c = 0; c < ncol; ++c) {
+            const int p = sh.s_piv[c];
+            const int tmp = idx[c]; idx[c] = idx[p]; idx[p] = tmp;
+        }
+        sh.s_cnt = 0;
+    }
+    __syncthreads();
+    if (t < 2 * ncol) {
+        const int r = t < ncol ? t : sh.s_piv[t - ncol];
+        bool first = idx[r] != r;
+        for (int q = 0; q < t && first; ++q) first = (q < ncol ? q : sh.s_piv[q - ncol]) != r;
+        if (first) { const int slot = atomicAdd(&sh.s_cnt, 1); sh.s_dst[slot] = r; sh.s_src[slot] = idx[r]; }
+    }
+    __syncthreads();
+    const int cnt = sh.s_cnt;
+
+    // my columns of the panel outside the sub-panel: exchange rows, then (right of it) U12
+    for (int e = t; e < ncol * ncol; e += kLuThreads) {
+        const int i = e % ncol, q = e / ncol;
+        sh.s_L11[q * kCluW + i] = Asub[i + (int64_t)q * a.lda];
+    }
+    __syncthreads();
+    const int nother = a.nb - w;
+    for (int base = b * 8; base < nother; base += kClu * 8) {
+        // up to 8 columns per pass; oc counts the columns outside the sub-panel
+        const int ncs = min(8, nother - base);
+        for (int e = t; e < cnt * ncs; e += kLuThreads) {
+            const int q = e % cnt, k = e / cnt;
+            const int oc = base + k, col = oc < a.c0 ? oc : oc + w;
+            sh.s_buf[q][k] = a.A[a.c0 + sh.s_src[q] + (int64_t)col * a.lda];
+        }
+        __syncthreads();
+        for (int e = t; e < cnt * ncs; e += kLuThreads) {
+            const int q = e % cnt, k = e / cnt;
+            const int oc = base + k, col = oc < a.c0 ? oc : oc + w;
+            a.A[a.c0 + sh.s_dst[q] + (int64_t)col * a.lda] = sh.s_buf[q][k];
+        }
+        __threadfence_block();
+        __syncthreads();
+        // U12: one warp per column right of the sub-panel, lane i holds element i
+        if (warp < ncs) {
+            const int oc = base + warp, col = oc < a.c0 ? oc : oc + w;
+            if (col >= a.c0 + w) {
+                double *x = a.A + a.c0 + (int64_t)col * a.lda;
+                double u = lane < ncol ? x[lane] : 0.0;
+                for (int q = 0; q + 1 < ncol; ++q) {
+                    const double uq = __shfl_sync(0xffffffffu, u, q);
+                    if (lane > q && lane < ncol) u -= sh.s_L11[q * kCluW + lane] * uq;
+                }
+                if (lane < ncol) x[lane] = u;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
 {
     cg::cluster_group cluster = cg::this_cluster();
@@ -321,10 +399,7 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
     __shared__ double s_row[kCluW];
     __shared__ double s_pivv[kCluW];             // pivot values (0 = column skipped as singular)
     __shared__ int s_wi[kLuThreads / 32];
-    __shared__ int s_piv[kCluW];                 // pivot of column c as a sub-panel row index
-    __shared__ int s_dst[2 * kCluW], s_src[2 * kCluW], s_cnt, s_info;
-    __shared__ double s_L11[kCluW * kCluW];
-    __shared__ double s_buf[2 * kCluW][8];
+    __shared__ CluShared sh;
 
     const int b = (int)cluster.block_rank(), t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int64_t ms = a.m - a.c0;                               // rows of the sub-panel
@@ -336,7 +411,7 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
 
     for (int cc = 0; cc < w; ++cc)
         for (int r = t; r < nr; r += kLuThreads) S[cc * ldS + r] = Asub[lo + r + (int64_t)cc * a.lda];
-    if (t == 0) s_info = 0;
+    if (t == 0) sh.s_info = 0;
     __syncthreads();
 
     const int ncol = (int)min((int64_t)w, ms);
@@ -380,8 +455,8 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
         // pivots and a zero-pivot report stay in shared memory until the sub-panel is done: a global
         // store here would have to drain before every cluster barrier's release
         if (t == 0) {
-            s_piv[c] = p;
-            if (singular && s_info == 0) s_info = c + 1;
+            sh.s_piv[c] = p;
+            if (singular && sh.s_info == 0) sh.s_info = c + 1;
         }
         if (!singular) {
             const int wr = min(kClu - 1, p / R);            // CTA that owns row p
@@ -434,75 +509,201 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
 
     // the factored sub-panel goes back, with its pivots (matrix row indices) and the first zero pivot
     if (b == 0) {
-        if (t < ncol) a.piv[a.row_off + a.c0 + t] = (int)(s_piv[t] + a.row_off + a.c0);
-        if (t == 0 && s_info != 0) atomicCAS(a.info, 0, (int)(a.row_off + a.c0 + s_info));
+        if (t < ncol) a.piv[a.row_off + a.c0 + t] = (int)(sh.s_piv[t] + a.row_off + a.c0);
+        if (t == 0 && sh.s_info != 0) atomicCAS(a.info, 0, (int)(a.row_off + a.c0 + sh.s_info));
     }
     for (int cc = 0; cc < w; ++cc)
         for (int r = t; r < nr; r += kLuThreads) Asub[lo + r + (int64_t)cc * a.lda] = S[cc * ldS + r];
     __threadfence();
     cluster.sync();
 
-    // its row exchanges as (destination row <- source row) pairs: replay them on a sparse index map
-    int *idx = reinterpret_cast<int *>(lu_smem);                 // the slab is no longer needed
-    if (t < ncol) { idx[t] = t; }
-    __syncthreads();
-    if (t < ncol) idx[s_piv[t]] = s_piv[t];
-    __syncthreads();
-    if (t == 0) {
-        for (int c = 0; c < ncol; ++c) {
-            const int p = s_piv[c];
-            const int tmp = idx[c]; idx[c] = idx[p]; idx[p] = tmp;
-        }
-        s_cnt = 0;
-    }
-    __syncthreads();
-    if (t < 2 * ncol) {
-        const int r = t < ncol ? t : s_piv[t - ncol];
-        bool first = idx[r] != r;
-        for (int q = 0; q < t && first; ++q) first = (q < ncol ? q : s_piv[q - ncol]) != r;
-        if (first) { const int slot = atomicAdd(&s_cnt, 1); s_dst[slot] = r; s_src[slot] = idx[r]; }
-    }
-    __syncthreads();
-    const int cnt = s_cnt;
+    cluster_post_phase(a, sh, reinterpret_cast<int *>(lu_smem), b, ncol);
+}
 
-    // my columns of the panel outside the sub-panel: exchange rows, then (right of it) U12
-    for (int e = t; e < ncol * ncol; e += kLuThreads) {
-        const int i = e % ncol, q = e / ncol;
-        s_L11[q * kCluW + i] = Asub[i + (int64_t)q * a.lda];
+// The same sub-panel factorisation with the rows held in REGISTERS: thread t of CTA b owns rows
+// lo + t + 256 i (i < RPT) of the sub-panel, all 32 columns of each.  The rank-1 update then costs no
+// shared-memory traffic at all, and a column needs one block barrier (inside the pivot search) and
+// one cluster barrier.  Requires a full 32-column sub-panel of at least 32 rows and at most
+// 16 * 256 * RPT rows; everything is unrolled so that the register arrays are indexed statically.
+__device__ __forceinline__ void lu_warp_argmax_key(double &v, int &i)
+{
+    // v is -1 (no candidate) or a non-negative number: its bit pattern orders like the number
+    const unsigned long long key = v < 0.0 ? 0ull : (unsigned long long)__double_as_longlong(v) + 1ull;
+    const unsigned hi = (unsigned)(key >> 32), lo = (unsigned)key;
+    const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+    const unsigned ml = __reduce_max_sync(0xffffffffu, hi == mh ? lo : 0u);
+    const bool mine = hi == mh && lo == ml;
+    i = __reduce_min_sync(0xffffffffu, mine ? i : INT_MAX);
+    const unsigned long long mk = ((unsigned long long)mh << 32) | ml;
+    v = mk == 0ull ? -1.0 : __longlong_as_double((long long)(mk - 1ull));
+}
+
+template <int RPT>
+__global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArgs a)
+{
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ double lu_smem[];                           // only the post phase's index map
+    __shared__ double sv[kLuThreads / 32];
+    __shared__ int s_wi[kLuThreads / 32];
+    __shared__ double pub_val[2][kClu];
+    __shared__ int pub_idx[2][kClu];
+    __shared__ double pub_row[2][kCluW];
+    __shared__ double pub_rowc[2][kCluW];
+    __shared__ double s_roww[kLuThreads / 32][kCluW];            // the pivot row, one copy per warp
+    __shared__ CluShared sh;
+
+    constexpr int W = kCluW;
+    const int b = (int)cluster.block_rank(), t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int ms = (int)(a.m - a.c0);
+    const int R = a.R;
+    const int lo = b * R, hi = min(ms, lo + R);
+    const int nr = max(0, hi - lo);
+    double *Asub = a.A + a.c0 + (int64_t)a.c0 * a.lda;
+
+    double row[RPT][W];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int r = t + kLuThreads * i;
+#pragma unroll
+        for (int cc = 0; cc < W; ++cc) row[i][cc] = r < nr ? Asub[lo + r + (int64_t)cc * a.lda] : 0.0;
     }
+    if (t == 0) sh.s_info = 0;
     __syncthreads();
-    const int nother = a.nb - w;
-    for (int base = b * 8; base < nother; base += kClu * 8) {
-        // up to 8 columns per pass; oc counts the columns outside the sub-panel
-        const int ncs = min(8, nother - base);
-        for (int e = t; e < cnt * ncs; e += kLuThreads) {
-            const int q = e % cnt, k = e / cnt;
-            const int oc = base + k, col = oc < a.c0 ? oc : oc + w;
-            s_buf[q][k] = a.A[a.c0 + s_src[q] + (int64_t)col * a.lda];
-        }
-        __syncthreads();
-        for (int e = t; e < cnt * ncs; e += kLuThreads) {
-            const int q = e % cnt, k = e / cnt;
-            const int oc = base + k, col = oc < a.c0 ? oc : oc + w;
-            a.A[a.c0 + s_dst[q] + (int64_t)col * a.lda] = s_buf[q][k];
-        }
-        __threadfence_block();
-        __syncthreads();
-        // U12: one warp per column right of the sub-panel, lane i holds element i
-        if (warp < ncs) {
-            const int oc = base + warp, col = oc < a.c0 ? oc : oc + w;
-            if (col >= a.c0 + w) {
-                double *x = a.A + a.c0 + (int64_t)col * a.lda;
-                double u = lane < ncol ? x[lane] : 0.0;
-                for (int q = 0; q + 1 < ncol; ++q) {
-                    const double uq = __shfl_sync(0xffffffffu, u, q);
-                    if (lane > q && lane < ncol) u -= s_L11[q * kCluW + lane] * uq;
-                }
-                if (lane < ncol) x[lane] = u;
+
+#pragma unroll
+    for (int c = 0; c < W; ++c) {
+        const int par = c & 1;
+        // (1) candidate among my rows >= c
+        double bv = -1.0;
+        int bi = INT_MAX;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const int r = t + kLuThreads * i, gr = lo + r;
+            if (r < nr && gr >= c) {
+                const double v = fabs(row[i][c]);
+                if (v > bv) { bv = v; bi = gr; }
             }
         }
+        lu_warp_argmax_key(bv, bi);
+        if (lane == 0) { sv[warp] = bv; s_wi[warp] = bi; }
         __syncthreads();
+        bv = lane < kLuThreads / 32 ? sv[lane] : -1.0;
+        bi = lane < kLuThreads / 32 ? s_wi[lane] : INT_MAX;
+        lu_warp_argmax_key(bv, bi);
+        // (2) publish: the candidate to everyone, its row (and row c) parked here
+        if (t < kClu) {
+            *cluster.map_shared_rank(&pub_val[par][b], t) = bv;
+            *cluster.map_shared_rank(&pub_idx[par][b], t) = bi;
+        }
+        if (bv >= 0.0) {
+            const int rl = bi - lo;
+            if (t == (rl & (kLuThreads - 1))) {
+                const int sel = rl / kLuThreads;
+#pragma unroll
+                for (int cc = 0; cc < W; ++cc) {
+                    double v = row[0][cc];
+#pragma unroll
+                    for (int i = 1; i < RPT; ++i) v = sel == i ? row[i][cc] : v;     // selects: static register indices
+                    pub_row[par][cc] = v;
+                }
+            }
+        }
+        if (c >= lo && c < hi) {
+            const int rl = c - lo;
+            if (t == (rl & (kLuThreads - 1))) {
+                const int sel = rl / kLuThreads;
+#pragma unroll
+                for (int cc = 0; cc < W; ++cc) {
+                    double v = row[0][cc];
+#pragma unroll
+                    for (int i = 1; i < RPT; ++i) v = sel == i ? row[i][cc] : v;
+                    pub_rowc[par][cc] = v;
+                }
+            }
+        }
+        cluster.sync();
+
+        // (3) the pivot, found by every warp on its own
+        double pv = lane < kClu ? pub_val[par][lane] : -1.0;
+        int p = lane < kClu ? pub_idx[par][lane] : INT_MAX;
+        lu_warp_argmax_key(pv, p);
+        const bool singular = !(pv > 0.0);
+        if (singular) p = c;
+        if (t == 0) {
+            sh.s_piv[c] = p;
+            if (singular && sh.s_info == 0) sh.s_info = c + 1;
+        }
+        if (!singular) {
+            const int wr = min(kClu - 1, p / R), oc = min(kClu - 1, c / R);
+            s_roww[warp][lane] = *cluster.map_shared_rank(&pub_row[par][lane], wr);
+            __syncwarp();
+            if (p != c) {
+                // the exchange, by the two threads that hold the rows
+                if (p >= lo && p < hi) {
+                    const int rl = p - lo;
+                    if (t == (rl & (kLuThreads - 1))) {
+                        const double *src = cluster.map_shared_rank(&pub_rowc[par][0], oc);
+                        const int sel = rl / kLuThreads;
+#pragma unroll
+                        for (int cc = 0; cc < W; ++cc) {
+                            const double v = src[cc];
+#pragma unroll
+                            for (int i = 0; i < RPT; ++i) row[i][cc] = sel == i ? v : row[i][cc];
+                        }
+                    }
+                }
+                if (c >= lo && c < hi) {
+                    const int rl = c - lo;
+                    if (t == (rl & (kLuThreads - 1))) {
+                        const int sel = rl / kLuThreads;
+#pragma unroll
+                        for (int cc = 0; cc < W; ++cc) {
+                            const double v = s_roww[warp][cc];
+#pragma unroll
+                            for (int i = 0; i < RPT; ++i) row[i][cc] = sel == i ? v : row[i][cc];
+                        }
+                    }
+                }
+            }
+            // (4) multipliers and rank-1 update, all in registers
+            const double piv = s_roww[warp][c];
+            const bool recip = fabs(piv) >= DBL_MIN;
+            const double rp = 1.0 / piv;
+            double l[RPT];
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) {
+                const int r = t + kLuThreads * i, gr = lo + r;
+                l[i] = 0.0;
+                if (r < nr && gr > c) {
+                    l[i] = recip ? row[i][c] * rp : row[i][c] / piv;
+                    row[i][c] = l[i];
+                }
+            }
+#pragma unroll
+            for (int cc = c + 1; cc < W; ++cc) {
+                const double pr = s_roww[warp][cc];
+#pragma unroll
+                for (int i = 0; i < RPT; ++i) row[i][cc] -= l[i] * pr;      // l = 0 leaves the row as it is
+            }
+        }
+        __syncwarp();
     }
+
+    if (b == 0) {
+        if (t < W) a.piv[a.row_off + a.c0 + t] = (int)(sh.s_piv[t] + a.row_off + a.c0);
+        if (t == 0 && sh.s_info != 0) atomicCAS(a.info, 0, (int)(a.row_off + a.c0 + sh.s_info));
+    }
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int r = t + kLuThreads * i;
+        if (r < nr) {
+#pragma unroll
+            for (int cc = 0; cc < W; ++cc) Asub[lo + r + (int64_t)cc * a.lda] = row[i][cc];
+        }
+    }
+    __threadfence();
+    cluster.sync();
+    cluster_post_phase(a, sh, reinterpret_cast<int *>(lu_smem), b, W);
 }
 
 // A22 <- A22 - L21 U12 inside the 128-column panel after a sub-panel: rows below the sub-panel's
@@ -655,7 +856,14 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                                        (int)(sizeof(double) * kLuSlabRows * kLuNB)));
     }
     static int64_t cluster_smem_max[kMaxDevices] = {};
+    static bool reg_ok[kMaxDevices] = {};
     if (cluster_smem_max[dev] == 0) {
+        reg_ok[dev] =
+            cudaFuncSetAttribute(getf2_cluster_reg_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+            cudaFuncSetAttribute(getf2_cluster_reg_kernel<2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+            // the index map of the post phase: 4 bytes per row of the sub-panel, up to 8192 rows
+            cudaFuncSetAttribute(getf2_cluster_reg_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 40 * 1024) == cudaSuccess &&
+            cudaFuncSetAttribute(getf2_cluster_reg_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 40 * 1024) == cudaSuccess;
         // what one CTA of a 16-CTA cluster may take next to the kernel's static shared memory
         cudaFuncAttributes fa;
         int optin = 0;
@@ -725,7 +933,15 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                 at[0].id = cudaLaunchAttributeClusterDimension;
                 at[0].val.clusterDim.x = kClu; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
                 cfg.attrs = at; cfg.numAttrs = 1;
-                ULMB_CUDA(cudaLaunchKernelEx(&cfg, getf2_cluster_kernel, q));
+                // full-width sub-panels of up to 8192 rows keep their rows in registers
+                static const int use_reg = [] { const char *e = getenv("ULMB200_LU_REG"); return e ? atoi(e) : 1; }();
+                if (use_reg && reg_ok[dev] && q.w == kCluW && rows >= kCluW && q.R <= 2 * kLuThreads) {
+                    cfg.dynamicSmemBytes = (size_t)(rows * 4 + 64);
+                    if (q.R <= kLuThreads) ULMB_CUDA(cudaLaunchKernelEx(&cfg, getf2_cluster_reg_kernel<1>, q));
+                    else                   ULMB_CUDA(cudaLaunchKernelEx(&cfg, getf2_cluster_reg_kernel<2>, q));
+                } else {
+                    ULMB_CUDA(cudaLaunchKernelEx(&cfg, getf2_cluster_kernel, q));
+                }
                 count_launch();
                 const int ncr = jb - c0 - q.w;
                 if (ncr > 0 && c0 + q.w < a.m) {
