@@ -523,7 +523,9 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_kernel(CluArgs a)
 // The same sub-panel factorisation with the rows held in REGISTERS: thread t of CTA b owns rows
 // lo + t + 256 i (i < RPT) of the sub-panel, all 32 columns of each.  The rank-1 update then costs no
 // shared-memory traffic at all, and a column needs one block barrier (inside the pivot search) and
-// one cluster barrier.  Requires a full 32-column sub-panel of at least 32 rows and at most
+// one cluster barrier.  Rows are not exchanged physically: each carries the position the reference's
+// exchanges would have given it (which also keeps the "first largest" rule exact), and goes to that
+// position when the sub-panel is written back.  Requires a full 32-column sub-panel of at least 32 rows and at most
 // 16 * 256 * RPT rows; everything is unrolled so that the register arrays are indexed statically.
 __device__ __forceinline__ void lu_warp_argmax_key(double &v, int &i)
 {
@@ -547,8 +549,7 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
     __shared__ int s_wi[kLuThreads / 32];
     __shared__ double pub_val[2][kClu];
     __shared__ int pub_idx[2][kClu];
-    __shared__ double pub_row[2][kCluW];
-    __shared__ double pub_rowc[2][kCluW];
+    __shared__ double pub_row[2][kCluW];                          // my candidate's row
     __shared__ double s_roww[kLuThreads / 32][kCluW];            // the pivot row, one copy per warp
     __shared__ CluShared sh;
 
@@ -560,10 +561,17 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
     const int nr = max(0, hi - lo);
     double *Asub = a.A + a.c0 + (int64_t)a.c0 * a.lda;
 
+    // Rows never move between threads.  pos[i] is the position the row currently has in the
+    // sub-panel (what the reference's explicit exchanges would have made it), done[i] says it has
+    // served as a pivot row and is final; the rows go back to their positions at the end.
     double row[RPT][W];
+    int pos[RPT];
+    bool done[RPT];
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
         const int r = t + kLuThreads * i;
+        pos[i] = lo + r;
+        done[i] = r >= nr;                         // rows that do not exist never take part
 #pragma unroll
         for (int cc = 0; cc < W; ++cc) row[i][cc] = r < nr ? Asub[lo + r + (int64_t)cc * a.lda] : 0.0;
     }
@@ -573,15 +581,14 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
 #pragma unroll
     for (int c = 0; c < W; ++c) {
         const int par = c & 1;
-        // (1) candidate among my rows >= c
+        // (1) candidate among my live rows: largest |value|, smallest position among equals
         double bv = -1.0;
         int bi = INT_MAX;
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-            const int r = t + kLuThreads * i, gr = lo + r;
-            if (r < nr && gr >= c) {
+            if (!done[i]) {
                 const double v = fabs(row[i][c]);
-                if (v > bv) { bv = v; bi = gr; }
+                if (v > bv || (v == bv && pos[i] < bi)) { bv = v; bi = pos[i]; }
             }
         }
         lu_warp_argmax_key(bv, bi);
@@ -590,15 +597,16 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
         bv = lane < kLuThreads / 32 ? sv[lane] : -1.0;
         bi = lane < kLuThreads / 32 ? s_wi[lane] : INT_MAX;
         lu_warp_argmax_key(bv, bi);
-        // (2) publish: the candidate to everyone, its row (and row c) parked here
+        // (2) publish: the candidate to everyone, its row parked here by the thread that holds it
         if (t < kClu) {
             *cluster.map_shared_rank(&pub_val[par][b], t) = bv;
             *cluster.map_shared_rank(&pub_idx[par][b], t) = bi;
         }
-        if (bv >= 0.0) {
-            const int rl = bi - lo;
-            if (t == (rl & (kLuThreads - 1))) {
-                const int sel = rl / kLuThreads;
+        {
+            int sel = -1;
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) sel = (!done[i] && pos[i] == bi) ? i : sel;
+            if (sel >= 0 && bv >= 0.0) {
 #pragma unroll
                 for (int cc = 0; cc < W; ++cc) {
                     double v = row[0][cc];
@@ -608,73 +616,43 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
                 }
             }
         }
-        if (c >= lo && c < hi) {
-            const int rl = c - lo;
-            if (t == (rl & (kLuThreads - 1))) {
-                const int sel = rl / kLuThreads;
-#pragma unroll
-                for (int cc = 0; cc < W; ++cc) {
-                    double v = row[0][cc];
-#pragma unroll
-                    for (int i = 1; i < RPT; ++i) v = sel == i ? row[i][cc] : v;
-                    pub_rowc[par][cc] = v;
-                }
-            }
-        }
         cluster.sync();
 
-        // (3) the pivot, found by every warp on its own
+        // (3) the pivot, found by every warp on its own; wr = the CTA whose candidate won
         double pv = lane < kClu ? pub_val[par][lane] : -1.0;
         int p = lane < kClu ? pub_idx[par][lane] : INT_MAX;
+        const double myv = pv;
+        const int myp = p;
         lu_warp_argmax_key(pv, p);
+        const unsigned won = __ballot_sync(0xffffffffu, lane < kClu && myv == pv && myp == p);
+        const int wr = won ? __ffs(won) - 1 : 0;
         const bool singular = !(pv > 0.0);
         if (singular) p = c;
         if (t == 0) {
             sh.s_piv[c] = p;
             if (singular && sh.s_info == 0) sh.s_info = c + 1;
         }
-        if (!singular) {
-            const int wr = min(kClu - 1, p / R), oc = min(kClu - 1, c / R);
-            s_roww[warp][lane] = *cluster.map_shared_rank(&pub_row[par][lane], wr);
-            __syncwarp();
-            if (p != c) {
-                // the exchange, by the two threads that hold the rows
-                if (p >= lo && p < hi) {
-                    const int rl = p - lo;
-                    if (t == (rl & (kLuThreads - 1))) {
-                        const double *src = cluster.map_shared_rank(&pub_rowc[par][0], oc);
-                        const int sel = rl / kLuThreads;
+        if (!singular) s_roww[warp][lane] = *cluster.map_shared_rank(&pub_row[par][lane], wr);
+        // the exchange of positions c and p: the pivot row becomes final at c, the row that sat at c
+        // (if it is another one) now sits at p
 #pragma unroll
-                        for (int cc = 0; cc < W; ++cc) {
-                            const double v = src[cc];
-#pragma unroll
-                            for (int i = 0; i < RPT; ++i) row[i][cc] = sel == i ? v : row[i][cc];
-                        }
-                    }
-                }
-                if (c >= lo && c < hi) {
-                    const int rl = c - lo;
-                    if (t == (rl & (kLuThreads - 1))) {
-                        const int sel = rl / kLuThreads;
-#pragma unroll
-                        for (int cc = 0; cc < W; ++cc) {
-                            const double v = s_roww[warp][cc];
-#pragma unroll
-                            for (int i = 0; i < RPT; ++i) row[i][cc] = sel == i ? v : row[i][cc];
-                        }
-                    }
-                }
+        for (int i = 0; i < RPT; ++i) {
+            if (!done[i]) {
+                if (pos[i] == p) { done[i] = true; pos[i] = c; }
+                else if (pos[i] == c) pos[i] = p;
             }
-            // (4) multipliers and rank-1 update, all in registers
+        }
+        __syncwarp();
+        if (!singular) {
+            // (4) multipliers and rank-1 update of the live rows, all in registers
             const double piv = s_roww[warp][c];
             const bool recip = fabs(piv) >= DBL_MIN;
             const double rp = 1.0 / piv;
             double l[RPT];
 #pragma unroll
             for (int i = 0; i < RPT; ++i) {
-                const int r = t + kLuThreads * i, gr = lo + r;
                 l[i] = 0.0;
-                if (r < nr && gr > c) {
+                if (!done[i]) {
                     l[i] = recip ? row[i][c] * rp : row[i][c] / piv;
                     row[i][c] = l[i];
                 }
@@ -698,7 +676,7 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
         const int r = t + kLuThreads * i;
         if (r < nr) {
 #pragma unroll
-            for (int cc = 0; cc < W; ++cc) Asub[lo + r + (int64_t)cc * a.lda] = row[i][cc];
+            for (int cc = 0; cc < W; ++cc) Asub[pos[i] + (int64_t)cc * a.lda] = row[i][cc];
         }
     }
     __threadfence();
