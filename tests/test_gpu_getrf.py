@@ -46,8 +46,38 @@ def check_lu(ulm, m, n, seed, extra=3):
 def test_dgetrf_shapes(ulm):
     for i, (m, n) in enumerate([(1, 1), (7, 5), (5, 7), (31, 31), (130, 130), (300, 200), (200, 300),
                                 (513, 513), (1100, 700),
-                                (30000, 40)]):      # the last one is too tall for the shared-memory panel
+                                (5000, 300),        # more than 4096 rows: two rows per thread in the register panel
+                                (9000, 160),        # more than 8192 rows: the cluster panel held in shared memory
+                                (14000, 40),        # ... with 16-column sub-panels
+                                (30000, 40),        # ... with 8-column sub-panels
+                                (60000, 20)]):      # too tall for a cluster's shared memory: cooperative panel
         check_lu(ulm, m, n, 70000 + i)
+
+
+def test_dgetrf_ties_follow_the_first_largest_rule(ulm):
+    """A = [B; B]: every row has a bit-identical twin, and twins stay bit-identical under elimination
+    (same operations on the same numbers), so every pivot search ends in an exact tie between two
+    rows.  The first of the two in the CURRENT row order has to win, as in the reference
+    (iamax returns the first maximum)."""
+    for i, (k, n) in enumerate([(32, 20), (300, 200), (5000, 96)]):
+        B = det_uniform(72000 + i, k, n)
+        A0 = np.asfortranarray(np.vstack([B, B]))
+        m = 2 * k
+        got = A0.copy(order="F")
+        piv, info = ulm.dgetrf(got)
+        assert ulm.last_status() == ulm.OK and info == 0
+        if oracle.have_ref("lapack"):
+            want = A0.copy(order="F")
+            rpiv, rinfo = oracle.ref_dgetrf(want)
+            assert rinfo == 0
+            assert np.array_equal(piv, rpiv), (k, n, int(np.argmax(piv != rpiv)))
+        mn = min(m, n)
+        L = np.tril(got, -1)[:, :mn] + np.eye(m, mn)
+        U = np.triu(got)[:mn, :]
+        resid = np.abs(apply_piv(A0, piv) - L @ U)
+        assert (resid <= 4.0 * mn * EPS64 * (np.abs(L) @ np.abs(U)) + 1e-300).all()
+        # each pivot row's twin has a multiplier of 1 up to the rounding of the reciprocal
+        assert (np.sum(np.abs(np.tril(got, -1) - 1.0) <= 4 * EPS64, axis=0)[:mn] >= 1).all()
 
 
 def test_dgetrf_2048_and_zero_pivot(ulm):

@@ -55,6 +55,8 @@ bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, cons
 int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n, int64_t k,
                  double alpha, const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
                  double *C, int64_t ldc, int *err_word = nullptr);
+// sets the number of SMs the persistent DGEMM grid leaves free; returns the previous value
+int sm_reserve_swap(int sms);
 int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri);
 // B <- alpha*op(A)^-1*B (side 0) or alpha*B*op(A)^-1 (side 1) with caller-provided scratch
 // (level3_sm100.cu): inv holds ceil(dim/128)*128*128 doubles, W 128*n (left) or m*128 (right).

@@ -620,6 +620,11 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     return set_status(r);
 }
 
+int sm_reserve_swap(int sms)
+{
+    return g_sm_reserve.exchange(sms < 0 ? 0 : sms, std::memory_order_relaxed);
+}
+
 }  // namespace ulmb200
 
 extern "C" void ulmb200_set_sm_reserve(int sms)

@@ -4,7 +4,7 @@
 //
 //   for each 128-column panel:   getf2 on the panel          -> getf2_cluster_kernel (+ lu_rank_update_kernel)
 //                                 row swaps left and right    -> lu_perm_list_kernel + laswp_gather_kernel
-//                                 A12 <- L11^-1 A12           -> device TRSM (unit lower)
+//                                 A12 <- L11^-1 A12           -> lu_trsm_unit_lower_kernel
 //                                 A22 <- A22 - A21 A12        -> device DGEMM
 //
 // Panels too tall for the cluster kernel's shared memory fall back to one cooperative launch: the CTAs split the panel's rows,
@@ -24,9 +24,6 @@
 namespace cg = cooperative_groups;
 
 namespace ulmb200 {
-
-int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
-                 double alpha, const double *A, int64_t lda, double *B, int64_t ldb);
 
 constexpr int kLuNB = 128;
 constexpr int kLuThreads = 256;
@@ -698,9 +695,9 @@ __global__ void __launch_bounds__(kLuThreads) lu_rank_update_kernel(RankArgs a)
     __shared__ double U[kCluW][128 + 1];
     const int t = threadIdx.x;
     const double *U12 = a.A + a.c0 + (int64_t)(a.c0 + a.w) * a.lda;
-    for (int e = t; e < a.w * a.ncr; e += kLuThreads) {
-        const int k = e % a.w, cc = e / a.w;
-        U[k][cc] = U12[k + (int64_t)cc * a.lda];
+    for (int e = t; e < kCluW * a.ncr; e += kLuThreads) {
+        const int k = e % kCluW, cc = e / kCluW;
+        U[k][cc] = k < a.w ? U12[k + (int64_t)cc * a.lda] : 0.0;       // rows beyond w take part as zeros
     }
     __syncthreads();
     const int64_t r = (int64_t)a.c0 + a.w + (int64_t)blockIdx.x * 64 + (t & 63);
@@ -792,6 +789,59 @@ __global__ void __launch_bounds__(kLuThreads) laswp_gather_kernel(double *A, int
     }
 }
 
+// U12 <- L11^-1 A12 for the columns right of a panel: L11 is the panel's unit lower triangle
+// (nb <= 128), A12 its nb x ncols row block.  The generic TRSM inverts diagonal blocks and runs
+// GEMMs -- four launches and ~150 us for what is 0.1 GFLOP here -- so LU has its own: L11 sits in
+// shared memory, a warp solves four columns at a time by forward substitution across its lanes
+// (lane = row mod 32, four rows per lane), 32 columns per CTA.
+constexpr int kTrsmCols = 32;          // columns per CTA: 8 warps x 4
+
+__global__ void __launch_bounds__(kLuThreads) lu_trsm_unit_lower_kernel(const double *L, int64_t ldl, int nb,
+                                                                        double *B, int64_t ldb, int64_t ncols)
+{
+    extern __shared__ double Ls[];                 // Ls[p * kLuNB + i] = L(i, p)
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    for (int e = t; e < nb * kLuNB; e += kLuThreads) {
+        const int i = e % kLuNB, p = e / kLuNB;
+        Ls[p * kLuNB + i] = (i < nb && i > p) ? L[i + (int64_t)p * ldl] : 0.0;
+    }
+    __syncthreads();
+    const int64_t col0 = (int64_t)blockIdx.x * kTrsmCols + warp * 4;
+    double x[4][4];                                // [column][row chunk]
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int row = lane + 32 * k;
+            x[j][k] = (col0 + j < ncols && row < nb) ? B[row + (col0 + j) * ldb] : 0.0;
+        }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        if (32 * kk >= nb) break;
+        for (int pl = 0; pl < 32; ++pl) {
+            const int p = 32 * kk + pl;
+            if (p >= nb) break;
+            double xp[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xp[j] = __shfl_sync(0xffffffffu, x[j][kk], pl);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (k < kk) continue;
+                const double l = Ls[p * kLuNB + lane + 32 * k];      // zero on and above the diagonal
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j][k] -= l * xp[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int row = lane + 32 * k;
+            if (col0 + j < ncols && row < nb) B[row + (col0 + j) * ldb] = x[j][k];
+        }
+}
+
 // Row exchanges given as (row, other row) pairs in the order they are to be applied.
 __global__ void laswp_pairs_kernel(double *A, int64_t lda, int64_t ncols, const int *pairs, int npairs)
 {
@@ -874,12 +924,18 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
     double *rowc = cand_rows + 2 * nG * kLuNB;
     int *cand_idx = reinterpret_cast<int *>(rowc + 2 * kLuNB);
     constexpr size_t kSlabSmem = sizeof(double) * (size_t)kLuSlabRows * kLuNB;
+    constexpr size_t kTrsmSmem = sizeof(double) * (size_t)kLuNB * kLuNB;
+    static bool trsm_attr[kMaxDevices] = {};
+    if (!trsm_attr[dev]) {
+        ULMB_CUDA(cudaFuncSetAttribute(lu_trsm_unit_lower_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTrsmSmem));
+        trsm_attr[dev] = true;
+    }
     int *perm_list = static_cast<int *>(device_scratch(13, sizeof(int) * (1 + 2 * kPermMax)));
     if (!perm_list) return set_status(ULMB200_CUDA_ERROR);
 
     const int64_t mn = m < n ? m : n;
-    for (int64_t j = 0; j < mn; j += kLuNB) {
-        const int jb = (int)((mn - j) < kLuNB ? (mn - j) : kLuNB);
+    // getf2 on the panel that starts at (j, j), queued on stream ps
+    auto factor_panel = [&](cudaStream_t ps, int64_t j, int jb) -> int {
         PanelArgs a;
         a.A = A + j + j * lda; a.lda = lda; a.m = m - j; a.jb = jb; a.row_off = j;
         a.piv = d_piv; a.info = d_info; a.cand_val = cand_val; a.cand_idx = cand_idx;
@@ -906,7 +962,7 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                 cudaLaunchConfig_t cfg = {};
                 cfg.gridDim = dim3(kClu); cfg.blockDim = dim3(kLuThreads);
                 cfg.dynamicSmemBytes = (size_t)slab_bytes(rows, q.w);
-                cfg.stream = st;
+                cfg.stream = ps;
                 cudaLaunchAttribute at[1];
                 at[0].id = cudaLaunchAttributeClusterDimension;
                 at[0].val.clusterDim.x = kClu; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
@@ -926,7 +982,7 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                     RankArgs r;
                     r.A = a.A; r.lda = lda; r.m = a.m; r.c0 = c0; r.w = q.w; r.ncr = ncr;
                     const int64_t below = a.m - c0 - q.w;
-                    lu_rank_update_kernel<<<(unsigned)((below + 63) / 64), kLuThreads, 0, st>>>(r);
+                    lu_rank_update_kernel<<<(unsigned)((below + 63) / 64), kLuThreads, 0, ps>>>(r);
                     count_launch();
                 }
             }
@@ -944,17 +1000,45 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
             q.cand_rows = cand_rows; q.rowc = rowc; q.cval = cand_val; q.cidx = cand_idx;
             void *args[] = {&q};
             ULMB_CUDA(cudaLaunchCooperativeKernel((const void *)getf2_panel_smem_kernel, dim3((unsigned)Gs),
-                                                  dim3(kLuThreads), args, kSlabSmem, st));
+                                                  dim3(kLuThreads), args, kSlabSmem, ps));
         } else {
             int64_t G = (a.m + 4 * kLuThreads - 1) / (4 * kLuThreads);        // >= 1024 rows per CTA
             if (G > max_ctas[dev]) G = max_ctas[dev];
             if (G < 1) G = 1;
             void *args[] = {&a};
             ULMB_CUDA(cudaLaunchCooperativeKernel((const void *)getf2_panel_kernel, dim3((unsigned)G),
-                                                  dim3(kLuThreads), args, 0, st));
+                                                  dim3(kLuThreads), args, 0, ps));
         }
         count_launch();
         }
+        return ULMB200_OK;
+    };
+
+    // Look-ahead: once the columns of the next panel are updated, that panel is factored on a second
+    // stream while the rest of the trailing update runs on the caller's.  The panel cluster needs 16
+    // SMs of one GPC; it is queued first and the trailing GEMM leaves 16 SMs free, so the two run side
+    // by side (if the GEMM wins the race for the SMs instead, the panel simply runs after it).
+    static const int use_la = [] { const char *e = getenv("ULMB200_LU_LOOKAHEAD"); return e ? atoi(e) : 1; }();
+    static cudaStream_t la_stream[kMaxDevices] = {};
+    static cudaEvent_t la_ev[kMaxDevices][2] = {};
+    bool la = use_la != 0 && mn > kLuNB;
+    if (la && !la_stream[dev]) {
+        if (cudaStreamCreateWithFlags(&la_stream[dev], cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&la_ev[dev][0], cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&la_ev[dev][1], cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            la_stream[dev] = nullptr;
+        }
+    }
+    if (!la_stream[dev]) la = false;
+    const cudaStream_t sb = la_stream[dev];
+
+    {
+        const int jb0 = (int)(mn < kLuNB ? mn : kLuNB);
+        if (int s0 = factor_panel(st, 0, jb0)) return set_status(s0);
+    }
+    for (int64_t j = 0; j < mn; j += kLuNB) {
+        const int jb = (int)((mn - j) < kLuNB ? (mn - j) : kLuNB);
         // the same exchanges on the columns left and right of the panel (getrf.tcc:50-57), as one
         // gather over both column ranges
         {
@@ -970,12 +1054,44 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
             }
         }
         if (j + jb < n) {
-            int s = dtrsm_device(st, 0, 1, 0, 1, jb, n - j - jb, 1.0, A + j + j * lda, lda, A + j + (j + jb) * lda, lda);
-            if (s != ULMB200_OK) return set_status(s);
+            int s = ULMB200_OK;
+            {
+                const int64_t nright = n - j - jb;
+                lu_trsm_unit_lower_kernel<<<(unsigned)((nright + kTrsmCols - 1) / kTrsmCols), kLuThreads, kTrsmSmem, st>>>(
+                    A + j + j * lda, lda, jb, A + j + (j + jb) * lda, lda, nright);
+                count_launch();
+                ULMB_CUDA(cudaGetLastError());
+            }
             if (j + jb < m) {
-                s = dgemm_device(st, 0, 0, 0, m - j - jb, n - j - jb, jb, -1.0, A + (j + jb) + j * lda, lda,
-                                 A + j + (j + jb) * lda, lda, 1.0, A + (j + jb) + (j + jb) * lda, lda);
-                if (s != ULMB200_OK) return set_status(s);
+                const int64_t jn = j + jb;                              // where the next panel starts
+                const int jb2 = jn < mn ? (int)((mn - jn) < kLuNB ? (mn - jn) : kLuNB) : 0;
+                const int64_t mrows = m - jn, ncols = n - jn;
+                const double *L21 = A + jn + j * lda, *U12 = A + j + jn * lda;
+                double *A22 = A + jn + jn * lda;
+                if (jb2 > 0) {
+                    // the next panel's columns first, then its factorisation, then the other columns
+                    s = dgemm_device(st, 0, 0, 0, mrows, jb2, jb, -1.0, L21, lda, U12, lda, 1.0, A22, lda);
+                    if (s != ULMB200_OK) return set_status(s);
+                    if (la) {
+                        ULMB_CUDA(cudaEventRecord(la_ev[dev][0], st));
+                        ULMB_CUDA(cudaStreamWaitEvent(sb, la_ev[dev][0], 0));
+                        if (int sp = factor_panel(sb, jn, jb2)) return set_status(sp);
+                        ULMB_CUDA(cudaEventRecord(la_ev[dev][1], sb));
+                    } else {
+                        if (int sp = factor_panel(st, jn, jb2)) return set_status(sp);
+                    }
+                    if (ncols > jb2) {
+                        const int old = la ? sm_reserve_swap(kClu) : 0;
+                        s = dgemm_device(st, 0, 0, 0, mrows, ncols - jb2, jb, -1.0, L21, lda, U12 + (int64_t)jb2 * lda, lda,
+                                         1.0, A22 + (int64_t)jb2 * lda, lda);
+                        if (la) sm_reserve_swap(old);
+                        if (s != ULMB200_OK) return set_status(s);
+                    }
+                    if (la) ULMB_CUDA(cudaStreamWaitEvent(st, la_ev[dev][1], 0));
+                } else if (ncols > 0) {
+                    s = dgemm_device(st, 0, 0, 0, mrows, ncols, jb, -1.0, L21, lda, U12, lda, 1.0, A22, lda);
+                    if (s != ULMB200_OK) return set_status(s);
+                }
             }
         }
     }
