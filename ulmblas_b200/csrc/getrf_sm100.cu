@@ -575,7 +575,12 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
     if (t == 0) sh.s_info = 0;
     __syncthreads();
 
-#pragma unroll
+    // The column loop is a real loop (one copy of the body in the instruction cache: fully unrolled,
+    // the kernel spent most of its time waiting for instruction fetches).  To keep every register
+    // index static, the row registers rotate by one column per step: slot 0 is always the current
+    // column, slot s holds column c + s, finished columns collect at the tail, and after 32 steps
+    // everything is back in its natural place.
+#pragma unroll 1
     for (int c = 0; c < W; ++c) {
         const int par = c & 1;
         // (1) candidate among my live rows: largest |value|, smallest position among equals
@@ -584,7 +589,7 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
             if (!done[i]) {
-                const double v = fabs(row[i][c]);
+                const double v = fabs(row[i][0]);
                 if (v > bv || (v == bv && pos[i] < bi)) { bv = v; bi = pos[i]; }
             }
         }
@@ -605,11 +610,11 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
             for (int i = 0; i < RPT; ++i) sel = (!done[i] && pos[i] == bi) ? i : sel;
             if (sel >= 0 && bv >= 0.0) {
 #pragma unroll
-                for (int cc = 0; cc < W; ++cc) {
-                    double v = row[0][cc];
+                for (int sl = 0; sl < W; ++sl) {
+                    double v = row[0][sl];
 #pragma unroll
-                    for (int i = 1; i < RPT; ++i) v = sel == i ? row[i][cc] : v;     // selects: static register indices
-                    pub_row[par][cc] = v;
+                    for (int i = 1; i < RPT; ++i) v = sel == i ? row[i][sl] : v;     // selects: static register indices
+                    pub_row[par][(c + sl) & (W - 1)] = v;                             // slot sl holds column c + sl
                 }
             }
         }
@@ -650,18 +655,28 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
             for (int i = 0; i < RPT; ++i) {
                 l[i] = 0.0;
                 if (!done[i]) {
-                    l[i] = recip ? row[i][c] * rp : row[i][c] / piv;
-                    row[i][c] = l[i];
+                    l[i] = recip ? row[i][0] * rp : row[i][0] / piv;
+                    row[i][0] = l[i];
                 }
             }
 #pragma unroll
-            for (int cc = c + 1; cc < W; ++cc) {
-                const double pr = s_roww[warp][cc];
+            for (int sl = 1; sl < W; ++sl) {
+                if (sl < W - c) {                                            // slots beyond hold finished columns
+                    const double pr = s_roww[warp][c + sl];
 #pragma unroll
-                for (int i = 0; i < RPT; ++i) row[i][cc] -= l[i] * pr;      // l = 0 leaves the row as it is
+                    for (int i = 0; i < RPT; ++i) row[i][sl] -= l[i] * pr;  // l = 0 leaves the row as it is
+                }
             }
         }
         __syncwarp();
+        // rotate: the finished column goes to the tail
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const double first = row[i][0];
+#pragma unroll
+            for (int sl = 0; sl + 1 < W; ++sl) row[i][sl] = row[i][sl + 1];
+            row[i][W - 1] = first;
+        }
     }
 
     if (b == 0) {

@@ -2,6 +2,7 @@
 
     python -m ulmblas_b200.perf_report [--quick]
     python -m ulmblas_b200.perf_report --modes 4096     # one DGEMM per transposition mode
+    python -m ulmblas_b200.perf_report --lu 2048        # two LU factorisations: the run to put under a profiler
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m ulmblas_b200.perf_report --sharded-trsm 8192  # DTRSM LLNN split over N GPUs
 
@@ -49,6 +50,23 @@ def modes(sz):
         ms = _time(lambda: u.dev_dgemm(ta, tb, sz, sz, sz, 1.0, A.data_ptr(), sz, B.data_ptr(), sz, 0.0,
                                        C.data_ptr(), sz, stream=s), 1)
         print(f"dgemm {'NT'[ta]}{'NT'[tb]} {sz}^3: {ms:.3f} ms {2.0 * sz ** 3 / ms * 1e-9:.2f} TFLOP/s")
+
+
+def lu_only(m):
+    """Two blocked LU factorisations of an m x m matrix (warm-up + one more), timed with CUDA events."""
+    s = torch.cuda.current_stream().cuda_stream
+    A0 = _buf(m, m, torch.float64, 5, 0)
+    W = A0.clone()
+    piv = torch.zeros(m + 1, dtype=torch.int32, device="cuda")
+    for it in range(2):
+        W.copy_(A0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        u.lib.ulmb200_dgetrf(s, m, m, W.data_ptr(), m, piv.data_ptr(), piv.data_ptr() + 4 * m)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    print(f"dgetrf n={m}: {ms:.3f} ms {2.0 * m ** 3 / 3.0 / ms * 1e-9:.2f} TFLOP/s, info = {int(piv[m].item())}")
 
 
 def sharded_trsm(m):
@@ -107,6 +125,8 @@ def sharded_trsm(m):
 def main():
     if "--sharded-trsm" in sys.argv:
         return sharded_trsm(int(sys.argv[sys.argv.index("--sharded-trsm") + 1]))
+    if "--lu" in sys.argv:
+        return lu_only(int(sys.argv[sys.argv.index("--lu") + 1]))
     if "--modes" in sys.argv:
         return modes(int(sys.argv[sys.argv.index("--modes") + 1]))
     quick = "--quick" in sys.argv
