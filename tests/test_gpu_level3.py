@@ -68,6 +68,32 @@ def test_sgemm_shapes_and_transposes(ulm, mode, monkeypatch):
                 assert ratio <= 1.0, (mode, m, n, k, ta, tb, alpha, beta, ratio)
 
 
+def test_sgemm_split_k_tail(ulm, monkeypatch):
+    """Tile counts a little above a multiple of the SM count: the FP32 kernel gives the last few tiles
+    to several CTAs each, one K range per CTA, added in a fixed order.  Checked on sampled columns
+    against the reference, and for run-to-run reproducibility (bit-identical results)."""
+    monkeypatch.setenv("ULMB200_SGEMM", "fp32")
+    for (m, n, k, ta, tb, alpha, beta) in [(3328, 1536, 1100, "N", "N", 1.0, 0.0),      # 156 tiles: 8 left over, 8 K ranges
+                                           (3300, 1500, 300, "T", "N", 0.7, 1.3),       # ragged edges, 2 K ranges
+                                           (2560, 2304, 515, "N", "T", -1.0, 1.0)]:     # 180 tiles: 32 left over, 4 ranges
+        ra, ca = (m, k) if ta == "N" else (k, m)
+        rb, cb = (k, n) if tb == "N" else (n, k)
+        A = np.asfortranarray(det_uniform(31, ra, ca, np.float32))
+        B = np.asfortranarray(det_uniform(32, rb, cb, np.float32))
+        C0 = np.asfortranarray(det_uniform(33, m, n, np.float32))
+        got = C0.copy(order="F")
+        assert ulm.sgemm(ta, tb, m, n, k, alpha, A, B, beta, got) == ulm.OK
+        again = C0.copy(order="F")
+        assert ulm.sgemm(ta, tb, m, n, k, alpha, A, B, beta, again) == ulm.OK
+        assert np.array_equal(got, again), "the split-K tail must not depend on timing"
+        cols = np.unique(np.concatenate([np.arange(n - 40, n), np.random.default_rng(4).choice(n, 60, replace=False)]))
+        Bs = np.asfortranarray(B[:, cols]) if tb == "N" else np.asfortranarray(B[cols, :])
+        Cs = np.asfortranarray(C0[:, cols])
+        want = reference_sgemm(ta, tb, m, len(cols), k, alpha, A, Bs, beta, Cs)
+        ratio = bound_ratio(got[:, cols], want, gemm_gauge(alpha, op(A, ta), op(Bs, tb), beta, Cs), k, EPS32)
+        assert ratio <= 1.0, (m, n, k, ta, tb, ratio)
+
+
 def test_golden_sgemm_cases_on_gpu(ulm):
     for name, c in load_golden().items():
         if c["kind"] != "sgemm":

@@ -16,6 +16,8 @@
 // fma.rn.f32x2 on row pairs, which halves the issue slots they need.
 #include "common.h"
 
+#include <atomic>
+
 namespace ulmb200 {
 
 namespace sg {
@@ -32,6 +34,11 @@ struct SgemmParams {
     float *C;
     int64_t ldc;
     int tiles_m, tiles_n;
+    int tile_first;           // first tile this launch works on
+    int ksplit;               // 1, or the number of K ranges a tile is cut into (tail launch)
+    int64_t kchunk;           // length of a K range (multiple of BK) when ksplit > 1
+    int *flags;               // ksplit > 1: one word per tile of this launch, zeroed beforehand
+    int *err;                 // device error word
 };
 
 // Global -> registers for one BMN x 16 operand tile, BMN*16/4/256 float4 per thread.
@@ -105,7 +112,7 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
     int tm, tn;
     {
         constexpr int GM = 8;
-        const int id = blockIdx.x, per_group = GM * p.tiles_n, group = id / per_group;
+        const int id = p.tile_first + (int)blockIdx.x / p.ksplit, per_group = GM * p.tiles_n, group = id / per_group;
         const int first = group * GM, gsz = min(GM, p.tiles_m - first), r = id - group * per_group;
         tm = first + r % gsz;
         tn = r / gsz;
@@ -124,12 +131,17 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
 
-    const int kt = (int)((p.k + BK - 1) / BK);
+    // a tail launch cuts K into ksplit ranges, one per CTA; part 0 applies beta, part i > 0 adds its
+    // share after part i-1 has stored its own (fixed order: the result does not depend on timing)
+    const int part = (int)blockIdx.x % p.ksplit;
+    const int64_t kbeg = p.ksplit > 1 ? part * p.kchunk : 0;
+    const int64_t kend = p.ksplit > 1 ? min(p.k, kbeg + p.kchunk) : p.k;
+    const int kt = (int)((kend - kbeg + BK - 1) / BK);
     float ra[BM * BK / NT], rb[BN * BK / NT];
     // op(A) is m x k: stored MN-contiguous when not transposed, K-contiguous when transposed.
     // op(B) is k x n: stored K-contiguous when not transposed, N-contiguous when transposed.
-    sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, 0, p.k);
-    sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, 0, p.k);
+    sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, kbeg, kend);
+    sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, kbeg, kend);
     sg_store<BM, LDA_, TA>(As, ra);
     sg_store<BN, LDB_, !TB>(Bs, rb);
     __syncthreads();
@@ -137,8 +149,8 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
     for (int kc = 0; kc < kt; ++kc) {
         const int cur = kc & 1;
         if (kc + 1 < kt) {
-            sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, (int64_t)(kc + 1) * BK, p.k);
-            sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, (int64_t)(kc + 1) * BK, p.k);
+            sg_load<BM, TA, VEC>(ra, p.A, p.lda, m0, p.m, kbeg + (int64_t)(kc + 1) * BK, kend);
+            sg_load<BN, !TB, VEC>(rb, p.B, p.ldb, n0, p.n, kbeg + (int64_t)(kc + 1) * BK, kend);
         }
         const float *a_t = As + cur * A_TILE + am;
         const float *b_t = Bs + cur * B_TILE + bn;
@@ -185,7 +197,29 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
     }
 
     // epilogue: column-major C, 4 consecutive rows per 16-byte store when legal
-    const float alpha = p.alpha, beta = p.beta;
+    const float alpha = p.alpha;
+    float beta = p.beta;
+    int *flag = nullptr;
+    if (p.ksplit > 1) {
+        flag = p.flags + (int)blockIdx.x / p.ksplit;
+        if (part > 0) {
+            // bounded wait for the previous part of this tile (about a second), then accumulate
+            __shared__ int s_ok;
+            if (threadIdx.x == 0) {
+                int ok = 0;
+                for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                    ok = (*reinterpret_cast<volatile int *>(flag) == part);
+                    if (!ok) __nanosleep(256);
+                }
+                if (!ok) atomicExch(p.err, 201);
+                s_ok = ok;
+            }
+            __syncthreads();
+            if (!s_ok) return;
+            __threadfence();
+            beta = 1.0f;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int64_t col = n0 + bn + (j & 3) + (j >> 2) * 16;
@@ -217,6 +251,11 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
             }
         }
     }
+    if (flag) {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicExch(flag, part + 1);
+    }
 }
 
 __global__ void sscal_matrix_kernel(float *C, int64_t ldc, int64_t m, int64_t n, float beta)
@@ -230,7 +269,7 @@ __global__ void sscal_matrix_kernel(float *C, int64_t ldc, int64_t m, int64_t n,
 }
 
 template <bool TA, bool TB, bool VEC>
-static int launch_fp32(cudaStream_t st, const SgemmParams &p)
+static int launch_fp32(cudaStream_t st, const SgemmParams &p, int grid)
 {
     constexpr int SMEM = 2 * (sg::A_TILE + sg::B_TILE) * (int)sizeof(float);
     auto kern = sgemm_fp32_kernel<TA, TB, VEC>;
@@ -240,7 +279,7 @@ static int launch_fp32(cudaStream_t st, const SgemmParams &p)
         ULMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         attr_done[dev] = true;
     }
-    kern<<<p.tiles_m * p.tiles_n, sg::NT, SMEM, st>>>(p);
+    kern<<<grid, sg::NT, SMEM, st>>>(p);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
     return ULMB200_OK;
@@ -281,14 +320,48 @@ int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, i
     p.tiles_n = (int)((n + sg::BN - 1) / sg::BN);
     const bool vec = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
                      lda % 4 == 0 && ldb % 4 == 0;
+    p.tile_first = 0; p.ksplit = 1; p.kchunk = 0; p.flags = nullptr;
+    p.err = device_error_word();
+    if (!p.err) return set_status(ULMB200_CUDA_ERROR);
+    // Wave quantisation: with one CTA per SM, tiles beyond the last full wave leave most SMs idle for
+    // a whole tile time (4096^3: 512 tiles = 3.46 waves of 148).  When that remainder is at most
+    // half a wave, it gets its own launch in which every tile is shared by ksplit CTAs, each taking
+    // one K range, so the tail costs 1/ksplit of a tile time.
+    const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
+    const int rem = tiles % sms;
+    int ksplit = (tiles > sms && rem > 0 && rem * 2 <= sms) ? sms / rem : 1;
+    if (ksplit > 8) ksplit = 8;
+    while (ksplit > 1 && k / ksplit < 8 * sg::BK) --ksplit;             // keep the ranges worth a launch
+    static const int allow_split = [] { const char *e = getenv("ULMB200_SGEMM_SPLITK"); return e ? atoi(e) : 1; }();
+    if (!allow_split) ksplit = 1;
     int r;
+#define ULMB_SG_LAUNCH(TA_, TB_, GRID_)                                            \
+    r = vec ? launch_fp32<TA_, TB_, true>(st, p, GRID_) : launch_fp32<TA_, TB_, false>(st, p, GRID_)
 #define ULMB_SG(TA_, TB_)                                                          \
-    r = vec ? launch_fp32<TA_, TB_, true>(st, p) : launch_fp32<TA_, TB_, false>(st, p)
+    do {                                                                           \
+        if (ksplit == 1) { ULMB_SG_LAUNCH(TA_, TB_, tiles); break; }               \
+        ULMB_SG_LAUNCH(TA_, TB_, tiles - rem);                                     \
+        if (r != ULMB200_OK) break;                                                \
+        p.tile_first = tiles - rem; p.ksplit = ksplit;                             \
+        p.kchunk = ((k + ksplit - 1) / ksplit + sg::BK - 1) / sg::BK * sg::BK;     \
+        p.flags = flags;                                                           \
+        ULMB_SG_LAUNCH(TA_, TB_, rem * ksplit);                                    \
+    } while (0)
+    int *flags = nullptr;
+    if (ksplit > 1) {
+        // eight flag areas taken in turn: launches in flight on different streams never share one
+        static std::atomic<unsigned> turn{0};
+        flags = static_cast<int *>(device_scratch(14, sizeof(int) * 256 * 8));
+        if (!flags) return set_status(ULMB200_CUDA_ERROR);
+        flags += 256 * (turn.fetch_add(1, std::memory_order_relaxed) % 8);
+        ULMB_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)rem, st));
+    }
     if (!transA && !transB)      { ULMB_SG(false, false); }
     else if (!transA && transB)  { ULMB_SG(false, true); }
     else if (transA && !transB)  { ULMB_SG(true, false); }
     else                         { ULMB_SG(true, true); }
 #undef ULMB_SG
+#undef ULMB_SG_LAUNCH
     return set_status(r);
 }
 
