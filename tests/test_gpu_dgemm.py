@@ -222,3 +222,20 @@ def test_random_shapes_property(ulm):
         ra, rb = (m if ta == "N" else k), (k if tb == "N" else n)
         check_case(ulm, ta, tb, m, n, k, alpha, beta, 30000 + 3 * it, lda=ra + int(rng.integers(0, 5)),
                    ldb=rb + int(rng.integers(0, 5)), ldc=m + int(rng.integers(0, 5)))
+
+
+def test_tail_split_tiles_shared_by_several_ctas(ulm):
+    """Tile counts a little above a multiple of the SM count: the last few 128x128 tiles are shared by
+    2-8 CTAs, one K range each, added in a fixed order.  Full comparison against the reference (the
+    split tiles are the last columns), all four transpositions once, and bit-identical repeats."""
+    # 13 x 12 = 156 tiles on 148 SMs: 8 left over
+    for i, (ta, tb, m, n, k, alpha, beta) in enumerate([("N", "N", 1664, 1536, 2100, 1.0, 0.0),
+                                                        ("T", "N", 1600, 1530, 700, -0.7, 1.3),
+                                                        ("N", "T", 1664, 1536, 1030, 1.5, 0.5),
+                                                        ("T", "T", 1601, 1500, 520, 1.0, 1.0)]):
+        check_case(ulm, ta, tb, m, n, k, alpha, beta, 88000 + 10 * i)
+    ra, rb = det_uniform(1, 1664, 2100), det_uniform(2, 2100, 1536)
+    c1, c2 = np.zeros((1664, 1536), order="F"), np.zeros((1664, 1536), order="F")
+    assert ulm.dgemm("N", "N", 1664, 1536, 2100, 1.0, ra, rb, 0.0, c1) == ulm.OK
+    assert ulm.dgemm("N", "N", 1664, 1536, 2100, 1.0, ra, rb, 0.0, c2) == ulm.OK
+    assert np.array_equal(c1, c2), "the split must not make results depend on timing"

@@ -149,6 +149,28 @@ def test_dsyrk_all_variants(ulm):
                 assert ratio <= 1.0, (n, k, uplo, tr, alpha, beta, ratio)
 
 
+def test_dsyrk_tail_split(ulm):
+    """n = 2176 is 17 tile rows: 153 tiles in the triangle, 5 more than the 148 SMs, so the last five
+    are shared by several CTAs (K ranges added in a fixed order).  Both triangles, full comparison."""
+    n, k = 2176, 1024
+    for i, (uplo, tr, alpha, beta) in enumerate([("U", "N", 1.0, 0.5), ("L", "T", -0.7, 1.3)]):
+        ra, ca = (n, k) if tr == "N" else (k, n)
+        A = np.asfortranarray(det_uniform(12500 + i, ra, ca))
+        C0 = np.asfortranarray(det_uniform(12600 + i, n, n))
+        mask = tri_mask(n, uplo)
+        C0[~mask] = ROGUE
+        want = syrk_reference(uplo, tr, n, k, alpha, A, beta, C0, n)
+        got, again = C0.copy(order="F"), C0.copy(order="F")
+        assert ulm.dsyrk(uplo, tr, n, k, alpha, A, beta, got) == ulm.OK
+        assert ulm.dsyrk(uplo, tr, n, k, alpha, A, beta, again) == ulm.OK
+        assert np.array_equal(got, again)
+        assert np.all(got[~mask] == ROGUE), "opposite triangle was written"
+        opA = op(A, tr)
+        gauge = gemm_gauge(alpha, opA, opA.T, beta, np.where(mask, C0, 0.0))
+        ratio = bound_ratio(np.where(mask, got, 0.0), np.where(mask, want, 0.0), gauge, k, EPS64)
+        assert ratio <= 1.0, (uplo, tr, ratio)
+
+
 def test_config4_dsyrk_8192_sampled_blocks(ulm, torch_cuda):
     """DSYRK uplo=U trans=N n=8192 k=4096 (alpha=1, beta=0.5), device-resident.  The CPU reference
     would need ~20 s for all of it; diagonal and off-diagonal 512-blocks are checked instead

@@ -23,6 +23,8 @@
 
 namespace ulmb200 {
 
+constexpr int kSplitSpan = 512;           // most tile ids a tail split may span (flag words per launch)
+
 struct GemmParams {
     int64_t m, n, k;
     double alpha, beta;
@@ -34,7 +36,25 @@ struct GemmParams {
     int tri;                  // 0 full, 1 upper triangle only (row<=col), 2 lower (row>=col)
     int *err;                 // device error word
     int *tile_counter;        // zeroed before the launch; hands out tiles beyond the first wave
+    // Tail split (whole tiles keep ksplit = 1): tiles with id >= split_first are each worked on by
+    // ksplit CTAs, one range of kchunk pipeline stages per CTA.  Work units are numbered
+    //   u < split_first:  tile u, all of K
+    //   u >= split_first: tile split_first + (u - split_first) / ksplit, part (u - split_first) % ksplit
+    int split_first, ksplit, kchunk;
+    int *flags;               // one word per split tile, zeroed beforehand: parts add into C in order
 };
+
+// work unit -> tile, part and the range of pipeline stages [kc0, kc1)
+__device__ __forceinline__ void unit_decode(const GemmParams &p, int unit, int kt, int &tile, int &part,
+                                            int &kc0, int &kc1)
+{
+    if (unit < p.split_first) { tile = unit; part = 0; kc0 = 0; kc1 = kt; return; }
+    const int r = unit - p.split_first;
+    tile = p.split_first + r / p.ksplit;
+    part = r % p.ksplit;
+    kc0 = part * p.kchunk;
+    kc1 = min(kt, kc0 + p.kchunk);
+}
 
 __device__ __forceinline__ void dmma_16x8x8(double (&c)[4], const double (&a)[4], const double (&b)[2])
 {
@@ -102,10 +122,10 @@ __device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32
 // then combined and stored.  With M-contiguous A the two rows a lane holds are
 // adjacent (2g, 2g+1), so a 16-byte aligned C moves them as one 16-byte access.
 template <int MAJOR_A, int MAJOR_B, int MT, int NT>
-__device__ __forceinline__ void epilogue(const GemmParams &p, int64_t m0, int64_t n0, int wm0,
+__device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64_t m0, int64_t n0, int wm0,
                                          int wn0, int lane, double (&acc)[MT][NT][4])
 {
-    const double alpha = p.alpha, beta = p.beta;
+    const double alpha = p.alpha;
     const bool use_c = beta != 0.0;
     const bool vec = MAJOR_A == MN_MAJOR && p.tri == 0 &&
                      ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 2 == 0);
@@ -171,20 +191,20 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, int64_t m0, int64_
 
 // Persistent tile order: groups of 8 tile-rows swept column by column, so the
 // CTAs running together share a handful of A and B panels in L2.
-__device__ __forceinline__ void tile_coord(int id, int tiles_m, int tiles_n, int &tm, int &tn)
+__host__ __device__ __forceinline__ void tile_coord(int id, int tiles_m, int tiles_n, int &tm, int &tn)
 {
     constexpr int GM = 8;
     const int per_group = GM * tiles_n;
     const int group = id / per_group;
     const int first = group * GM;
-    const int gsz = min(GM, tiles_m - first);
+    const int gsz = GM < tiles_m - first ? GM : tiles_m - first;
     const int r = id - group * per_group;
     tm = first + r % gsz;
     tn = r / gsz;
 }
 
 // true if the whole tile lies outside the requested triangle
-__device__ __forceinline__ bool tile_skipped(int tri, int64_t m0, int64_t n0, int bm, int bn)
+__host__ __device__ __forceinline__ bool tile_skipped(int tri, int64_t m0, int64_t n0, int bm, int bn)
 {
     if (tri == 1) return m0 > n0 + bn - 1;      // all rows below the diagonal
     if (tri == 2) return m0 + bm - 1 < n0;      // all rows above the diagonal
@@ -233,6 +253,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncthreads();
 
     const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_units = p.split_first + (num_tiles - p.split_first) * p.ksplit;
     const int kt = (int)((p.k + kBK - 1) / kBK);
 
     constexpr bool REBALANCE = (NCW == 8 && MIN_CTAS == 1);
@@ -246,19 +267,20 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // whole grid with a fixed share.
             uint32_t it = 0;
             bool live = true;
-            int tile = blockIdx.x;
+            int unit = blockIdx.x;
             while (live) {
                 bool skip = false;
                 int64_t m0 = 0, n0 = 0;
-                if (tile < num_tiles) {
-                    int tm, tn;
+                int kc0 = 0, kc1 = 1;                                // one empty stage carries the end mark
+                if (unit < num_units) {
+                    int tile, part, tm, tn;
+                    unit_decode(p, unit, kt, tile, part, kc0, kc1);
                     tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
                     m0 = (int64_t)tm * BM; n0 = (int64_t)tn * BN;
                     skip = tile_skipped(p.tri, m0, n0, BM, BN);
                 }
                 if (!skip) {
-                    const int nk = tile < num_tiles ? kt : 1;        // one empty stage carries the end mark
-                    for (int kc = 0; kc < nk; ++kc, ++it) {
+                    for (int kc = kc0; kc < kc1; ++kc, ++it) {
                         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                         if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
                             *abort_flag = 1;
@@ -266,13 +288,13 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             live = false;
                             break;
                         }
-                        if (tile >= num_tiles) {
+                        if (unit >= num_units) {
                             tile_slot[s] = -1;
                             mbar_arrive(&full[s]);
                             live = false;
                             break;
                         }
-                        tile_slot[s] = tile;
+                        tile_slot[s] = unit;
                         uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
                         mbar_expect_tx(&full[s], STAGE_BYTES);
                         const int k0 = kc * kBK;
@@ -292,7 +314,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         }
                     }
                 }
-                if (live) tile = (int)gridDim.x + atomicAdd(p.tile_counter, 1);
+                if (live) unit = (int)gridDim.x + atomicAdd(p.tile_counter, 1);
             }
             live = (*abort_flag == 0);
             if (!live) {
@@ -325,9 +347,10 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 return;
             }
         }
-        const int tile = tile_slot[it % STAGES];
-        if (tile < 0) return;
-        int tm, tn;
+        const int unit = tile_slot[it % STAGES];
+        if (unit < 0) return;
+        int tile, part, kc0, kc1, tm, tn;
+        unit_decode(p, unit, kt, tile, part, kc0, kc1);
         tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
 
@@ -339,9 +362,9 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0;
 
-        for (int kc = 0; kc < kt; ++kc, ++it) {
+        for (int kc = kc0; kc < kc1; ++kc, ++it) {
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-            if (kc > 0 && (*abort_flag || !mbar_wait(&full[s], ph))) {
+            if (kc > kc0 && (*abort_flag || !mbar_wait(&full[s], ph))) {
                 *abort_flag = 1;
                 atomicExch(p.err, 102);
                 return;
@@ -351,7 +374,32 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
         }
-        epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane, acc);
+        if (unit < p.split_first) {
+            epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+            continue;
+        }
+        // A split tile: part 0 applies beta; part i > 0 waits (bounded) until part i-1 has stored its
+        // share, then adds its own.  The order is fixed, so the result does not depend on timing.  A
+        // unit is only ever picked up by a running CTA after all units before it, so the part waited
+        // for is already being worked on.
+        int *flag = p.flags + (tile - p.split_first);
+        if (part > 0) {
+            if (threadIdx.x == 0) {
+                bool ok = false;
+                for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                    ok = *reinterpret_cast<volatile int *>(flag) >= part;
+                    if (!ok) __nanosleep(128);
+                }
+                if (!ok) { *abort_flag = 1; atomicExch(p.err, 103); }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+            if (*abort_flag) return;
+            __threadfence();
+        }
+        epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, part > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        if (threadIdx.x == 0) atomicExch(flag, part + 1);
     }
 }
 
@@ -451,7 +499,7 @@ dgemm_ldg_kernel(const GemmParams p)
         }
         __syncthreads();
     }
-    epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane, acc);
+    epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
 }
 
 // C <- beta*C (beta == 0 assigns zeros), the alpha == 0 / k == 0 quick path
@@ -515,11 +563,56 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     const int tiles = p.tiles_m * p.tiles_n;
     int sms = sm_count() - g_sm_reserve.load(std::memory_order_relaxed);
     if (sms < 1) sms = 1;
-    const int grid = tiles < sms * ctas_per_sm ? tiles : sms * ctas_per_sm;
+    GemmParams q = p;
+    const bool may_alloc = p.ksplit != 0;
+    q.split_first = tiles; q.ksplit = 1; q.kchunk = 0; q.flags = nullptr;
+    // Tail split.  With one CTA per SM the tiles beyond the last full wave leave most SMs idle for a
+    // whole tile time (a SYRK of order 8192: 2080 tiles = 14 waves + 8 tiles).  When that remainder
+    // is at most half a wave, each of its tiles is shared by 2-8 CTAs, one K range each.
+    static const int allow_split = [] { const char *e = getenv("ULMB200_DGEMM_SPLITK"); return e ? atoi(e) : 1; }();
+    const int kt = (int)((p.k + kBK - 1) / kBK);
+    if (allow_split && may_alloc && ctas_per_sm == 1 && tiles > sms && tiles <= 64 * sms && kt >= 32) {
+        // tiles that do work (a triangular update skips those outside its triangle)
+        auto real = [&](int id) {
+            int tm, tn;
+            tile_coord(id, p.tiles_m, p.tiles_n, tm, tn);
+            return !tile_skipped(p.tri, (int64_t)tm * BM, (int64_t)tn * BN, BM, BN);
+        };
+        int64_t nreal = tiles;
+        if (p.tri != 0) {
+            // count per tile row/column analytically: tile (tm, tn) is real unless wholly outside
+            nreal = 0;
+            for (int tn = 0; tn < p.tiles_n; ++tn)
+                for (int tm = 0; tm < p.tiles_m; ++tm)
+                    nreal += !tile_skipped(p.tri, (int64_t)tm * BM, (int64_t)tn * BN, BM, BN);
+        }
+        const int rem = (int)(nreal % sms);
+        if (nreal > sms && rem > 0 && rem * 2 <= sms) {
+            int ks = sms / rem;
+            if (ks > 8) ks = 8;
+            while (ks > 1 && kt / ks < 16) --ks;                 // at least 16 stages (256 k) per part
+            if (ks > 1) {
+                const int kchunk = (kt + ks - 1) / ks;
+                ks = (kt + kchunk - 1) / kchunk;                 // no empty part
+                int first = tiles, found = 0;
+                while (first > 0 && found < rem) { --first; found += real(first); }
+                if (ks > 1 && tiles - first <= kSplitSpan) {
+                    static std::atomic<unsigned> turn{0};
+                    int *flags = static_cast<int *>(device_scratch(15, sizeof(int) * kSplitSpan * 8));
+                    if (flags) {
+                        flags += kSplitSpan * (turn.fetch_add(1, std::memory_order_relaxed) % 8);
+                        ULMB_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)(tiles - first), st));
+                        q.split_first = first; q.ksplit = ks; q.kchunk = kchunk; q.flags = flags;
+                    }
+                }
+            }
+        }
+    }
+    const int64_t units = (int64_t)q.split_first + (int64_t)(tiles - q.split_first) * q.ksplit;
+    const int grid = (int)(units < (int64_t)sms * ctas_per_sm ? units : (int64_t)sms * ctas_per_sm);
     // tile counter: one of 60 words next to the error word, taken round-robin so that launches
     // in flight on different streams do not share one
     static std::atomic<unsigned> rr{0};
-    GemmParams q = p;
     q.tile_counter = p.err + 1 + (rr.fetch_add(1, std::memory_order_relaxed) % 60);
     ULMB_CUDA(cudaMemsetAsync(q.tile_counter, 0, sizeof(int), st));
     kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, q);
@@ -602,6 +695,9 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
     p.tiles_m = p.tiles_n = 0; p.tri = tri; p.tile_counter = nullptr;
+    // ksplit = 0 on the way in: the caller brought its own error word because it must not allocate
+    // device memory, so the tail split (which takes flag words from the scratch cache) stays off
+    p.split_first = 0; p.ksplit = err_word ? 0 : 1; p.kchunk = 0; p.flags = nullptr;
     p.err = err_word ? err_word : device_error_word();
     if (!p.err) return set_status(ULMB200_CUDA_ERROR);
 
