@@ -71,7 +71,7 @@ static bool on_device(const void *p)
 // ---- per-thread streams and events for staged calls -------------------------
 struct Streams {
     cudaStream_t in = nullptr, run = nullptr, out = nullptr;
-    cudaEvent_t ev[64] = {};
+    cudaEvent_t ev[128] = {};
     int dev = -1;
     bool ok = false;
 };
@@ -160,7 +160,7 @@ static int gemm_any(Launch launch, int transA, int transB, int64_t m, int64_t n,
     if (int s0 = ensure_device()) return set_status(s0);
     const bool dA = on_device(A), dB = on_device(B), dC = on_device(C);
     if (dA && dB && dC) {
-        int st = launch(nullptr, A, lda, B, ldb, C, ldc, 0, n);
+        int st = launch(nullptr, A, lda, B, ldb, C, ldc, 0, n, 0, k, true);
         if (st != ULMB200_OK) return set_status(st);
         if (int e = check_cuda(cudaStreamSynchronize(nullptr), "synchronize", __FILE__, __LINE__)) return e;
         return set_status(poll_device_error());
@@ -186,27 +186,62 @@ static int gemm_any(Launch launch, int transA, int transB, int64_t m, int64_t n,
     HostPin pc(dC ? nullptr : C, span_bytes<T>(m, n, ldc));
 
     cudaError_t e = cudaSuccess;
-    if (!dA && k > 0) e = copy_in(const_cast<T *>(Ad), ua, A, lda, rowsA, colsA, s->in);
-    if (e != cudaSuccess) return check_cuda(e, "copy A", __FILE__, __LINE__);
-
-    // column blocks: big enough to keep the GEMM efficient, small enough to overlap
+    // Column blocks of B and C: big enough to keep the GEMM efficient, small enough to overlap.  The
+    // last block is cut into four, so that less of the final copy back to the host is exposed.
     int64_t nblk = std::min<int64_t>(16, std::max<int64_t>(1, (sizeof(T) * m * n) >> 27));
     int64_t nc = round_up((n + nblk - 1) / nblk, 128);
     nblk = (n + nc - 1) / nc;
     if (nblk > 31) { nc = round_up((n + 30) / 31, 128); nblk = (n + nc - 1) / nc; }
+    struct Blk { int64_t j0, jn; };
+    Blk blocks[40];
+    int nblocks = 0;
+    for (int64_t b = 0; b < nblk; ++b) {
+        const int64_t j0 = b * nc, jn = std::min(nc, n - j0);
+        if (b == nblk - 1 && nblk >= 4 && !dC && jn >= 4 * 128) {
+            const int64_t q = round_up((jn + 3) / 4, 128);
+            for (int64_t o = 0; o < jn; o += q) blocks[nblocks++] = {j0 + o, std::min(q, jn - o)};
+        } else {
+            blocks[nblocks++] = {j0, jn};
+        }
+    }
+    // A host-resident A travels in K panels, and the first column block is multiplied panel by panel
+    // as they arrive: the product starts after one panel (and the first block of B), not after all of A.
+    const int64_t bytesA = (int64_t)sizeof(T) * rowsA * colsA;
+    int64_t npan = (!dA && k > 0) ? std::min<int64_t>(16, bytesA >> 29) : 1;
+    if (npan < 1) npan = 1;
+    while (npan > 1 && k / npan < 512) --npan;
+    const int64_t kp = round_up((k + npan - 1) / npan, 128);
+    npan = k > 0 ? (k + kp - 1) / kp : 1;
+    constexpr int kEvA = 96;                                  // events of the A panels
+
     // B^T blocks are row ranges of the stored matrix: ship B whole in that case
     if (!dB && transB && k > 0) {
         e = copy_in(const_cast<T *>(Bd), ub, B, ldb, rowsB, colsB, s->in);
         if (e != cudaSuccess) return check_cuda(e, "copy B", __FILE__, __LINE__);
     }
-    for (int64_t b = 0; b < nblk; ++b) {
-        const int64_t j0 = b * nc, jn = std::min(nc, n - j0);
+    for (int b = 0; b < nblocks; ++b) {
+        const int64_t j0 = blocks[b].j0, jn = blocks[b].jn;
         if (!dB && !transB && k > 0) e = copy_in(const_cast<T *>(Bd) + j0 * ub, ub, B + j0 * ldb, ldb, rowsB, jn, s->in);
         if (e == cudaSuccess && !dC && read_c) e = copy_in(Cd + j0 * uc, uc, C + j0 * ldc, ldc, m, jn, s->in);
         if (e == cudaSuccess) e = cudaEventRecord(s->ev[2 * b], s->in);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(s->run, s->ev[2 * b], 0);
         if (e != cudaSuccess) return check_cuda(e, "stage block", __FILE__, __LINE__);
-        int st = launch(s->run, Ad, ua, Bd, ub, Cd, uc, j0, jn);
+        int st = ULMB200_OK;
+        if (b == 0 && !dA && k > 0) {
+            // A follows the first block of B on the copy stream, one K panel at a time
+            for (int64_t pn = 0; pn < npan && st == ULMB200_OK; ++pn) {
+                const int64_t k0 = pn * kp, kn = std::min(kp, k - k0);
+                // op(A)[:, k0:k0+kn] is a column range of A as stored, or a row range of A^T as stored
+                if (!transA) e = copy_in(const_cast<T *>(Ad) + k0 * ua, ua, A + k0 * lda, lda, rowsA, kn, s->in);
+                else         e = copy_in(const_cast<T *>(Ad) + k0, ua, A + k0, lda, kn, colsA, s->in);
+                if (e == cudaSuccess) e = cudaEventRecord(s->ev[kEvA + pn], s->in);
+                if (e == cudaSuccess) e = cudaStreamWaitEvent(s->run, s->ev[kEvA + pn], 0);
+                if (e != cudaSuccess) return check_cuda(e, "stage A panel", __FILE__, __LINE__);
+                st = launch(s->run, Ad, ua, Bd, ub, Cd, uc, j0, jn, k0, kn, pn == 0);
+            }
+        } else {
+            st = launch(s->run, Ad, ua, Bd, ub, Cd, uc, j0, jn, 0, k, true);
+        }
         if (st != ULMB200_OK) { finish(s); return set_status(st); }
         if (!dC) {
             e = cudaEventRecord(s->ev[2 * b + 1], s->run);
@@ -222,10 +257,12 @@ static int dgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, do
                      const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
                      double *C, int64_t ldc)
 {
+    // columns [j0, j0+jn) of C from the K range [k0, k0+kn); beta applies on the first range only
     auto launch = [=](cudaStream_t st, const double *Ad, int64_t ua, const double *Bd, int64_t ub,
-                      double *Cd, int64_t uc, int64_t j0, int64_t jn) {
-        const double *Bblk = transB ? Bd + j0 : Bd + j0 * ub;
-        return dgemm_device(st, 0, transA, transB, m, jn, k, alpha, Ad, ua, Bblk, ub, beta,
+                      double *Cd, int64_t uc, int64_t j0, int64_t jn, int64_t k0, int64_t kn, bool first) {
+        const double *Ablk = transA ? Ad + k0 : Ad + k0 * ua;
+        const double *Bblk = transB ? Bd + j0 + k0 * ub : Bd + j0 * ub + k0;
+        return dgemm_device(st, 0, transA, transB, m, jn, kn, alpha, Ablk, ua, Bblk, ub, first ? beta : 1.0,
                             Cd + j0 * uc, uc);
     };
     return gemm_any<double>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0, C, ldc);
@@ -243,9 +280,10 @@ static int sgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, fl
 {
     const int mode = sgemm_mode();
     auto launch = [=](cudaStream_t st, const float *Ad, int64_t ua, const float *Bd, int64_t ub,
-                      float *Cd, int64_t uc, int64_t j0, int64_t jn) {
-        const float *Bblk = transB ? Bd + j0 : Bd + j0 * ub;
-        return sgemm_device(st, mode, transA, transB, m, jn, k, alpha, Ad, ua, Bblk, ub, beta,
+                      float *Cd, int64_t uc, int64_t j0, int64_t jn, int64_t k0, int64_t kn, bool first) {
+        const float *Ablk = transA ? Ad + k0 : Ad + k0 * ua;
+        const float *Bblk = transB ? Bd + j0 + k0 * ub : Bd + j0 * ub + k0;
+        return sgemm_device(st, mode, transA, transB, m, jn, kn, alpha, Ablk, ua, Bblk, ub, first ? beta : 1.0f,
                             Cd + j0 * uc, uc);
     };
     return gemm_any<float>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0f, C, ldc);
