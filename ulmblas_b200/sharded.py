@@ -124,26 +124,56 @@ class ShardedDgemm:
         self.reserve_sms = reserve_sms if self.world > 1 else 0
         self.reserve_panels = reserve_panels
 
-    def run(self, alpha, A, Br, beta, Cr):
+    def run(self, alpha, A, Br, beta, Cr, host=None):
+        """One sharded product on device buffers.
+
+        host = (hA, hB, hC), pinned host tensors shaped like A (root only, else None), Br and Cr, makes it
+        an end-to-end call: the root's A goes host -> device panel by panel, each panel broadcast as soon
+        as it has landed (the first product waits for one panel, not for all of A); every rank copies its
+        own block of B in (and of C, when beta != 0), and its block of C back out in four column pieces,
+        each as soon as the last panel's product of that piece is done.  Returns when the device work
+        is queued; the caller synchronises."""
         torch, dist, api, p = self.torch, self.dist, self.api, self.plan
         j0, j1 = p.cols
         nr = j1 - j0
         cur = torch.cuda.current_stream()
         self.compute.wait_stream(cur)
         self.comm.wait_stream(cur)
+        hA = hB = hC = None
+        if host is not None:
+            hA, hB, hC = host
+            if not hasattr(self, "h2d"):
+                self.h2d, self.d2h = torch.cuda.Stream(), torch.cuda.Stream()
+            self.h2d.wait_stream(cur)
+            self.d2h.wait_stream(cur)
+            with torch.cuda.stream(self.h2d):
+                if nr > 0:
+                    Br.copy_(hB, non_blocking=True)
+                    if beta != 0.0:
+                        Cr.copy_(hC, non_blocking=True)
+            self.compute.wait_stream(self.h2d)       # B (and C) of this rank before its first product
 
         def A_panel(l0, l1):
             return A[l0:l1, :]                      # rows of the (k, m) tensor = columns l0..l1 of A
 
+        def stage_panel(h, l0, l1):
+            if hA is not None and self.rank == self.root:
+                with torch.cuda.stream(self.h2d):
+                    h.copy_(hA[l0:l1, :], non_blocking=True)
+                self.comm.wait_stream(self.h2d)      # the broadcast (or the product) follows the copy
+
         def recv_panel(h, l0, l1):
+            stage_panel(h, l0, l1)
             with torch.cuda.stream(self.comm):
                 return dist.broadcast(h, src=self.root, group=self.group, async_op=True)
 
         launched = [0]
+        npanels = len(p.panels)
 
         def gemm(h, l0, l1, beta_l, w):
             api.set_sm_reserve(self.reserve_sms if launched[0] < self.reserve_panels else 0)
             launched[0] += 1
+            last = launched[0] == npanels
             with torch.cuda.stream(self.compute):
                 if w is not None:
                     w.wait()                         # compute stream waits for the panel, host does not
@@ -151,17 +181,47 @@ class ShardedDgemm:
                 if self.kernel_events is not None:
                     ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                     ev[0].record(self.compute)
-                api.dev_dgemm(0, 0, p.m, nr, l1 - l0, alpha, h.data_ptr(), p.m,
-                              Br.data_ptr() + 8 * l0, p.k, beta_l, Cr.data_ptr(), p.m,
-                              stream=self.compute.cuda_stream)
+                # the last panel's product goes by column pieces when C returns to the host, so that
+                # each piece can leave while the next is still being multiplied
+                pieces = [(0, nr)]
+                if last and hC is not None and nr >= 4 * ALIGN:
+                    q = ((nr + 3) // 4 + ALIGN - 1) // ALIGN * ALIGN
+                    pieces = [(c0, min(q, nr - c0)) for c0 in range(0, nr, q)]
+                for (c0, cn) in pieces:
+                    api.dev_dgemm(0, 0, p.m, cn, l1 - l0, alpha, h.data_ptr(), p.m,
+                                  Br.data_ptr() + 8 * (l0 + c0 * p.k), p.k, beta_l, Cr.data_ptr() + 8 * c0 * p.m, p.m,
+                                  stream=self.compute.cuda_stream)
+                    if last and hC is not None:
+                        done = torch.cuda.Event()
+                        done.record(self.compute)
+                        self.d2h.wait_event(done)
+                        with torch.cuda.stream(self.d2h):
+                            hC[c0:c0 + cn, :].copy_(Cr[c0:c0 + cn, :], non_blocking=True)
                 if ev is not None:
                     ev[1].record(self.compute)
                     self.kernel_events.append((ev[0], ev[1], 2.0 * p.m * nr * (l1 - l0)))
 
-        run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
+        if self.world == 1:
+            # one piece (or, with host staging, the same panels as the copy of A)
+            if hA is None:
+                run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
+            else:
+                pans = k_panels(p.k, p.kp, p.first)
+                npanels = len(pans)
+                for i, (l0, l1) in enumerate(pans):
+                    h = A_panel(l0, l1)
+                    stage_panel(h, l0, l1)
+                    self.compute.wait_stream(self.h2d)
+                    if nr > 0:
+                        gemm(h, l0, l1, beta if i == 0 else 1.0, None)
+        else:
+            run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
         api.set_sm_reserve(0)
         cur.wait_stream(self.compute)
         cur.wait_stream(self.comm)
+        if host is not None:
+            cur.wait_stream(self.h2d)
+            cur.wait_stream(self.d2h)
         return j0, j1
 
 
