@@ -613,8 +613,12 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     // tile counter: one of 60 words next to the error word, taken round-robin so that launches
     // in flight on different streams do not share one
     static std::atomic<unsigned> rr{0};
-    q.tile_counter = p.err + 1 + (rr.fetch_add(1, std::memory_order_relaxed) % 60);
-    ULMB_CUDA(cudaMemsetAsync(q.tile_counter, 0, sizeof(int), st));
+    const unsigned turn = rr.fetch_add(1, std::memory_order_relaxed);
+    q.tile_counter = p.err + 1 + (turn % 60);
+    // The counter only matters when there is more work than CTAs.  Otherwise every CTA just learns
+    // from it that nothing is left, which any non-negative value tells it -- so small products skip
+    // the memset launch (except now and then, to keep the word from creeping towards overflow).
+    if (units > grid || (turn & 1023u) < 60u) ULMB_CUDA(cudaMemsetAsync(q.tile_counter, 0, sizeof(int), st));
     kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, q);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
