@@ -62,7 +62,7 @@ int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int6
 // (level3_sm100.cu): inv holds ceil(dim/128)*128*128 doubles, W 128*n (left) or m*128 (right).
 int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                        double alpha, const double *A, int64_t lda, double *B, int64_t ldb, double *inv,
-                       double *W, int *err_word = nullptr);
+                       double *W, int *err_word = nullptr, int leaf = 128);
 
 #ifdef __CUDACC__
 // ---- device-side PTX wrappers ---------------------------------------------

@@ -52,7 +52,7 @@ constexpr int kTrtriThreads = 256;
 constexpr int kTrtriLeaf = 16;
 
 __global__ void __launch_bounds__(kTrtriThreads)
-trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *inv)
+trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *inv, int paired)
 {
     extern __shared__ double trtri_smem[];
     double *M = trtri_smem;                   // M[p*kNB + i] = L(i, p)
@@ -138,12 +138,66 @@ trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int un
     }
 
     // the full kNB x kNB block goes out (zeros outside len x len and outside the triangle)
-    double *out = inv + (int64_t)blk * kNB * kNB;
+    // paired: block blk is a diagonal block of the 256 x 256 inverse of blocks (blk & ~1, blk | 1)
+    const int old_ = paired ? 2 * kNB : kNB;
+    double *out = paired ? inv + (int64_t)(blk >> 1) * (2 * kNB) * (2 * kNB) + (blk & 1) * (kNB * old_ + kNB)
+                         : inv + (int64_t)blk * kNB * kNB;
     for (int e = t; e < kNB * kNB; e += kTrtriThreads) {
         const int i = e % kNB, j = e / kNB;           // lower view (i, j)
         const double v = (i < len && j < len && j <= i) ? M[j * kNB + i] : 0.0;
-        if (lower) out[i + j * kNB] = v;
-        else       out[j + i * kNB] = v;
+        if (lower) out[i + j * old_] = v;
+        else       out[j + i * old_] = v;
+    }
+}
+
+// Completes the 256 x 256 inverses: for the pair of diagonal blocks (A, B) with off-diagonal block C,
+//   lower-stored [[A,0],[C,B]]^-1 = [[A',0],[X,B']],  X = -B' C A'
+//   upper-stored [[A,C],[0,B]]^-1 = [[A',X],[0,B']],  X = -A' C B'
+// and the other off-diagonal block is zero.  One CTA computes a 128 x 16 strip of X: first the strip of
+// the inner product (C A' or C B'), kept in shared memory, then the outer one.  A', B' are read from the
+// 256 x 256 block itself, C from the matrix (rows and columns beyond its order count as zero).
+constexpr int kPairStrip = 16;
+
+__global__ void __launch_bounds__(256) trtri_pair_kernel(const double *A, int64_t lda, int64_t dim, int lower,
+                                                         double *inv)
+{
+    __shared__ double Ws[kPairStrip][kNB + 1];
+    const int pair = blockIdx.x / (kNB / kPairStrip), strip = blockIdx.x % (kNB / kPairStrip);
+    const int t = threadIdx.x, i = t & (kNB - 1), half = t >> 7;         // row i, 8 of the 16 columns
+    constexpr int LD = 2 * kNB;
+    double *blk = inv + (int64_t)pair * LD * LD;
+    const double *Ai = blk, *Bi = blk + kNB * LD + kNB;                  // A' and B'
+    const int64_t r0 = (int64_t)pair * LD;                               // first row/column of the pair in the matrix
+    // C as stored: lower -> rows r0+128.., columns r0..; upper -> rows r0.., columns r0+128..
+    const int64_t cr = lower ? r0 + kNB : r0, cc = lower ? r0 : r0 + kNB;
+    const double *inner = lower ? Ai : Bi;                               // right factor of the inner product
+    const double *outer = lower ? Bi : Ai;                               // left factor of the outer product
+    const int j0 = strip * kPairStrip + half * 8;
+    double acc[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = 0.0;
+    const bool row_ok = cr + i < dim;
+    for (int p = 0; p < kNB; ++p) {
+        const double c = (row_ok && cc + p < dim) ? __ldg(A + cr + i + (cc + p) * lda) : 0.0;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] += c * inner[(j0 + u) * LD + p];
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) Ws[half * 8 + u][i] = acc[u];
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = 0.0;
+    for (int p = 0; p < kNB; ++p) {
+        const double o = outer[p * LD + i];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] += o * Ws[half * 8 + u][p];
+    }
+    double *X = lower ? blk + kNB : blk + kNB * LD;                      // where X sits in the 256-block
+    double *Z = lower ? blk + kNB * LD : blk + kNB;                      // the zero block
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        X[i + (j0 + u) * LD] = -acc[u];
+        Z[i + (j0 + u) * LD] = 0.0;
     }
 }
 
@@ -165,7 +219,8 @@ struct TrsmCtx {
     int64_t m, n;             // B is m x n
     const double *A; int64_t lda;
     double *B; int64_t ldb;
-    const double *inv;        // kNB x kNB inverses of the diagonal blocks
+    const double *inv;        // inverses of the diagonal blocks, leaf x leaf each
+    int leaf;                 // 128, or 256 when the inverses have been completed pairwise
     double *W; int64_t ldw;   // leaf result before it is copied back
     int *err;                 // error word handed to the GEMM kernels (nullptr = library default)
     int status;
@@ -199,13 +254,13 @@ static void gemm_chk(TrsmCtx &c, int ta, int tb, int64_t m, int64_t n, int64_t k
 static void solve_left(TrsmCtx &c, int64_t r0, int64_t len)
 {
     if (c.status != ULMB200_OK) return;
-    if (len <= kNB) {
-        const double *iv = c.inv + (r0 / kNB) * kNB * kNB;
-        gemm_chk(c, c.trans, 0, len, c.n, len, 1.0, iv, kNB, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
+    if (len <= c.leaf) {
+        const double *iv = c.inv + (r0 / c.leaf) * c.leaf * c.leaf;
+        gemm_chk(c, c.trans, 0, len, c.n, len, 1.0, iv, c.leaf, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
         return;
     }
-    const int64_t half = ((len / 2 + kNB - 1) / kNB) * kNB;
+    const int64_t half = ((len / 2 + c.leaf - 1) / c.leaf) * c.leaf;
     const int64_t l1 = half, l2 = len - half;
     if (c.eff_lower) {
         solve_left(c, r0, l1);
@@ -226,13 +281,13 @@ static void solve_left(TrsmCtx &c, int64_t r0, int64_t len)
 static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
 {
     if (c.status != ULMB200_OK) return;
-    if (len <= kNB) {
-        const double *iv = c.inv + (c0 / kNB) * kNB * kNB;
-        gemm_chk(c, 0, c.trans, c.m, len, len, 1.0, c.B + c0 * c.ldb, c.ldb, iv, kNB, 0.0, c.W, c.ldw);
+    if (len <= c.leaf) {
+        const double *iv = c.inv + (c0 / c.leaf) * c.leaf * c.leaf;
+        gemm_chk(c, 0, c.trans, c.m, len, len, 1.0, c.B + c0 * c.ldb, c.ldb, iv, c.leaf, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
         return;
     }
-    const int64_t half = ((len / 2 + kNB - 1) / kNB) * kNB;
+    const int64_t half = ((len / 2 + c.leaf - 1) / c.leaf) * c.leaf;
     const int64_t l1 = half, l2 = len - half;
     if (c.eff_lower) {
         // X * L = B: last columns first, then B1 -= X2 * L21
@@ -250,11 +305,12 @@ static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
 }
 
 // Shared by the allocating entry point and any caller that brings its own
-// scratch: inv must hold ceil(dim/kNB) * kNB * kNB doubles, W kNB*n (left) or
-// m*kNB (right) doubles.
+// scratch, with leaf = 128: inv holds ceil(dim/128) * 128 * 128 doubles, W 128*n (left) or m*128 (right);
+// with leaf = 256 (inverses completed pairwise, half as many and larger leaf products):
+// inv holds ceil(dim/256) * 256 * 256 doubles, W 256*n or m*256.
 int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m,
                        int64_t n, double alpha, const double *A, int64_t lda, double *B,
-                       int64_t ldb, double *inv, double *W, int *err_word)
+                       int64_t ldb, double *inv, double *W, int *err_word, int leaf)
 {
     const int left = (side == 0);
     const int64_t dim = left ? m : n;
@@ -272,15 +328,28 @@ int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int uni
         ULMB_CUDA(cudaFuncSetAttribute(trtri_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done[dev] = true;
     }
-    trtri_blocks_kernel<<<nblk, kTrtriThreads, smem, st>>>(A, lda, dim, lower, unit, inv);
+    const int paired = leaf == 2 * kNB;
+    trtri_blocks_kernel<<<nblk, kTrtriThreads, smem, st>>>(A, lda, dim, lower, unit, inv, paired);
     count_launch();
+    if (paired) {
+        // an odd last block has no partner: its pair is completed against an all-zero second block,
+        // which the first kernel never wrote, so clear that corner first
+        const int npair = (nblk + 1) / 2;
+        if (nblk & 1) {
+            double *last = inv + (int64_t)(npair - 1) * leaf * leaf;
+            ULMB_CUDA(cudaMemset2DAsync(last + kNB * leaf + kNB, sizeof(double) * leaf, 0, sizeof(double) * kNB, kNB, st));
+        }
+        trtri_pair_kernel<<<npair * (kNB / kPairStrip), 256, 0, st>>>(A, lda, dim, lower, inv);
+        count_launch();
+    }
     ULMB_CUDA(cudaGetLastError());
 
     TrsmCtx c;
     c.st = st; c.left = left; c.lower = lower; c.trans = transA;
     c.eff_lower = (lower != 0) != (transA != 0);
     c.m = m; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb;
-    c.inv = inv; c.W = W; c.ldw = left ? kNB : m;
+    c.inv = inv; c.W = W; c.ldw = left ? leaf : m;
+    c.leaf = leaf;
     c.err = err_word;
     c.status = ULMB200_OK;
     if (left) solve_left(c, 0, m);
@@ -296,12 +365,14 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
     if (lda < (dim > 1 ? dim : 1) || ldb < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s = ensure_device()) return set_status(s);
-    const int64_t nblk = (dim + kNB - 1) / kNB;
-    double *inv = static_cast<double *>(device_scratch(3, (size_t)nblk * kNB * kNB * sizeof(double)));
-    const int64_t wel = (side == 0) ? (int64_t)kNB * n : m * (int64_t)kNB;
+    // 256-leaves once the triangle spans several of them; small triangles keep the 128 ones
+    const int leaf = dim > 2 * kNB ? 2 * kNB : kNB;
+    const int64_t nblk = (dim + leaf - 1) / leaf;
+    double *inv = static_cast<double *>(device_scratch(3, (size_t)nblk * leaf * leaf * sizeof(double)));
+    const int64_t wel = (side == 0) ? (int64_t)leaf * n : m * (int64_t)leaf;
     double *W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
     if (!inv || !W) return set_status(ULMB200_CUDA_ERROR);
-    return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, A, lda, B, ldb, inv, W));
+    return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, A, lda, B, ldb, inv, W, nullptr, leaf));
 }
 
 // ---------------------------------------------------------------------------
