@@ -260,7 +260,8 @@ def trsm_check(ulm, side, uplo, tr, diag, m, n, alpha, seed):
 
 def test_dtrsm_all_variants(ulm):
     seed = 20000
-    for (m, n) in [(1, 1), (7, 5), (31, 12), (130, 70), (300, 129)]:
+    # (700, 20) / (20, 700): three 256-wide diagonal blocks, the last one ragged and without a partner
+    for (m, n) in [(1, 1), (7, 5), (31, 12), (130, 70), (300, 129), (700, 20), (20, 700)]:
         for side, uplo, tr, diag in itertools.product("LR", "UL", "NT", "NU"):
             seed += 2
             trsm_check(ulm, side, uplo, tr, diag, m, n, 0.7 if (m + n) % 2 else 1.0, seed)

@@ -59,7 +59,8 @@ def test_dsymm_all_variants(ulm):
 def test_dtrmm_all_variants(ulm):
     seed = 50000
     R = ref("plain")
-    for (m, n) in [(1, 1), (7, 5), (31, 12), (130, 70), (300, 129), (257, 260)]:
+    # the last two shapes have several 256-wide diagonal blocks and a ragged last one
+    for (m, n) in [(1, 1), (7, 5), (31, 12), (130, 70), (300, 129), (257, 260), (1100, 33), (33, 1300)]:
         for side, uplo, tr, diag in itertools.product("LR", "UL", "NT", "NU"):
             seed += 2
             alpha = 0.7 if (m + n) % 2 else 1.0

@@ -587,10 +587,15 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
                     nreal += !tile_skipped(p.tri, (int64_t)tm * BM, (int64_t)tn * BN, BM, BN);
         }
         const int rem = (int)(nreal % sms);
-        if (nreal > sms && rem > 0 && rem * 2 <= sms) {
-            int ks = sms / rem;
-            if (ks > 8) ks = 8;
-            while (ks > 1 && kt / ks < 16) --ks;                 // at least 16 stages (256 k) per part
+        if (nreal > sms && rem > 0) {
+            // cut s ways (all parts resident at once: rem * s <= SMs), the last wave costs 1/s of a tile
+            // time plus a chain of s short epilogues: take the cheapest s with at least 16 stages per part
+            int ks = 1;
+            double best = 0.8;
+            for (int cand = 2; cand <= 8 && kt / cand >= 16 && rem * cand <= sms; ++cand) {
+                const double cost = (double)((rem * cand + sms - 1) / sms) / cand + 0.01 * cand;
+                if (cost < best) { best = cost; ks = cand; }
+            }
             if (ks > 1) {
                 const int kchunk = (kt + ks - 1) / ks;
                 ks = (kt + kchunk - 1) / kchunk;                 // no empty part

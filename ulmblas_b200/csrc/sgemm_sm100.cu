@@ -329,9 +329,16 @@ int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, i
     // one K range, so the tail costs 1/ksplit of a tile time.
     const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
     const int rem = tiles % sms;
-    int ksplit = (tiles > sms && rem > 0 && rem * 2 <= sms) ? sms / rem : 1;
-    if (ksplit > 8) ksplit = 8;
-    while (ksplit > 1 && k / ksplit < 8 * sg::BK) --ksplit;             // keep the ranges worth a launch
+    // cut s ways (all parts resident at once: rem * s <= SMs), the last wave costs 1/s of a tile time
+    // plus a chain of s short epilogues: take the cheapest s whose K ranges are still worth a launch
+    int ksplit = 1;
+    if (tiles > sms && rem > 0) {
+        double best = 0.8;
+        for (int cand = 2; cand <= 8 && k / cand >= 8 * sg::BK && rem * cand <= sms; ++cand) {
+            const double cost = (double)((rem * cand + sms - 1) / sms) / cand + 0.01 * cand;
+            if (cost < best) { best = cost; ksplit = cand; }
+        }
+    }
     static const int allow_split = [] { const char *e = getenv("ULMB200_SGEMM_SPLITK"); return e ? atoi(e) : 1; }();
     if (!allow_split) ksplit = 1;
     int r;
