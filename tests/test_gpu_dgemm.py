@@ -239,3 +239,15 @@ def test_tail_split_tiles_shared_by_several_ctas(ulm):
     assert ulm.dgemm("N", "N", 1664, 1536, 2100, 1.0, ra, rb, 0.0, c1) == ulm.OK
     assert ulm.dgemm("N", "N", 1664, 1536, 2100, 1.0, ra, rb, 0.0, c2) == ulm.OK
     assert np.array_equal(c1, c2), "the split must not make results depend on timing"
+
+
+def test_few_tiles_long_k_every_tile_split(ulm):
+    """A product of tall, narrow operands (few 128x128 tiles, long inner dimension): every tile is cut
+    along K over several CTAs.  All four transpositions, alpha/beta != trivial, bit-identical repeats."""
+    for i, (ta, tb) in enumerate(itertools.product("NT", "NT")):
+        check_case(ulm, ta, tb, 700, 500, 4100, -0.7, 1.3, 89000 + 10 * i)
+    A, B = det_uniform(5, 640, 8192), det_uniform(6, 8192, 384)
+    c1, c2 = np.zeros((640, 384), order="F"), np.zeros((640, 384), order="F")
+    assert ulm.dgemm("N", "N", 640, 384, 8192, 1.0, A, B, 0.0, c1) == ulm.OK
+    assert ulm.dgemm("N", "N", 640, 384, 8192, 1.0, A, B, 0.0, c2) == ulm.OK
+    assert np.array_equal(c1, c2)

@@ -535,6 +535,13 @@ int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int6
 }
 
 
+// ULMB200_DGEMM_SPLITK=0 switches the K splits off (test hook)
+static int split_allowed()
+{
+    static const int v = [] { const char *e = getenv("ULMB200_DGEMM_SPLITK"); return e ? atoi(e) : 1; }();
+    return v;
+}
+
 template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B, int STAGES, int CTAS_PER_SM>
 static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, const double *B)
 {
@@ -569,7 +576,7 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     // Tail split.  With one CTA per SM the tiles beyond the last full wave leave most SMs idle for a
     // whole tile time (a SYRK of order 8192: 2080 tiles = 14 waves + 8 tiles).  When that remainder
     // is at most half a wave, each of its tiles is shared by 2-8 CTAs, one K range each.
-    static const int allow_split = [] { const char *e = getenv("ULMB200_DGEMM_SPLITK"); return e ? atoi(e) : 1; }();
+    const int allow_split = split_allowed();
     const int kt = (int)((p.k + kBK - 1) / kBK);
     if (allow_split && may_alloc && ctas_per_sm == 1 && tiles > sms && tiles <= 64 * sms && kt >= 32) {
         // tiles that do work (a triangular update skips those outside its triangle)
@@ -613,6 +620,24 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
             }
         }
     }
+    // Few tiles and a long inner dimension (a product of tall, narrow operands): every tile is cut,
+    // so that all SMs work on it.  Same mechanism, split_first = 0.
+    if (allow_split && may_alloc && ctas_per_sm == 1 && p.tri == 0 && q.ksplit == 1 && tiles * 2 <= sms && kt >= 128) {
+        int ks = sms / tiles;
+        if (ks > 8) ks = 8;
+        while (ks > 1 && kt / ks < 64) --ks;                     // at least 64 stages (1024 k) per part
+        if (ks > 1) {
+            const int kchunk = (kt + ks - 1) / ks;
+            ks = (kt + kchunk - 1) / kchunk;
+            static std::atomic<unsigned> turn_all{0};
+            int *flags = ks > 1 ? static_cast<int *>(device_scratch(15, sizeof(int) * kSplitSpan * 8)) : nullptr;
+            if (flags) {
+                flags += kSplitSpan * (turn_all.fetch_add(1, std::memory_order_relaxed) % 8);
+                ULMB_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)tiles, st));
+                q.split_first = 0; q.ksplit = ks; q.kchunk = kchunk; q.flags = flags;
+            }
+        }
+    }
     const int64_t units = (int64_t)q.split_first + (int64_t)(tiles - q.split_first) * q.ksplit;
     const int grid = (int)(units < (int64_t)sms * ctas_per_sm ? units : (int64_t)sms * ctas_per_sm);
     // tile counter: one of 60 words next to the error word, taken round-robin so that launches
@@ -653,6 +678,12 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, int force_tile, 
     // Large tiles once they fill the machine; small tiles for small problems.
     const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
     bool big = t128 >= (int64_t)sm_count() * 3 / 4;
+    // few tiles but a long inner dimension: large tiles cut along K fill the machine better than
+    // small tiles do (768 x 768 x 8192: 30.2 TFLOP/s against 24.9 with 64 x 64 tiles); parts shorter
+    // than 1024 k do not pay (1024^3 is faster on small tiles)
+    if (p.tri == 0 && tma_ok && p.ksplit != 0 && split_allowed() && t128 * 2 <= sm_count() && p.k >= 128 * kBK &&
+        t128 * (p.k / (64 * kBK)) >= sm_count() / 2)
+        big = true;
     if (force_tile == 128) big = true;
     if (force_tile == 64) big = false;
     if (force_path == 1) tma_ok = false;
