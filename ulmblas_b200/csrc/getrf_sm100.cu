@@ -2,19 +2,21 @@
 // reference's trlsm + gemm (ulmblas/lapack/getrf.tcc:30-73, getf2.tcc:15-62,
 // laswp.tcc), kept right-looking with the reference's loop structure:
 //
-//   for each 128-column panel:   getf2 on the panel          -> getf2_cluster_kernel (+ lu_rank_update_kernel)
+//   for each 128-column panel:   getf2 on the panel          -> getf2_cluster_reg_kernel / getf2_cluster_kernel
+//                                                                (+ lu_rank_update_kernel between sub-panels)
 //                                 row swaps left and right    -> lu_perm_list_kernel + laswp_gather_kernel
 //                                 A12 <- L11^-1 A12           -> lu_trsm_unit_lower_kernel
 //                                 A22 <- A22 - A21 A12        -> device DGEMM
 //
-// Panels too tall for the cluster kernel's shared memory fall back to one cooperative launch: the CTAs split the panel's rows,
-// and per column they (1) propose their largest entry, (2) after a grid-wide
-// barrier agree on the pivot (first largest, as iamax does) while CTA 0 swaps the
-// two rows inside the panel, (3) after a second barrier scale their part of the
-// column by the reciprocal pivot (the reference's scal(1/pivot), getf2.tcc:42-44)
-// and apply the rank-1 update to their rows.  Pivots are 0-based row indices as in
-// the reference (piv[i] = row exchanged with row i); info is the 1-based index of
-// the first exactly-zero pivot, 0 if none.
+// with look-ahead: the next panel is factored on a second stream while the rest of the trailing
+// update runs (see dgetrf_device).  Panels too tall for a cluster's shared memory fall back to one
+// cooperative launch: the CTAs split the panel's rows, and per column they (1) propose their
+// largest entry, (2) after a grid-wide barrier agree on the pivot (first largest, as iamax does)
+// while CTA 0 swaps the two rows inside the panel, (3) after a second barrier scale their part of
+// the column by the reciprocal pivot (the reference's scal(1/pivot), getf2.tcc:42-44) and apply
+// the rank-1 update to their rows.  Pivots are 0-based row indices as in the reference
+// (piv[i] = row exchanged with row i); info is the 1-based index of the first exactly-zero pivot,
+// 0 if none.
 #include "common.h"
 
 #include <cooperative_groups.h>
