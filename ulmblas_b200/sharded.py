@@ -214,8 +214,10 @@ class ShardedDgemm:
                     self.compute.wait_stream(self.h2d)
                     if nr > 0:
                         gemm(h, l0, l1, beta if i == 0 else 1.0, None)
-        else:
+        elif hC is None or nr < 8 * ALIGN or len(p.panels) < 3:
             run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
+        else:
+            self._run_host_two_phase(alpha, beta, A, Br, Cr, hC, A_panel, recv_panel)
         api.set_sm_reserve(0)
         cur.wait_stream(self.compute)
         cur.wait_stream(self.comm)
@@ -223,6 +225,56 @@ class ShardedDgemm:
             cur.wait_stream(self.h2d)
             cur.wait_stream(self.d2h)
         return j0, j1
+
+
+    def _run_host_two_phase(self, alpha, beta, A, Br, Cr, hC, A_panel, recv_panel):
+        """End-to-end order of the products when C has to go back to the host.
+
+        Panel by panel, C is complete only after the last panel, so its copy back could overlap nothing
+        but that last product.  Here the first panels (about the time A needs to arrive) are still
+        applied to the whole block, and the remaining ones column piece by column piece: piece j is
+        complete -- and leaves for the host -- after (j+1)/J of that second phase, so the copies spread
+        over most of the run."""
+        torch, api, p = self.torch, self.api, self.plan
+        j0, j1 = p.cols
+        nr = j1 - j0
+        pans = list(p.panels)
+        pending = []
+        for (l0, l1) in pans:
+            h = A_panel(l0, l1)
+            pending.append((h, l0, l1, recv_panel(h, l0, l1)))
+        # phase 1 covers the first quarter to third of K
+        covered, n1 = 0, 0
+        while n1 < len(pans) - 1 and covered * 4 < p.k:
+            covered += pans[n1][1] - pans[n1][0]
+            n1 += 1
+        cs = self.compute.cuda_stream
+        npieces = 8
+        q = ((nr + npieces - 1) // npieces + ALIGN - 1) // ALIGN * ALIGN
+        pieces = [(c0, min(q, nr - c0)) for c0 in range(0, nr, q)]
+
+        def product(h, l0, l1, c0, cn, beta_l):
+            api.dev_dgemm(0, 0, p.m, cn, l1 - l0, alpha, h.data_ptr(), p.m, Br.data_ptr() + 8 * (l0 + c0 * p.k), p.k,
+                          beta_l, Cr.data_ptr() + 8 * c0 * p.m, p.m, stream=cs)
+
+        with torch.cuda.stream(self.compute):
+            for i, (h, l0, l1, w) in enumerate(pending[:n1]):
+                api.set_sm_reserve(self.reserve_sms if i < self.reserve_panels else 0)
+                if w is not None:
+                    w.wait()
+                product(h, l0, l1, 0, nr, beta if i == 0 else 1.0)
+            api.set_sm_reserve(0)
+            for (h, l0, l1, w) in pending[n1:]:
+                if w is not None:
+                    w.wait()                      # all of A is here before the second phase starts
+            for (c0, cn) in pieces:
+                for (h, l0, l1, w) in pending[n1:]:
+                    product(h, l0, l1, c0, cn, 1.0)
+                done = torch.cuda.Event()
+                done.record(self.compute)
+                self.d2h.wait_event(done)
+                with torch.cuda.stream(self.d2h):
+                    hC[c0:c0 + cn, :].copy_(Cr[c0:c0 + cn, :], non_blocking=True)
 
 
 # ---------------------------------------------------------------------------
