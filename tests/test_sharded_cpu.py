@@ -37,6 +37,18 @@ def test_k_panels():
     assert PanelPlan(4, 4, 16384, 8, 0, 4096, 1024).panels == [(0, 1024), (1024, 5120), (5120, 9216), (9216, 13312), (13312, 16384)]
 
 
+def test_two_phase_plan_for_end_to_end_runs():
+    from ulmblas_b200.sharded import two_phase_plan
+    pans = PanelPlan(4, 4, 16384, 8, 0, 4096, 1024).panels
+    n1, pieces = two_phase_plan(pans, 16384, 8192)
+    assert n1 == 2 and sum(l1 - l0 for l0, l1 in pans[:n1]) == 5120          # 31 % of K in the first phase
+    assert pieces == [(c, 1024) for c in range(0, 8192, 1024)]
+    n1, pieces = two_phase_plan(pans, 16384, 1000)                            # a narrow block: aligned pieces
+    assert pieces[0] == (0, 128) and pieces[-1] == (896, 104) and sum(c for _, c in pieces) == 1000
+    assert two_phase_plan([(0, 10), (10, 20)], 20, 256)[0] == 1               # one panel is always left for phase 2
+    assert two_phase_plan([(0, 20)], 20, 256)[0] == 0
+
+
 def test_run_panels_orders_beta_and_waits():
     plan = PanelPlan(m=6, n=300, k=10, world=2, rank=1, kp=4)
     log = []

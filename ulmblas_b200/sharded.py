@@ -49,6 +49,19 @@ def k_panels(k, kp, first=None):
     return out
 
 
+def two_phase_plan(panels, k, nr, npieces=8, align=ALIGN):
+    """(number of leading panels applied to the whole column block, [(c0, cn)] column pieces that take the
+    remaining panels one piece at a time).  The first phase covers the first quarter to third of K --
+    about the time the root needs to bring A in -- and always leaves at least one panel for the second."""
+    covered, n1 = 0, 0
+    while n1 < len(panels) - 1 and covered * 4 < k:
+        covered += panels[n1][1] - panels[n1][0]
+        n1 += 1
+    q = max(align, ((nr + npieces - 1) // npieces + align - 1) // align * align)
+    pieces = [(c0, min(q, nr - c0)) for c0 in range(0, nr, q)]
+    return n1, pieces
+
+
 @dataclass
 class PanelPlan:
     m: int
@@ -243,15 +256,8 @@ class ShardedDgemm:
         for (l0, l1) in pans:
             h = A_panel(l0, l1)
             pending.append((h, l0, l1, recv_panel(h, l0, l1)))
-        # phase 1 covers the first quarter to third of K
-        covered, n1 = 0, 0
-        while n1 < len(pans) - 1 and covered * 4 < p.k:
-            covered += pans[n1][1] - pans[n1][0]
-            n1 += 1
+        n1, pieces = two_phase_plan(pans, p.k, nr)
         cs = self.compute.cuda_stream
-        npieces = 8
-        q = ((nr + npieces - 1) // npieces + ALIGN - 1) // ALIGN * ALIGN
-        pieces = [(c0, min(q, nr - c0)) for c0 in range(0, nr, q)]
 
         def product(h, l0, l1, c0, cn, beta_l):
             api.dev_dgemm(0, 0, p.m, cn, l1 - l0, alpha, h.data_ptr(), p.m, Br.data_ptr() + 8 * (l0 + c0 * p.k), p.k,
