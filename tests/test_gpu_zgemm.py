@@ -1,7 +1,7 @@
 """Complex double GEMM on the GPU against the reference's zgemm_.
 
 Bound: the one the reference's own tester applies (test/F77/zblat3.f:3003-3160, ZMMCH), with the
-north-star constant: |C - C_ref|_1 <= 2 k eps (|alpha|_1 (|A|_1 |B|_1) + |beta|_1 |C0|_1), where
+constant 2 k eps used for the real routines: |C - C_ref|_1 <= 2 k eps (|alpha|_1 (|A|_1 |B|_1) + |beta|_1 |C0|_1), where
 |z|_1 = |re z| + |im z| elementwise."""
 import itertools
 
