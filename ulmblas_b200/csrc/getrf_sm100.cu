@@ -699,7 +699,9 @@ __global__ void __launch_bounds__(kLuThreads, 1) getf2_cluster_reg_kernel(CluArg
 }
 
 // A22 <- A22 - L21 U12 inside the 128-column panel after a sub-panel: rows below the sub-panel's
-// diagonal block, columns right of it.  64 rows per CTA; U12 (w x ncr) sits in shared memory.
+// diagonal block, columns right of it.  32 rows per CTA; U12 (w x ncr) sits in shared memory.
+constexpr int kRankRows = 32;
+
 struct RankArgs {
     double *A;            // top-left of the panel
     int64_t lda;
@@ -717,17 +719,27 @@ __global__ void __launch_bounds__(kLuThreads) lu_rank_update_kernel(RankArgs a)
         U[k][cc] = k < a.w ? U12[k + (int64_t)cc * a.lda] : 0.0;       // rows beyond w take part as zeros
     }
     __syncthreads();
-    const int64_t r = (int64_t)a.c0 + a.w + (int64_t)blockIdx.x * 64 + (t & 63);
+    // 32 rows per CTA (lane = row), the eight warps share the columns: twice as many CTAs as with 64
+    // rows each, and four loads in flight per thread instead of one
+    const int64_t r = (int64_t)a.c0 + a.w + (int64_t)blockIdx.x * kRankRows + (t & 31);
     if (r >= a.m) return;
     double l[kCluW];
 #pragma unroll
     for (int k = 0; k < kCluW; ++k) l[k] = k < a.w ? a.A[r + (int64_t)(a.c0 + k) * a.lda] : 0.0;
-    for (int cc = t >> 6; cc < a.ncr; cc += 4) {
-        double *x = a.A + r + (int64_t)(a.c0 + a.w + cc) * a.lda;
-        double acc = *x;
+    const int g = t >> 5;
+    for (int cc = g; cc < a.ncr; cc += 32) {
+        double acc[4];
 #pragma unroll
-        for (int k = 0; k < kCluW; ++k) acc -= l[k] * U[k][cc];
-        *x = acc;
+        for (int u = 0; u < 4; ++u)
+            acc[u] = cc + 8 * u < a.ncr ? a.A[r + (int64_t)(a.c0 + a.w + cc + 8 * u) * a.lda] : 0.0;
+#pragma unroll
+        for (int k = 0; k < kCluW; ++k) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] -= l[k] * U[k][(cc + 8 * u) & 127];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (cc + 8 * u < a.ncr) a.A[r + (int64_t)(a.c0 + a.w + cc + 8 * u) * a.lda] = acc[u];
     }
 }
 
@@ -999,7 +1011,7 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                     RankArgs r;
                     r.A = a.A; r.lda = lda; r.m = a.m; r.c0 = c0; r.w = q.w; r.ncr = ncr;
                     const int64_t below = a.m - c0 - q.w;
-                    lu_rank_update_kernel<<<(unsigned)((below + 63) / 64), kLuThreads, 0, ps>>>(r);
+                    lu_rank_update_kernel<<<(unsigned)((below + kRankRows - 1) / kRankRows), kLuThreads, 0, ps>>>(r);
                     count_launch();
                 }
             }
