@@ -3,6 +3,7 @@
     python -m ulmblas_b200.perf_report [--quick]
     python -m ulmblas_b200.perf_report --modes 4096     # one DGEMM per transposition mode
     python -m ulmblas_b200.perf_report --lu 2048        # two LU factorisations: the run to put under a profiler
+    python -m ulmblas_b200.perf_report --c4 8192        # DTRSM LLNN n x n and DSYRK UN n x n/2, twice each
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m ulmblas_b200.perf_report --sharded-trsm 8192  # DTRSM LLNN split over N GPUs
 
@@ -69,6 +70,27 @@ def lu_only(m):
     print(f"dgetrf n={m}: {ms:.3f} ms {2.0 * m ** 3 / 3.0 / ms * 1e-9:.2f} TFLOP/s, info = {int(piv[m].item())}")
 
 
+def config4(n):
+    """DTRSM side=L uplo=L trans=N diag=N (n x n) and DSYRK uplo=U trans=N (n, k = n/2): warm-up + one."""
+    s = torch.cuda.current_stream().cuda_stream
+    k = n // 2
+    T = _buf(n, n, torch.float64, 3, 0, dist=1, scale=1.0 / n)
+    B = _buf(n, n, torch.float64, 3, 1)
+    A = _buf(n, k, torch.float64, 3, 0)
+    C = _buf(n, n, torch.float64, 3, 2)
+    for name, flops, fn in (("dtrsm LLNN", float(n) ** 3, lambda: u.dev_dtrsm(0, 1, 0, 0, n, n, 1.0, T.data_ptr(), n, B.data_ptr(), n, stream=s)),
+                            ("dsyrk UN", float(n) * (n + 1) * k, lambda: u.dev_dsyrk(0, 0, n, k, 1.0, A.data_ptr(), n, 0.5, C.data_ptr(), n, stream=s))):
+        ms = None
+        for it in range(2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+        print(f"{name} n={n}: {ms:.3f} ms {flops / ms * 1e-9:.2f} TFLOP/s")
+
+
 def sharded_trsm(m):
     """DTRSM left/lower/no-trans/non-unit, m x m, B split by column blocks over the ranks of the
     job; A starts on rank 0 only.  Prints the whole-job rate (m^2 n / max-over-ranks device time)
@@ -125,6 +147,8 @@ def sharded_trsm(m):
 def main():
     if "--sharded-trsm" in sys.argv:
         return sharded_trsm(int(sys.argv[sys.argv.index("--sharded-trsm") + 1]))
+    if "--c4" in sys.argv:
+        return config4(int(sys.argv[sys.argv.index("--c4") + 1]))
     if "--lu" in sys.argv:
         return lu_only(int(sys.argv[sys.argv.index("--lu") + 1]))
     if "--modes" in sys.argv:
