@@ -192,8 +192,9 @@ int ulmblas_dgetrf(enum CBLAS_ORDER order, int m, int n, double *A, int ldA, int
  * i = k1..k2-1 of the n columns of A with rows piv[i*incPiv] (0-based; piv is host memory).   */
 void ulmblas_dlaswp(int n, double *A, int ldA, int k1, int k2, int *piv, int incPiv);
 
-/* replaces CBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-17 (weak)            */
+/* replace CBLAS(xerbla) and ULMBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-17 (both weak) */
 void cblas_xerbla(int info, const char *rout, const char *form, ...);
+void ulmblas_xerbla(int info, const char *rout, const char *form, ...);
 /* interfaces/blas/C/cblas_globals.cc:3-4 (the Netlib C testers read these)   */
 extern int CBLAS_CallFromC;
 extern int RowMajorStrg;
@@ -286,54 +287,43 @@ int ulmb200_strsm(void *stream, int side, int lower, int transA, int unit,
                   int64_t m, int64_t n, float alpha,
                   const float *dA, int64_t ldA, float *dB, int64_t ldB);
 
-/* Deterministic test/bench matrices: element (i,j) of matrix `mat` under
- * `seed` is a pure function of (seed, mat, i, j), identical on host and device,
- * uniform in [-1,1).  Fills the rows x cols block whose top-left element has
- * global index (row0, col0).  dist 0 = uniform[-1,1); 1 = the same scaled by
- * `scale` off the diagonal and uniform[1,2) on the diagonal (triangular
- * solver inputs).  (Plays the role of ATL_gegen in bench/l3blastst.c.)        */
-int ulmb200_fill_f64(void *stream, double *d, int64_t ld, int64_t rows, int64_t cols,
-                     uint64_t seed, uint32_t mat, int64_t row0, int64_t col0,
-                     int dist, double scale);
-int ulmb200_fill_f32(void *stream, float *d, int64_t ld, int64_t rows, int64_t cols,
-                     uint64_t seed, uint32_t mat, int64_t row0, int64_t col0);
-void ulmb200_host_fill_f64(double *h, int64_t ld, int64_t rows, int64_t cols,
-                           uint64_t seed, uint32_t mat, int64_t row0, int64_t col0,
-                           int dist, double scale);
-void ulmb200_host_fill_f32(float *h, int64_t ld, int64_t rows, int64_t cols,
-                           uint64_t seed, uint32_t mat, int64_t row0, int64_t col0);
-
-/* Largest gauge-scaled error of a result (device buffers):
- *   max_ij |C - Cref| / (|alpha| * (|A||B|)_ij + |beta| * |C0|_ij)
- * with the gauge product computed by the library's own kernel on |A|, |B|.
- * Used by the bench to check full-size results without a host copy.          */
-int ulmb200_abs_f64(void *stream, double *d, int64_t ld, int64_t rows, int64_t cols);
-
-/* Register-only throughput probes (FP64 DMMA shapes, FP64 FMA, FP32 FMA):
- * runs `iters` dependent-free instruction groups per warp on every SM and
- * returns achieved TFLOP/s in *tflops.  which: 0 dmma.m8n8k4, 1 dmma.m16n8k4,
- * 2 dmma.m16n8k8, 3 dmma.m16n8k16, 4 dfma, 5 ffma, 6 dmma+dfma mixed,
- * 7 packed fma.rn.f32x2.         */
-int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms);
-
 /* The persistent DGEMM grid normally takes every SM.  A caller that runs a collective
  * (e.g. the NCCL broadcast of the next A panel) beside it can ask the following DGEMM
  * launches to leave `sms` SMs free so that the collective's kernels are never starved;
  * 0 restores the default.  Process-wide.                                               */
 void ulmb200_set_sm_reserve(int sms);
 
-/* Failure-path self test: launches a kernel whose (short, bounded) wait can never be
- * satisfied.  The kernel gives up, records it in the device error word and returns
- * normally; the call reports ULMB200_KERNEL_FAULT and the context stays usable.       */
-int ulmb200_selftest_wait_timeout(void);
-
 /* Number of kernels this library has launched in this process so far.        */
 int64_t ulmb200_launch_count(void);
 
-/* Host-pointer staging used by the BLAS entry points: 1 = caller's buffers
- * are pinned with cudaHostRegister for the duration of the call (default),
- * 0 = copied as pageable memory.                                              */
+/* Host-pointer staging used by the BLAS entry points.  0 (the default): pageable caller
+ * buffers are copied as they are (buffers the caller has page-locked itself are always used
+ * in place, with overlapped copies).  1: pageable buffers of 1 MB and more are page-locked
+ * with cudaHostRegister for the duration of the call, which lets the copies overlap the
+ * arithmetic at the price of the registration itself.  Process-wide.                       */
 void ulmb200_set_pin_host(int on);
+
+/* Waits for `stream`, then reports whether any kernel of this library gave up on one of its
+ * bounded waits since the last check on the current device (ULMB200_KERNEL_FAULT, and the
+ * record is cleared) or not (ULMB200_OK).  The blocking BLAS entry points check by
+ * themselves; callers of the asynchronous ulmb200_* functions use this.  Allocates nothing,
+ * so it also serves ulmb200_dtrsm_noalloc.                                                  */
+int ulmb200_check_device_error(void *stream);
+
+/* Cached device work memory of the current device (staging buffers of host-pointer calls, the
+ * solvers' work areas): its size, and a call that waits for the device and gives all of it
+ * back.  ULMB200_WORKSPACE_CAP_MB in the environment bounds the cache; a request beyond the
+ * bound fails with ULMB200_CUDA_ERROR instead of allocating.                               */
+int64_t ulmb200_workspace_bytes(void);
+int     ulmb200_release_workspace(void);
+
+/* Number of device allocations (cudaMalloc) the library has made in this process.          */
+int64_t ulmb200_alloc_count(void);
+
+/* The library reads its environment variables (ULMB200_TRACE, ULMB200_SGEMM,
+ * ULMB200_WORKSPACE_CAP_MB and the ULMB200_DGEMM_* test hooks) once, at first use; this reads
+ * them again.                                                                              */
+void ulmb200_reload_env(void);
 
 #ifdef __cplusplus
 }

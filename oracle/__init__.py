@@ -25,10 +25,23 @@ _i64, _dbl, _flt, _chr, _int = C.c_int64, C.c_double, C.c_float, C.c_char, C.c_i
 _vp = C.c_void_p
 
 
+def reference_tree():
+    """Root of the ulmBLAS source tree: $ULMBLAS_REF, else a `reference` directory beside the
+    repository; None when neither holds the sources."""
+    cands = [os.environ.get("ULMBLAS_REF"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "interfaces", "blas", "F77", "gemm.cc")):
+            return c
+    return None
+
+
 def build(ref=True):
     """Compile the restatement and, if the reference tree is present, the reference."""
-    subprocess.run(["make", "-j8", "-C", _HERE, "all" if ref else "port"], check=True,
-                   stdout=subprocess.DEVNULL)
+    tree = reference_tree() if ref else None
+    cmd = ["make", "-j8", "-C", _HERE, "all" if ref else "port"]
+    if tree:
+        cmd.append("REF=" + tree)
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
 
 
 def _ld(a):
@@ -106,7 +119,8 @@ class Port:
 
 
 def ref_path(variant=""):
-    name = {"": "libulmref.so", "tiny": "libulmref_tiny.so", "plain": "libulmref_plain.so", "lapack": "libulmref_lapack.so", "cblas": "libulmref_cblas.so"}[variant]
+    name = {"": "libulmref.so", "tiny": "libulmref_tiny.so", "plain": "libulmref_plain.so", "lapack": "libulmref_lapack.so",
+            "cblas": "libulmref_cblas.so", "nox": "libulmref_nox.so", "cblas_nox": "libulmref_cblas_nox.so"}[variant]
     return os.path.join(_HERE, "_ref", name)
 
 

@@ -29,3 +29,14 @@ def torch_cuda():
         pytest.fail("this test is marked gpu but no CUDA device is visible")
     torch.cuda.init()
     return torch
+
+
+@pytest.fixture(autouse=True)
+def _library_rereads_its_environment():
+    """The library reads its ULMB200_* variables once.  Tests that set one call ``ulm.reload_env()``
+    themselves; this puts the library back on the unmodified environment afterwards (it is set up
+    before ``monkeypatch`` and therefore torn down after it)."""
+    yield
+    api = sys.modules.get("ulmblas_b200.api")
+    if api is not None:
+        api.reload_env()

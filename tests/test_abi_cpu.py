@@ -122,6 +122,103 @@ def test_bad_arguments_reach_a_caller_supplied_xerbla(ulm, tmp_path):
         assert (info, name) == (want, "cblas_dgemm"), (a, info)
 
 
+_GOLDEN_DRIVER = r"""
+import ctypes as C, json, sys
+sys.path.insert(0, %(tests)r); sys.path.insert(0, %(root)r)
+hook = C.CDLL(%(hook)r, mode=C.RTLD_GLOBAL)
+import ulmblas_b200.api as u, xerbla_cases as X
+rows = json.load(open(%(golden)r))
+cs = [(r["routine"], tuple(r["args"])) for r in rows]
+got = X.record(hook, lambda r: u.lib, cs)
+print(json.dumps(got))
+"""
+
+
+def test_error_exits_match_the_reference_case_by_case(ulm, tmp_path):
+    """Every Level-3 entry point, Fortran ABI and CBLAS in both storage orders, called with one bad
+    argument at a time (the reference tester's DCHKE procedure, test/F77/dblat3.f:1801,
+    test/C/c_d3chke.c): routine name and argument index reported to a caller-supplied xerbla must
+    equal what the compiled reference reported for the same call (tests/golden/xerbla_codes.json,
+    recorded by tests/golden/make_golden_errors.py from interfaces/blas/F77/*.cc and
+    interfaces/blas/C/*.cc -- e.g. trsm.cc:410-443, syrk.cc:232-249 of the C interface)."""
+    import json
+    golden = os.path.join(ROOT, "tests", "golden", "xerbla_codes.json")
+    rows = json.load(open(golden))
+    assert len(rows) > 700 and all(r["info"] > 0 for r in rows)
+    routines = {r["routine"] for r in rows}
+    assert {"dgemm_", "sgemm_", "zgemm_", "dtrsm_", "strsm_", "dtrmm_", "dsyrk_", "ssyrk_", "dsymm_", "dsyr2k_",
+            "cblas_dgemm", "cblas_sgemm", "cblas_zgemm", "cblas_dtrsm", "cblas_dtrmm", "cblas_dsyrk",
+            "cblas_dsymm", "cblas_dsyr2k"} <= routines
+    hook = str(tmp_path / "libxerbla_hook.so")
+    subprocess.run(["gcc", "-shared", "-fPIC", "-o", hook, HOOK_SRC], check=True)
+    code = _GOLDEN_DRIVER % dict(tests=os.path.join(ROOT, "tests"), root=ROOT, hook=hook, golden=golden)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    got = json.loads(r.stdout.strip().splitlines()[-1])
+    wrong = [(row["routine"], row["args"], (row["info"], row["name"]), tuple(g))
+             for row, g in zip(rows, got) if (row["info"], row["name"]) != tuple(g)]
+    assert not wrong, wrong[:10]
+
+
+def test_ulmblas_xerbla_is_exported_and_overridable(ulm):
+    """interfaces/blas/C/xerbla.cc:7-11 exports ULMBLAS(xerbla) beside CBLAS(xerbla)."""
+    out = subprocess.run(["nm", "-D", "--defined-only", ulm.LIB_PATH], capture_output=True, text=True).stdout
+    table = {line.split()[-1]: line.split()[-2] for line in out.splitlines() if len(line.split()) >= 3}
+    assert table.get("ulmblas_xerbla") == "W"
+
+
+def test_product_library_exports_no_bench_helpers(ulm):
+    """Generator, probes and self tests live in libulmb200_benchsupport.so, which declares them in
+    its own header and exports each of them."""
+    out = subprocess.run(["nm", "-D", "--defined-only", ulm.LIB_PATH], capture_output=True, text=True).stdout
+    names = {line.split()[-1] for line in out.splitlines() if line.split()}
+    for helper in ("ulmb200_peak_probe", "ulmb200_fill_f64", "ulmb200_host_fill_f64", "ulmb200_abs_f64",
+                   "ulmb200_selftest_wait_timeout"):
+        assert helper not in names
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "ulmb200_benchsupport.h")).read(), flags=re.S)
+    funcs = sorted({n for n in re.findall(r"\b(ulmb200_[A-Za-z0-9_]*)\s*\(", text)})
+    assert len(funcs) >= 8
+    for name in funcs:
+        assert hasattr(ulm.sup, name), name
+
+
+def test_no_multicast_in_any_kernel_source():
+    """No TMA or bulk load with cluster multicast anywhere in the library's sources: every CTA issues its
+    own plain loads and relies on L2 for reuse, so the same code runs on one GPU and on several."""
+    csrc = os.path.join(ROOT, "ulmblas_b200", "csrc")
+    hits = []
+    for base, _, files in os.walk(csrc):
+        for f in files:
+            if f.endswith((".cu", ".h", ".cuh")):
+                for i, line in enumerate(open(os.path.join(base, f), errors="replace"), 1):
+                    if "multicast" in line.lower():
+                        hits.append(f"{f}:{i}")
+    assert not hits, hits
+
+
+def test_work_schedule_model(tmp_path):
+    """CPU model of how the persistent DGEMM kernel shares the last tiles among its CTAs."""
+    exe = str(tmp_path / "schedule_model")
+    subprocess.run(["g++", "-O1", "-std=c++17", "-o", exe, os.path.join(ROOT, "tests", "cpu", "schedule_model.cpp")],
+                   check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout
+
+
+def test_trace_and_environment_reload(ulm, monkeypatch, capfd):
+    """ULMB200_TRACE=1 prints one line per call; the environment is read once and again on request."""
+    A = np.ones((4, 4), order="F")
+    monkeypatch.setenv("ULMB200_TRACE", "1")
+    ulm.reload_env()
+    ulm.dgemm("N", "T", 0, 4, 4, 1.0, A, A, 0.0, A)          # m == 0: returns before any device work
+    err = capfd.readouterr().err
+    assert "ulmb200: dgemm NT m=0 n=4 k=4" in err, err
+    monkeypatch.delenv("ULMB200_TRACE")
+    ulm.reload_env()
+    ulm.dgemm("N", "T", 0, 4, 4, 1.0, A, A, 0.0, A)
+    assert "ulmb200:" not in capfd.readouterr().err
+
+
 def test_quick_returns_need_no_device(ulm):
     A = np.ones((4, 4), order="F")
     Cm = np.full((4, 4), 3.0, order="F")
@@ -141,6 +238,8 @@ def test_no_cpu_fallback_without_a_device(ulm):
     assert ulm.dsyrk("U", "N", 4, 4, 1.0, A, 0.0, Cm) == ulm.NO_DEVICE
     assert ulm.dtrsm("L", "L", "N", "N", 4, 4, 1.0, A, Cm) == ulm.NO_DEVICE
     assert ulm.launch_count() == 0
+    assert ulm.alloc_count() == 0 and ulm.workspace_bytes() == 0
+    assert ulm.check_device_error() == ulm.NO_DEVICE
 
 
 def test_host_generator_is_deterministic_and_blockwise_consistent(ulm):

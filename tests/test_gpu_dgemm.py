@@ -107,6 +107,7 @@ def test_every_kernel_variant(ulm, tile, path, monkeypatch):
     monkeypatch.setenv("ULMB200_DGEMM_TILE", tile)
     if path:
         monkeypatch.setenv("ULMB200_DGEMM_PATH", path)
+    ulm.reload_env()
     seed = 5000
     for (m, n, k) in [(300, 260, 100), (129, 65, 17), (64, 64, 16), (200, 1, 33)]:
         for ta, tb in itertools.product("NT", "NT"):
@@ -183,7 +184,7 @@ def test_bounded_wait_reports_and_context_survives(ulm):
     """Every mbarrier wait in the kernels is bounded; when one runs out the kernel records it and
     returns.  Provoked here with a wait nothing can satisfy (no fault, no trap, no hang): the call
     must report KERNEL_FAULT and the very next product must still be right."""
-    assert ulm.lib.ulmb200_selftest_wait_timeout() == ulm.KERNEL_FAULT
+    assert ulm.sup.ulmb200_selftest_wait_timeout() == ulm.KERNEL_FAULT
     assert ulm.last_status() == ulm.KERNEL_FAULT
     check_case(ulm, "N", "T", 150, 140, 70, 1.0, 0.0, 777)
 
@@ -239,6 +240,85 @@ def test_tail_split_tiles_shared_by_several_ctas(ulm):
     assert ulm.dgemm("N", "N", 1664, 1536, 2100, 1.0, ra, rb, 0.0, c1) == ulm.OK
     assert ulm.dgemm("N", "N", 1664, 1536, 2100, 1.0, ra, rb, 0.0, c2) == ulm.OK
     assert np.array_equal(c1, c2), "the split must not make results depend on timing"
+
+
+@pytest.mark.parametrize("mode", ["2", "0"])
+def test_shared_tiles_forced_on_and_off(ulm, mode, monkeypatch):
+    """ULMB200_DGEMM_SPLITK=2 shares the tiles beyond the last full wave among all CTAs whenever the
+    schedule allows it (also where it would not pay), =0 never does.  Either way every result is
+    inside the bound; shapes cover one tile, a few tiles, a wave and a bit, ragged edges, short and
+    long inner dimensions, all four transpositions."""
+    monkeypatch.setenv("ULMB200_DGEMM_SPLITK", mode)
+    monkeypatch.setenv("ULMB200_DGEMM_TILE", "128")
+    ulm.reload_env()
+    seed = 91000
+    shapes = [(128, 128, 64), (100, 90, 33), (1024, 1024, 1024), (300, 260, 100), (1664, 1536, 50), (2000, 1300, 513),
+              (129, 4000, 700), (2304, 2304, 16), (640, 384, 4099)]
+    for i, (m, n, k) in enumerate(shapes):
+        for ta, tb in ([("N", "N"), ("T", "N"), ("N", "T"), ("T", "T")] if i % 3 == 0 else [("NT"[i % 2], "NT"[(i // 2) % 2])]):
+            seed += 3
+            check_case(ulm, ta, tb, m, n, k, -0.7, 1.3, seed)
+    A, B = det_uniform(7, 1024, 1024), det_uniform(8, 1024, 1024)
+    c1, c2 = np.zeros((1024, 1024), order="F"), np.zeros((1024, 1024), order="F")
+    assert ulm.dgemm("N", "N", 1024, 1024, 1024, 1.0, A, B, 0.0, c1) == ulm.OK
+    assert ulm.dgemm("N", "N", 1024, 1024, 1024, 1.0, A, B, 0.0, c2) == ulm.OK
+    assert np.array_equal(c1, c2), "sharing tiles must not make results depend on timing"
+
+
+def test_launches_on_two_streams_do_not_disturb_each_other(ulm, torch_cuda):
+    """One large product on stream A while 160 small ones go out on stream B: the persistent kernels'
+    tile counters and fold flags belong to the stream, so neither side can advance or reset the
+    other's.  The large result is checked on sampled columns, every small one in full."""
+    torch = torch_cuda
+    m, n, k = 4096, 4224, 2048                      # 33 x 33 tiles = 1089 = 7 waves + 53 shared tiles
+    A, B = det_uniform(61, m, k), det_uniform(62, k, n)
+    dA = torch.from_numpy(np.ascontiguousarray(A.T)).cuda()
+    dB = torch.from_numpy(np.ascontiguousarray(B.T)).cuda()
+    dC = torch.zeros((n, m), dtype=torch.float64, device="cuda")
+    sm, sn, sk = 256, 192, 96
+    a = det_uniform(63, sm, sk); b = det_uniform(64, sk, sn)
+    da = torch.from_numpy(np.ascontiguousarray(a.T)).cuda()
+    db = torch.from_numpy(np.ascontiguousarray(b.T)).cuda()
+    nsmall = 160
+    dc = torch.zeros((nsmall, sn, sm), dtype=torch.float64, device="cuda")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for rep in range(2):
+        ulm.dev_dgemm(0, 0, m, n, k, 1.0, dA.data_ptr(), m, dB.data_ptr(), k, 0.0, dC.data_ptr(), m, stream=s1.cuda_stream)
+        for i in range(nsmall):
+            ulm.dev_dgemm(0, 0, sm, sn, sk, 1.0 + i, da.data_ptr(), sm, db.data_ptr(), sk, 0.0, dc[i].data_ptr(), sm,
+                          stream=s2.cuda_stream)
+    torch.cuda.synchronize()
+    assert ulm.check_device_error() == ulm.OK
+    cols = np.sort(np.random.default_rng(5).choice(n, 48, replace=False))
+    Bs = np.asfortranarray(B[:, cols])
+    want = reference_dgemm("N", "N", m, len(cols), k, 1.0, A, Bs, 0.0, np.zeros((m, len(cols)), order="F"), m)
+    got = dC[torch.from_numpy(cols).cuda()].cpu().numpy().T
+    assert bound_ratio(got, want, gemm_gauge(1.0, A, Bs, 0.0, want), k, EPS64) <= 1.0
+    small = dc.cpu().numpy()
+    base = a @ b
+    gauge = np.abs(a) @ np.abs(b)
+    for i in range(nsmall):
+        assert bound_ratio(small[i].T, (1.0 + i) * base, (1.0 + i) * gauge, sk, EPS64) <= 1.0, i
+
+
+def test_workspace_can_be_released_and_capped(ulm, monkeypatch):
+    """Host-pointer calls stage through cached device buffers; the cache can be given back, and
+    ULMB200_WORKSPACE_CAP_MB bounds it (a request beyond the bound fails cleanly, C untouched)."""
+    check_case(ulm, "N", "N", 600, 500, 300, 1.0, 0.5, 92000)
+    assert ulm.workspace_bytes() > 0
+    assert ulm.release_workspace() == ulm.OK and ulm.workspace_bytes() == 0
+    check_case(ulm, "T", "N", 600, 500, 300, 1.0, 0.5, 92010)          # the cache grows again on demand
+    assert ulm.release_workspace() == ulm.OK
+    monkeypatch.setenv("ULMB200_WORKSPACE_CAP_MB", "1")
+    ulm.reload_env()
+    A, B = det_uniform(1, 600, 300), det_uniform(2, 300, 500)
+    Cm = np.full((600, 500), 3.0, order="F")
+    assert ulm.dgemm("N", "N", 600, 500, 300, 1.0, A, B, 0.0, Cm) == ulm.CUDA_ERROR
+    assert np.all(Cm == 3.0)
+    monkeypatch.delenv("ULMB200_WORKSPACE_CAP_MB")
+    ulm.reload_env()
+    check_case(ulm, "N", "T", 600, 500, 300, 1.0, 0.5, 92020)
 
 
 def test_few_tiles_long_k_every_tile_split(ulm):

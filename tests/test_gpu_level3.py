@@ -32,6 +32,7 @@ def reference_sgemm(ta, tb, m, n, k, alpha, A, B, beta, C0):
 def test_config2_sgemm_4096_tn(ulm, mode, monkeypatch):
     """SGEMM m=n=k=4096, transA='T', transB='N', alpha=1, beta=0, seed 7; both arithmetic modes."""
     monkeypatch.setenv("ULMB200_SGEMM", mode)
+    ulm.reload_env()
     m = n = k = 4096
     A, _ = ulm.fmat(k, m, dtype=np.float32); B, _ = ulm.fmat(k, n, dtype=np.float32)
     ulm.host_fill(A, 7, 0); ulm.host_fill(B, 7, 1)
@@ -49,6 +50,7 @@ def test_config2_sgemm_4096_tn(ulm, mode, monkeypatch):
 @pytest.mark.parametrize("mode", ["fp32", "3xtf32"])
 def test_sgemm_shapes_and_transposes(ulm, mode, monkeypatch):
     monkeypatch.setenv("ULMB200_SGEMM", mode)
+    ulm.reload_env()
     seed = 9000
     for (m, n, k) in [(1, 1, 1), (7, 12, 31), (129, 65, 17), (300, 260, 100), (128, 256, 64), (200, 1, 33)]:
         for ta, tb in itertools.product("NT", "NT"):
@@ -73,6 +75,7 @@ def test_sgemm_split_k_tail(ulm, monkeypatch):
     to several CTAs each, one K range per CTA, added in a fixed order.  Checked on sampled columns
     against the reference, and for run-to-run reproducibility (bit-identical results)."""
     monkeypatch.setenv("ULMB200_SGEMM", "fp32")
+    ulm.reload_env()
     for (m, n, k, ta, tb, alpha, beta) in [(3328, 1536, 1100, "N", "N", 1.0, 0.0),      # 156 tiles: 8 left over, 8 K ranges
                                            (3300, 1500, 300, "T", "N", 0.7, 1.3),       # ragged edges, 2 K ranges
                                            (2560, 2304, 515, "N", "T", -1.0, 1.0)]:     # 180 tiles: 32 left over, 4 ranges

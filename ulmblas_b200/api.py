@@ -21,6 +21,7 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libulmblas_b200.so")
+SUPPORT_LIB_PATH = os.path.join(_HERE, "libulmb200_benchsupport.so")
 
 OK, BAD_ARGUMENT, CUDA_ERROR, NO_DEVICE, KERNEL_FAULT, TOO_LARGE = range(6)
 SGEMM_FP32, SGEMM_3XTF32 = 0, 1
@@ -40,6 +41,16 @@ def _load():
 
 lib = _load()
 
+
+def _load_support():
+    """libulmb200_benchsupport.so: generator, probes and self tests (not part of the product)."""
+    if not os.path.exists(SUPPORT_LIB_PATH):
+        raise LibraryMissing(f"{SUPPORT_LIB_PATH} is missing: build it with `python -m ulmblas_b200.build`")
+    return C.CDLL(SUPPORT_LIB_PATH)
+
+
+sup = _load_support()
+
 _i64, _dbl, _flt, _int, _vp, _u64, _u32 = (C.c_int64, C.c_double, C.c_float, C.c_int, C.c_void_p,
                                            C.c_uint64, C.c_uint32)
 _pi, _pd, _pf, _cp = C.POINTER(C.c_int), C.POINTER(C.c_double), C.POINTER(C.c_float), C.c_char_p
@@ -48,20 +59,27 @@ lib.ulmb200_last_status.restype = _int
 lib.ulmb200_status_string.restype = C.c_char_p
 lib.ulmb200_status_string.argtypes = [_int]
 lib.ulmb200_launch_count.restype = _i64
-lib.ulmb200_selftest_wait_timeout.restype = _int
+sup.ulmb200_selftest_wait_timeout.restype = _int
+sup.ulmb200_selftest_wait_timeout_noalloc_word.restype = _int
+lib.ulmb200_alloc_count.restype = _i64
+lib.ulmb200_workspace_bytes.restype = _i64
+lib.ulmb200_release_workspace.restype = _int
+lib.ulmb200_check_device_error.argtypes = [_vp]
+lib.ulmb200_check_device_error.restype = _int
+lib.ulmb200_reload_env.restype = None
 lib.ulmb200_dgemm.argtypes = [_vp, _int, _int, _i64, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64]
 lib.ulmb200_sgemm.argtypes = [_vp, _int, _int, _int, _i64, _i64, _i64, _flt, _vp, _i64, _vp, _i64, _flt, _vp, _i64]
 lib.ulmb200_dtrsm.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
 lib.ulmb200_dtrsm_noalloc.argtypes = [_vp, _int, _int, _int, _int, _i64, _i64, _dbl, _vp, _i64, _vp, _i64]
 lib.ulmb200_dsyrk.argtypes = [_vp, _int, _int, _i64, _i64, _dbl, _vp, _i64, _dbl, _vp, _i64]
-lib.ulmb200_fill_f64.argtypes = [_vp, _vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64, _int, _dbl]
-lib.ulmb200_fill_f32.argtypes = [_vp, _vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64]
-lib.ulmb200_host_fill_f64.argtypes = [_vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64, _int, _dbl]
-lib.ulmb200_host_fill_f64.restype = None
-lib.ulmb200_host_fill_f32.argtypes = [_vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64]
-lib.ulmb200_host_fill_f32.restype = None
-lib.ulmb200_abs_f64.argtypes = [_vp, _vp, _i64, _i64, _i64]
-lib.ulmb200_peak_probe.argtypes = [_int, _int, _pd, _pd]
+sup.ulmb200_fill_f64.argtypes = [_vp, _vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64, _int, _dbl]
+sup.ulmb200_fill_f32.argtypes = [_vp, _vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64]
+sup.ulmb200_host_fill_f64.argtypes = [_vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64, _int, _dbl]
+sup.ulmb200_host_fill_f64.restype = None
+sup.ulmb200_host_fill_f32.argtypes = [_vp, _i64, _i64, _i64, _u64, _u32, _i64, _i64]
+sup.ulmb200_host_fill_f32.restype = None
+sup.ulmb200_abs_f64.argtypes = [_vp, _vp, _i64, _i64, _i64]
+sup.ulmb200_peak_probe.argtypes = [_int, _int, _pd, _pd]
 lib.ulmb200_set_sm_reserve.argtypes = [_int]
 lib.ulmb200_set_sm_reserve.restype = None
 lib.ulmb200_set_pin_host.argtypes = [_int]
@@ -273,24 +291,46 @@ def dev_dsyrk(lower, trans, n, k, alpha, dA, lda, beta, dC, ldc, stream=0):
 
 
 def dev_fill_f64(d, ld, rows, cols, seed, mat, row0=0, col0=0, dist=0, scale=1.0, stream=0):
-    _check(lib.ulmb200_fill_f64(stream, d, ld, rows, cols, seed, mat, row0, col0, dist, scale),
+    _check(sup.ulmb200_fill_f64(stream, d, ld, rows, cols, seed, mat, row0, col0, dist, scale),
            "ulmb200_fill_f64")
 
 
 def dev_fill_f32(d, ld, rows, cols, seed, mat, row0=0, col0=0, stream=0):
-    _check(lib.ulmb200_fill_f32(stream, d, ld, rows, cols, seed, mat, row0, col0), "ulmb200_fill_f32")
+    _check(sup.ulmb200_fill_f32(stream, d, ld, rows, cols, seed, mat, row0, col0), "ulmb200_fill_f32")
 
 
 def host_fill(a, seed, mat, row0=0, col0=0, dist=0, scale=1.0):
     """Fill a numpy column-major matrix with the library's deterministic generator."""
     rows, cols = a.shape
     if a.dtype == np.float64:
-        lib.ulmb200_host_fill_f64(_p(a), _ld(a), rows, cols, seed, mat, row0, col0, dist, scale)
+        sup.ulmb200_host_fill_f64(_p(a), _ld(a), rows, cols, seed, mat, row0, col0, dist, scale)
     elif a.dtype == np.float32:
-        lib.ulmb200_host_fill_f32(_p(a), _ld(a), rows, cols, seed, mat, row0, col0)
+        sup.ulmb200_host_fill_f32(_p(a), _ld(a), rows, cols, seed, mat, row0, col0)
     else:
         raise TypeError("float64 or float32 only")
     return a
+
+
+def reload_env():
+    """The library reads its ULMB200_* environment variables once; read them again."""
+    lib.ulmb200_reload_env()
+
+
+def check_device_error(stream=0):
+    """Waits for `stream`; KERNEL_FAULT if a kernel gave up on a bounded wait since the last check."""
+    return lib.ulmb200_check_device_error(stream)
+
+
+def alloc_count():
+    return lib.ulmb200_alloc_count()
+
+
+def workspace_bytes():
+    return lib.ulmb200_workspace_bytes()
+
+
+def release_workspace():
+    return lib.ulmb200_release_workspace()
 
 
 def set_sm_reserve(sms):
@@ -301,7 +341,7 @@ def set_sm_reserve(sms):
 def peak_probe(which, iters=2000):
     """Register-only throughput probe: returns (TFLOP/s, ms)."""
     tf, ms = _dbl(0.0), _dbl(0.0)
-    _check(lib.ulmb200_peak_probe(which, iters, C.byref(tf), C.byref(ms)), "ulmb200_peak_probe")
+    _check(sup.ulmb200_peak_probe(which, iters, C.byref(tf), C.byref(ms)), "ulmb200_peak_probe")
     return tf.value, ms.value
 
 

@@ -1,9 +1,12 @@
-"""Builds libulmblas_b200.so in-tree with nvcc for sm_100a (no JIT, no torch extension).
+"""Builds the libraries in-tree with nvcc for sm_100a (no JIT, no torch extension).
 
     python -m ulmblas_b200.build [--force] [--verbose]
 
-Every .cu under csrc/ is compiled to an object (in parallel) and linked into one shared
-library that exports the BLAS symbols and the ulmb200_* device ABI.
+Every .cu under csrc/ is compiled to an object (in parallel) and linked into
+libulmblas_b200.so, the product: the BLAS symbols and the ulmb200_* device ABI
+(include/ulmblas_b200.h).  The .cu files under csrc/support/ go into
+libulmb200_benchsupport.so (include/ulmb200_benchsupport.h): matrix generator, throughput
+probes and failure-path self tests for the bench and the tests, linked against the product.
 """
 import concurrent.futures
 import os
@@ -15,6 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libulmblas_b200.so")
+SUPPORT_LIB = os.path.join(HERE, "libulmb200_benchsupport.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -33,6 +37,11 @@ def sources():
     return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
+def support_sources():
+    d = os.path.join(CSRC, "support")
+    return sorted(os.path.join("support", f) for f in os.listdir(d) if f.endswith(".cu"))
+
+
 def _stale(target, deps):
     if not os.path.exists(target):
         return True
@@ -44,13 +53,15 @@ def build(force=False, verbose=False):
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")]
+    headers += [os.path.join(CSRC, "support", f) for f in os.listdir(os.path.join(CSRC, "support")) if f.endswith(".h")]
     headers.append(os.path.join(HERE, "..", "include", "ulmblas_b200.h"))
+    headers.append(os.path.join(HERE, "..", "include", "ulmb200_benchsupport.h"))
     jobs = []
-    objs = []
-    for src in sources():
+    objs, sobjs = [], []
+    for src in sources() + support_sources():
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, src[:-3] + ".o")
-        objs.append(o)
+        o = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+        (sobjs if src.startswith("support") else objs).append(o)
         if force or _stale(o, [s] + headers):
             cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
@@ -65,13 +76,15 @@ def build(force=False, verbose=False):
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
             if r.returncode != 0:
                 raise RuntimeError("nvcc failed on " + cmd[-3])
-    if force or jobs or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
-                                                      "-Xcompiler", "-fPIC"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("link failed")
+    arch = ["-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
+    links = [(LIB, objs, []),
+             (SUPPORT_LIB, sobjs, ["-L" + HERE, "-lulmblas_b200", "-Xlinker", "-rpath=$ORIGIN"])]
+    for lib, obs, extra in links:
+        if force or jobs or _stale(lib, obs):
+            r = subprocess.run([nvcc, "-shared", "-o", lib] + obs + arch + extra, capture_output=True, text=True)
+            if r.returncode != 0:
+                sys.stderr.write(r.stdout + r.stderr)
+                raise RuntimeError("link failed: " + lib)
     return LIB
 
 

@@ -18,6 +18,7 @@
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
+#include <time.h>
 #include <vector>
 
 namespace ulmb200 {
@@ -48,13 +49,22 @@ int dsyr2k_device(cudaStream_t st, int lower, int trans, int64_t n, int64_t k, d
 
 static int g_pin_host = 0;
 
-// The blocking BLAS entry points share the per-device staging and work buffers, so calls from
-// different host threads take turns (the reference guards its memory pool the same way,
-// ulmblas/auxiliary/memorypool.tcc:43,57).  Callers of the asynchronous ulmb200_* device ABI
-// order their own work: routines that use work buffers (dtrsm, dtrmm, dsymm, dgetrf, 3xTF32
-// sgemm) must not overlap on one device.
-static std::recursive_mutex g_call_mu;
-#define ULMB_SERIALISE std::lock_guard<std::recursive_mutex> ulmb_call_lock(g_call_mu)
+// The blocking BLAS entry points share one set of staging and work buffers per device, so calls
+// from different host threads on the SAME device take turns (the reference guards its memory pool
+// the same way, ulmblas/auxiliary/memorypool.tcc:43,57); calls on different devices run side by
+// side, each thread on its own streams.  Callers of the asynchronous ulmb200_* device ABI order
+// their own work: routines that use work buffers (dtrsm, dtrmm, dsymm, dgetrf, 3xTF32 sgemm) must
+// not overlap on one device.
+static std::recursive_mutex g_call_mu[kMaxDevices];
+#define ULMB_SERIALISE std::lock_guard<std::recursive_mutex> ulmb_call_lock(g_call_mu[current_device()])
+
+// wall-clock milliseconds for the trace lines
+static double now_ms()
+{
+    timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+}
 
 // ---- where does a pointer live? -------------------------------------------
 static bool on_device(const void *p)
@@ -69,20 +79,22 @@ static bool on_device(const void *p)
 }
 
 // ---- per-thread streams and events for staged calls -------------------------
+// One set per calling thread and device, created on first use with that device current.
 struct Streams {
     cudaStream_t in = nullptr, run = nullptr, out = nullptr;
     cudaEvent_t ev[128] = {};
     int dev = -1;
     bool ok = false;
 };
-static thread_local Streams t_streams;
+static thread_local std::vector<Streams *> t_streams;
 
 static Streams *streams()
 {
-    Streams &s = t_streams;
     const int dev = current_device();
-    if (s.ok && s.dev == dev) return &s;
-    if (s.ok) return &s;     // one device per thread for staged calls
+    if ((int)t_streams.size() <= dev) t_streams.resize(dev + 1, nullptr);
+    if (!t_streams[dev]) t_streams[dev] = new Streams;
+    Streams &s = *t_streams[dev];
+    if (s.ok) return &s;
     if (cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaStreamCreateWithFlags(&s.run, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
@@ -153,12 +165,17 @@ static int finish(Streams *s)
 // copy-out stream while the next block computes.
 template <typename T, typename Launch>
 static int gemm_any(Launch launch, int transA, int transB, int64_t m, int64_t n, int64_t k,
-                    const T *A, int64_t lda, const T *B, int64_t ldb, bool read_c, T *C, int64_t ldc)
+                    const T *A, int64_t lda, const T *B, int64_t ldb, bool read_c, T *C, int64_t ldc,
+                    bool scale_only)
 {
     ULMB_SERIALISE;
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
-    const bool dA = on_device(A), dB = on_device(B), dC = on_device(C);
+    // alpha == 0 or k == 0: only C <- beta*C happens and A and B are never touched, as in the
+    // reference (ulmblas/level3/gemm.tcc:52-55) -- callers may pass dummy pointers for them
+    if (scale_only) { A = nullptr; B = nullptr; k = 0; }
+    const bool dC = on_device(C);
+    const bool dA = scale_only ? dC : on_device(A), dB = scale_only ? dC : on_device(B);
     if (dA && dB && dC) {
         int st = launch(nullptr, A, lda, B, ldb, C, ldc, 0, n, 0, k, true);
         if (st != ULMB200_OK) return set_status(st);
@@ -265,13 +282,18 @@ static int dgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, do
         return dgemm_device(st, 0, transA, transB, m, jn, kn, alpha, Ablk, ua, Bblk, ub, first ? beta : 1.0,
                             Cd + j0 * uc, uc);
     };
-    return gemm_any<double>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0, C, ldc);
+    const double t0 = settings().trace ? now_ms() : 0.0;
+    const int st = gemm_any<double>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0, C, ldc,
+                                    alpha == 0.0 || k == 0);
+    trace("dgemm %c%c m=%lld n=%lld k=%lld lda=%lld ldb=%lld ldc=%lld alpha=%g beta=%g status=%d %.3f ms",
+          transA ? 'T' : 'N', transB ? 'T' : 'N', (long long)m, (long long)n, (long long)k, (long long)lda,
+          (long long)ldb, (long long)ldc, alpha, beta, st, now_ms() - t0);
+    return st;
 }
 
 static int sgemm_mode()
 {
-    const char *e = getenv("ULMB200_SGEMM");
-    return (e && (e[0] == '3' || e[0] == 't')) ? ULMB200_SGEMM_3XTF32 : ULMB200_SGEMM_FP32;
+    return settings().sgemm_3xtf32 ? ULMB200_SGEMM_3XTF32 : ULMB200_SGEMM_FP32;
 }
 
 static int sgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, float alpha,
@@ -286,7 +308,13 @@ static int sgemm_any(int transA, int transB, int64_t m, int64_t n, int64_t k, fl
         return sgemm_device(st, mode, transA, transB, m, jn, kn, alpha, Ablk, ua, Bblk, ub, first ? beta : 1.0f,
                             Cd + j0 * uc, uc);
     };
-    return gemm_any<float>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0f, C, ldc);
+    const double t0 = settings().trace ? now_ms() : 0.0;
+    const int st = gemm_any<float>(launch, transA, transB, m, n, k, A, lda, B, ldb, beta != 0.0f, C, ldc,
+                                   alpha == 0.0f || k == 0);
+    trace("sgemm %c%c m=%lld n=%lld k=%lld mode=%s status=%d %.3f ms", transA ? 'T' : 'N', transB ? 'T' : 'N',
+          (long long)m, (long long)n, (long long)k, mode == ULMB200_SGEMM_3XTF32 ? "3xtf32" : "fp32", st,
+          now_ms() - t0);
+    return st;
 }
 
 // Staging for the two-operand routines (whole matrices; no pipelining).
@@ -296,11 +324,14 @@ static int dsyrk_any(int lower, int trans, int64_t n, int64_t k, double alpha, c
     ULMB_SERIALISE;
     if (n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
-    const bool dA = on_device(A), dC = on_device(C);
+    // alpha == 0 or k == 0 only scales the triangle; A is not touched (syurk.tcc:44-51)
+    const bool scale_only = alpha == 0.0 || k == 0;
+    if (scale_only) { k = 0; alpha = 0.0; }
+    const bool dC = on_device(C), dA = scale_only ? true : on_device(A);
     Streams *s = streams();
     if (!s) return set_status(ULMB200_CUDA_ERROR);
     const int64_t rowsA = trans ? k : n, colsA = trans ? n : k;
-    const double *Ad = A;
+    const double *Ad = scale_only ? C : A;
     double *Cd = C;
     int64_t ua = lda, uc = ldc;
     if (!dA) { ua = round_up(std::max<int64_t>(rowsA, 1), 2); Ad = static_cast<double *>(device_scratch(0, 8 * ua * std::max<int64_t>(colsA, 1))); }
@@ -327,11 +358,13 @@ static int dtrsm_any(int side, int lower, int transA, int unit, int64_t m, int64
     ULMB_SERIALISE;
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s0 = ensure_device()) return set_status(s0);
-    const bool dA = on_device(A), dB = on_device(B);
+    // alpha == 0 assigns zeros to B and reads neither A nor B (trlsm.tcc:46-49)
+    const bool zero_only = alpha == 0.0;
+    const bool dB = on_device(B), dA = zero_only ? true : on_device(A);
     Streams *s = streams();
     if (!s) return set_status(ULMB200_CUDA_ERROR);
     const int64_t dim = side == 0 ? m : n;
-    const double *Ad = A;
+    const double *Ad = zero_only ? B : A;
     double *Bd = B;
     int64_t ua = lda, ub = ldb;
     if (!dA) { ua = round_up(dim, 2); Ad = static_cast<double *>(device_scratch(0, 8 * ua * dim)); }
@@ -341,7 +374,7 @@ static int dtrsm_any(int side, int lower, int transA, int unit, int64_t m, int64
     // The whole square of A is shipped, but the kernels only ever read the
     // referenced triangle (and skip the diagonal when it is unit).
     if (!dA) e = copy_in(const_cast<double *>(Ad), ua, A, lda, dim, dim, s->run);
-    if (e == cudaSuccess && !dB) e = copy_in(Bd, ub, B, ldb, m, n, s->run);
+    if (e == cudaSuccess && !dB && !zero_only) e = copy_in(Bd, ub, B, ldb, m, n, s->run);
     if (e != cudaSuccess) return check_cuda(e, "copy in", __FILE__, __LINE__);
     int st = dtrsm_device(s->run, side, lower, transA, unit, m, n, alpha, Ad, ua, Bd, ub);
     if (st != ULMB200_OK) { finish(s); return set_status(st); }
@@ -548,6 +581,14 @@ __attribute__((weak)) void xerbla_(const char rout[6], const int *info)
 }
 
 __attribute__((weak)) void cblas_xerbla(int info, const char *rout, const char *form, ...)
+{
+    (void)form;
+    fprintf(stderr, "Parameter %d to routine %s was incorrect\n", info, rout);
+}
+
+// ULMBLAS(xerbla), interfaces/blas/C/xerbla.cc:7-11: the reference's libcblas exports it beside
+// CBLAS(xerbla) with the same text
+__attribute__((weak)) void ulmblas_xerbla(int info, const char *rout, const char *form, ...)
 {
     (void)form;
     fprintf(stderr, "Parameter %d to routine %s was incorrect\n", info, rout);

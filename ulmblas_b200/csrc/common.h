@@ -30,11 +30,44 @@ int  sm_count();                         // SMs of the current device
 // Device-side error word (one per device, zero-initialised).  A kernel whose
 // bounded wait runs out stores a non-zero code here and returns normally.
 int *device_error_word();                // device pointer, for the current device
-int  poll_device_error();                // syncs nothing; reads the word with a blocking copy
+void register_error_word(int *dev_word); // a further word poll_device_error() should read (current device)
+int *registered_error_word(int i);       // i-th registered word of the current device or nullptr
+int  poll_device_error();                // syncs nothing; reads the words with blocking copies, allocates nothing
+int  release_workspace(int64_t *freed_bytes);
+int64_t workspace_bytes();
 
-// Cached scratch buffers in device memory (grow-only, one set per device),
-// the counterpart of the reference's MemoryPool (ulmblas/auxiliary/memorypool.tcc).
+// Cached scratch buffers in device memory (one set per device, grown on demand, given back
+// by ulmb200_release_workspace), the counterpart of the reference's MemoryPool
+// (ulmblas/auxiliary/memorypool.tcc).  Returns nullptr when the allocation fails or would
+// take the cache beyond ULMB200_WORKSPACE_CAP_MB.
 void *device_scratch(int slot, size_t bytes);
+int64_t alloc_count();                   // device allocations made by the library so far
+
+// Scheduler words of the persistent GEMM kernels: per CUDA stream one zero-initialised block of
+// kSchedWords ints in device memory -- [0] tile counter, [1] CTAs that have finished,
+// [2 ...] fold flags of tiles shared by several CTAs.  Kernels leave every word at zero when
+// they end, so launches that follow each other on one stream reuse the block without a
+// memset, and launches on different streams never share one.  nullptr when no block is left
+// (more than kSchedSlots streams in use on the device): the caller then schedules statically.
+constexpr int kSchedFlags = 320;
+constexpr int kSchedWords = 384;
+constexpr int kSchedSlots = 256;
+int *sched_words(cudaStream_t st);
+
+// Settings taken from the environment, read at first use and again by ulmb200_reload_env():
+//   ULMB200_TRACE=1              one line per call on stderr
+//   ULMB200_SGEMM=fp32|3xtf32    arithmetic of sgemm_ / cblas_sgemm
+//   ULMB200_WORKSPACE_CAP_MB=n   upper limit of the cached device work memory
+//   ULMB200_DGEMM_TILE=64|128, ULMB200_DGEMM_PATH=ldg, ULMB200_DGEMM_SPLITK=0   (test hooks)
+struct Settings {
+    int trace = 0;
+    int sgemm_3xtf32 = 0;
+    int64_t workspace_cap = -1;          // bytes, -1 = none
+    int dgemm_tile = 0, dgemm_ldg = 0, dgemm_split = 1;
+    int sgemm_path = 0;                  // 0 auto, 1 force the plain-load kernel
+};
+const Settings &settings();
+void trace(const char *fmt, ...) __attribute__((format(printf, 1, 2)));
 
 // cuTensorMapEncodeTiled fetched through the runtime (no link against libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -126,7 +159,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
     return false;
 }
 
-// One 2-D TMA tile load, no multicast; completion is signalled on `bar`.
+// One 2-D TMA tile load for this CTA alone; completion is signalled on `bar`.
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int32_t x,
                                             int32_t y, uint64_t *bar)
 {

@@ -18,12 +18,11 @@
 //                     8-byte global loads; any alignment, any ld.
 #include "common.h"
 #include "tile_layout.h"
+#include "dgemm_schedule.h"
 
 #include <atomic>
 
 namespace ulmb200 {
-
-constexpr int kSplitSpan = 512;           // most tile ids a tail split may span (flag words per launch)
 
 struct GemmParams {
     int64_t m, n, k;
@@ -35,25 +34,24 @@ struct GemmParams {
     int tiles_m, tiles_n;
     int tri;                  // 0 full, 1 upper triangle only (row<=col), 2 lower (row>=col)
     int *err;                 // device error word
-    int *tile_counter;        // zeroed before the launch; hands out tiles beyond the first wave
-    // Tail split (whole tiles keep ksplit = 1): tiles with id >= split_first are each worked on by
-    // ksplit CTAs, one range of kchunk pipeline stages per CTA.  Work units are numbered
-    //   u < split_first:  tile u, all of K
-    //   u >= split_first: tile split_first + (u - split_first) / ksplit, part (u - split_first) % ksplit
-    int split_first, ksplit, kchunk;
-    int *flags;               // one word per split tile, zeroed beforehand: parts add into C in order
+    // Scheduler words of this launch's stream, all zero between launches (the kernel puts them
+    // back): [0] hands out work units beyond the first wave, [1] counts CTAs that are done,
+    // [2 + r] is the fold flag of shared tile r.  nullptr: units go round-robin by CTA index.
+    int *sched;
+    int dynamic;              // 1: units beyond the CTA's own index come from sched[0]
+    // Work units.  u < split_first: tile u, all of K.  u >= split_first: stream unit
+    // j = u - split_first of nsu.  The region_tiles tiles that do work among the tile ids
+    // >= split_first form, stage by stage, one sequence of region_tiles * kt pipeline stages,
+    // and stream unit j takes the j-th of nsu equal shares of it -- so the tiles beyond the
+    // last full wave are shared evenly by all CTAs instead of idling most of them.
+    int split_first, nsu, region_tiles;
+    unsigned short rtile[kRegionMax];   // tri != 0: tile id - split_first of region tile r
 };
 
-// work unit -> tile, part and the range of pipeline stages [kc0, kc1)
-__device__ __forceinline__ void unit_decode(const GemmParams &p, int unit, int kt, int &tile, int &part,
-                                            int &kc0, int &kc1)
+// tile id of region tile r
+__device__ __forceinline__ int region_tile(const GemmParams &p, int r)
 {
-    if (unit < p.split_first) { tile = unit; part = 0; kc0 = 0; kc1 = kt; return; }
-    const int r = unit - p.split_first;
-    tile = p.split_first + r / p.ksplit;
-    part = r % p.ksplit;
-    kc0 = part * p.kchunk;
-    kc1 = min(kt, kc0 + p.kchunk);
+    return p.split_first + (p.tri ? (int)p.rtile[r] : r);
 }
 
 __device__ __forceinline__ void dmma_16x8x8(double (&c)[4], const double (&a)[4], const double (&b)[2])
@@ -252,71 +250,91 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncthreads();
 
-    const int num_tiles = p.tiles_m * p.tiles_n;
-    const int num_units = p.split_first + (num_tiles - p.split_first) * p.ksplit;
+    const int num_units = p.split_first + p.nsu;
     const int kt = (int)((p.k + kBK - 1) / kBK);
 
     constexpr bool REBALANCE = (NCW == 8 && MIN_CTAS == 1);
+    constexpr bool SHARE = (MIN_CTAS == 1);          // only the one-CTA-per-SM shape shares tiles
     if (warp >= NCW) {
         // ---------------- producer warpgroup ----------------
         if (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp == NCW && lane == 0) {
-            // Tiles are handed out dynamically: the first one is the CTA's own index, the rest come
+            // Units are handed out dynamically: the first one is the CTA's own index, the rest come
             // from a global counter.  A CTA that starts late (its SM was busy with another
-            // kernel, e.g. a collective) then simply takes fewer tiles instead of holding up the
+            // kernel, e.g. a collective) then simply takes fewer units instead of holding up the
             // whole grid with a fixed share.
             uint32_t it = 0;
             bool live = true;
-            int unit = blockIdx.x;
-            while (live) {
-                bool skip = false;
-                int64_t m0 = 0, n0 = 0;
-                int kc0 = 0, kc1 = 1;                                // one empty stage carries the end mark
-                if (unit < num_units) {
-                    int tile, part, tm, tn;
-                    unit_decode(p, unit, kt, tile, part, kc0, kc1);
-                    tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
-                    m0 = (int64_t)tm * BM; n0 = (int64_t)tn * BN;
-                    skip = tile_skipped(p.tri, m0, n0, BM, BN);
-                }
-                if (!skip) {
-                    for (int kc = kc0; kc < kc1; ++kc, ++it) {
-                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                        if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
-                            *abort_flag = 1;
-                            atomicExch(p.err, 101);
-                            live = false;
-                            break;
-                        }
-                        if (unit >= num_units) {
-                            tile_slot[s] = -1;
-                            mbar_arrive(&full[s]);
-                            live = false;
-                            break;
-                        }
-                        tile_slot[s] = unit;
-                        uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
-                        mbar_expect_tx(&full[s], STAGE_BYTES);
-                        const int k0 = kc * kBK;
-                        if (MAJOR_A == K_MAJOR) {
-                            tma_load_2d(sa, &tmA, k0, (int)m0, &full[s]);
-                        } else {
+            // loads the stages [kc0, kc1) of the tile at (m0, n0); false once the kernel has given up
+            auto load_piece = [&](int unit, int64_t m0, int64_t n0, int kc0, int kc1) -> bool {
+                for (int kc = kc0; kc < kc1; ++kc, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
+                        *abort_flag = 1;
+                        atomicExch(p.err, 101);
+                        return false;
+                    }
+                    tile_slot[s] = unit;
+                    uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    const int k0 = kc * kBK;
+                    if (MAJOR_A == K_MAJOR) {
+                        tma_load_2d(sa, &tmA, k0, (int)m0, &full[s]);
+                    } else {
 #pragma unroll
-                            for (int b = 0; b < BM / 16; ++b)
-                                tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0, &full[s]);
-                        }
-                        if (MAJOR_B == K_MAJOR) {
-                            tma_load_2d(sb, &tmB, k0, (int)n0, &full[s]);
-                        } else {
+                        for (int b = 0; b < BM / 16; ++b)
+                            tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0, &full[s]);
+                    }
+                    if (MAJOR_B == K_MAJOR) {
+                        tma_load_2d(sb, &tmB, k0, (int)n0, &full[s]);
+                    } else {
 #pragma unroll
-                            for (int b = 0; b < BN / 16; ++b)
-                                tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0, &full[s]);
-                        }
+                        for (int b = 0; b < BN / 16; ++b)
+                            tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0, &full[s]);
                     }
                 }
-                if (live) unit = (int)gridDim.x + atomicAdd(p.tile_counter, 1);
+                return true;
+            };
+            int unit = blockIdx.x;
+            while (live && unit < num_units) {
+                if (!SHARE || unit < p.split_first) {
+                    int tm, tn;
+                    tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
+                    const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+                    if (!tile_skipped(p.tri, m0, n0, BM, BN)) live = load_piece(unit, m0, n0, 0, kt);
+                } else {
+                    StreamWalk walk(p.region_tiles, p.nsu, unit - p.split_first, kt);
+                    Piece pc;
+                    while (live && walk.next(pc)) {
+                        int tm, tn;
+                        tile_coord(region_tile(p, pc.r), p.tiles_m, p.tiles_n, tm, tn);
+                        live = load_piece(unit, (int64_t)tm * BM, (int64_t)tn * BN, pc.kc0, pc.kc1);
+                    }
+                }
+                if (live) unit = p.dynamic ? (int)gridDim.x + atomicAdd(p.sched, 1) : unit + (int)gridDim.x;
             }
-            live = (*abort_flag == 0);
+            if (live) {
+                // one empty stage carries the end mark to the consumers
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
+                    *abort_flag = 1;
+                    atomicExch(p.err, 101);
+                    live = false;
+                } else {
+                    tile_slot[s] = -1;
+                    mbar_arrive(&full[s]);
+                }
+            }
+            if (p.dynamic) {
+                // every CTA has taken its last number by the time it counts itself done; the last one
+                // to do so puts both words back to zero for the next launch on this stream
+                __threadfence();
+                if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+                    atomicExch(p.sched, 0);
+                    atomicExch(p.sched + 1, 0);
+                }
+            }
+            live = live && (*abort_flag == 0);
             if (!live) {
                 // give loads already in flight a bounded time to land before the CTA retires
                 for (int s = 0; s < STAGES; ++s)
@@ -337,8 +355,32 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t smem_base = smem_u32(smem);
 
     uint32_t it = 0;
+    double acc[MT][NT][4];
+    // multiplies the stages [kc0, kc1) of one tile into acc (zeroed first); false once the kernel has given up
+    auto run_piece = [&](int kc0, int kc1, bool first_stage_ready) -> bool {
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0;
+        for (int kc = kc0; kc < kc1; ++kc, ++it) {
+            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+            if (!(first_stage_ready && kc == kc0) && (*abort_flag || !mbar_wait(&full[s], ph))) {
+                *abort_flag = 1;
+                atomicExch(p.err, 102);
+                return false;
+            }
+            const uint32_t sA = smem_base + s * STAGE_BYTES;
+            mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        return true;
+    };
+
     for (;;) {
-        // the first stage of a tile tells which tile it is
+        // the first stage of a unit tells which unit it is
         {
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
             if (*abort_flag || !mbar_wait(&full[s], ph)) {
@@ -349,57 +391,49 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int unit = tile_slot[it % STAGES];
         if (unit < 0) return;
-        int tile, part, kc0, kc1, tm, tn;
-        unit_decode(p, unit, kt, tile, part, kc0, kc1);
-        tile_coord(tile, p.tiles_m, p.tiles_n, tm, tn);
-        const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
-
-        double acc[MT][NT][4];
-#pragma unroll
-        for (int i = 0; i < MT; ++i)
-#pragma unroll
-            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0;
-
-        for (int kc = kc0; kc < kc1; ++kc, ++it) {
-            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-            if (kc > kc0 && (*abort_flag || !mbar_wait(&full[s], ph))) {
-                *abort_flag = 1;
-                atomicExch(p.err, 102);
-                return;
-            }
-            const uint32_t sA = smem_base + s * STAGE_BYTES;
-            mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-        }
-        if (unit < p.split_first) {
-            epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+        if (!SHARE || unit < p.split_first) {
+            int tm, tn;
+            tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
+            if (!run_piece(0, kt, true)) return;
+            epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
             continue;
         }
-        // A split tile: part 0 applies beta; part i > 0 waits (bounded) until part i-1 has stored its
-        // share, then adds its own.  The order is fixed, so the result does not depend on timing.  A
-        // unit is only ever picked up by a running CTA after all units before it, so the part waited
-        // for is already being worked on.
-        int *flag = p.flags + (tile - p.split_first);
-        if (part > 0) {
-            if (threadIdx.x == 0) {
-                bool ok = false;
-                for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
-                    ok = *reinterpret_cast<volatile int *>(flag) >= part;
-                    if (!ok) __nanosleep(128);
-                }
-                if (!ok) { *abort_flag = 1; atomicExch(p.err, 103); }
+        StreamWalk walk(p.region_tiles, p.nsu, unit - p.split_first, kt);
+        Piece pc;
+        bool first = true;
+        while (walk.next(pc)) {
+            int tm, tn;
+            tile_coord(region_tile(p, pc.r), p.tiles_m, p.tiles_n, tm, tn);
+            const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+            if (!run_piece(pc.kc0, pc.kc1, first)) return;
+            first = false;
+            if (pc.kc0 == 0 && pc.kc1 == kt) {
+                epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+                continue;
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-            if (*abort_flag) return;
+            // A shared tile.  Its pieces fold into C in order of k: the head [0, x) applies beta and
+            // leaves x in the tile's flag; the piece that starts at x waits (bounded) for that value,
+            // adds its share and leaves its own end; the piece that ends at kt puts the flag back to
+            // zero.  The order is fixed, so the result does not depend on timing.
+            int *flag = p.sched + 2 + pc.r;
+            if (pc.kc0 > 0) {
+                if (threadIdx.x == 0) {
+                    bool ok = false;
+                    for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                        ok = *reinterpret_cast<volatile int *>(flag) == pc.kc0;
+                        if (!ok) __nanosleep(64);
+                    }
+                    if (!ok) { *abort_flag = 1; atomicExch(p.err, 103); }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+                if (*abort_flag) return;
+                __threadfence();
+            }
+            epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, pc.kc0 > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
             __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+            if (threadIdx.x == 0) atomicExch(flag, pc.kc1 == kt ? 0 : pc.kc1);
         }
-        epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, part > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-        if (threadIdx.x == 0) atomicExch(flag, part + 1);
     }
 }
 
@@ -535,15 +569,8 @@ int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int6
 }
 
 
-// ULMB200_DGEMM_SPLITK=0 switches the K splits off (test hook)
-static int split_allowed()
-{
-    static const int v = [] { const char *e = getenv("ULMB200_DGEMM_SPLITK"); return e ? atoi(e) : 1; }();
-    return v;
-}
-
 template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B, int STAGES, int CTAS_PER_SM>
-static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, const double *B)
+static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, const double *B, bool may_share)
 {
     constexpr int ctas_per_sm = CTAS_PER_SM;
     CUtensorMap tmA, tmB;
@@ -570,16 +597,16 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     const int tiles = p.tiles_m * p.tiles_n;
     int sms = sm_count() - g_sm_reserve.load(std::memory_order_relaxed);
     if (sms < 1) sms = 1;
+    const int slots = sms * ctas_per_sm;
     GemmParams q = p;
-    const bool may_alloc = p.ksplit != 0;
-    q.split_first = tiles; q.ksplit = 1; q.kchunk = 0; q.flags = nullptr;
-    // Tail split.  With one CTA per SM the tiles beyond the last full wave leave most SMs idle for a
-    // whole tile time (a SYRK of order 8192: 2080 tiles = 14 waves + 8 tiles).  When that remainder
-    // is at most half a wave, each of its tiles is shared by 2-8 CTAs, one K range each.
-    const int allow_split = split_allowed();
+    q.split_first = tiles; q.nsu = 0; q.region_tiles = 0;
     const int kt = (int)((p.k + kBK - 1) / kBK);
-    if (allow_split && may_alloc && ctas_per_sm == 1 && tiles > sms && tiles <= 64 * sms && kt >= 32) {
-        // tiles that do work (a triangular update skips those outside its triangle)
+    const int mode = settings().dgemm_split;
+    // Sharing the last tiles.  With one CTA per SM the tiles beyond the last full wave leave most
+    // SMs idle for a whole tile time (a SYRK of order 8192: 2080 tiles = 14 waves + 8 tiles; a
+    // 1024^3 product: 64 tiles on 148 SMs).  Those tiles' pipeline stages are dealt out evenly to
+    // all CTAs instead, whenever that is cheaper than one more wave of whole tiles.
+    if (mode != 0 && may_share && p.sched && ctas_per_sm == 1 && tiles < (1 << 30)) {
         auto real = [&](int id) {
             int tm, tn;
             tile_coord(id, p.tiles_m, p.tiles_n, tm, tn);
@@ -587,68 +614,32 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
         };
         int64_t nreal = tiles;
         if (p.tri != 0) {
-            // count per tile row/column analytically: tile (tm, tn) is real unless wholly outside
             nreal = 0;
             for (int tn = 0; tn < p.tiles_n; ++tn)
                 for (int tm = 0; tm < p.tiles_m; ++tm)
                     nreal += !tile_skipped(p.tri, (int64_t)tm * BM, (int64_t)tn * BN, BM, BN);
         }
-        const int rem = (int)(nreal % sms);
-        if (nreal > sms && rem > 0) {
-            // cut s ways (all parts resident at once: rem * s <= SMs), the last wave costs 1/s of a tile
-            // time plus a chain of s short epilogues: take the cheapest s with at least 16 stages per part
-            int ks = 1;
-            double best = 0.8;
-            for (int cand = 2; cand <= 8 && kt / cand >= 16 && rem * cand <= sms; ++cand) {
-                const double cost = (double)((rem * cand + sms - 1) / sms) / cand + 0.01 * cand;
-                if (cost < best) { best = cost; ks = cand; }
-            }
-            if (ks > 1) {
-                const int kchunk = (kt + ks - 1) / ks;
-                ks = (kt + kchunk - 1) / kchunk;                 // no empty part
-                int first = tiles, found = 0;
-                while (first > 0 && found < rem) { --first; found += real(first); }
-                if (ks > 1 && tiles - first <= kSplitSpan) {
-                    static std::atomic<unsigned> turn{0};
-                    int *flags = static_cast<int *>(device_scratch(15, sizeof(int) * kSplitSpan * 8));
-                    if (flags) {
-                        flags += kSplitSpan * (turn.fetch_add(1, std::memory_order_relaxed) % 8);
-                        ULMB_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)(tiles - first), st));
-                        q.split_first = first; q.ksplit = ks; q.kchunk = kchunk; q.flags = flags;
-                    }
+        const SharePlan sp = plan_shared_tiles(nreal, kt, slots, mode == 2);
+        if (sp.nsu > 0) {
+            int first = tiles, found = 0;
+            while (first > 0 && found < sp.region_tiles) { --first; found += real(first); }
+            if (tiles - first <= 65535) {
+                if (p.tri != 0) {
+                    int r = 0;
+                    for (int id = first; id < tiles; ++id)
+                        if (real(id)) q.rtile[r++] = (unsigned short)(id - first);
                 }
+                q.split_first = first; q.nsu = sp.nsu; q.region_tiles = sp.region_tiles;
             }
         }
     }
-    // Few tiles and a long inner dimension (a product of tall, narrow operands): every tile is cut,
-    // so that all SMs work on it.  Same mechanism, split_first = 0.
-    if (allow_split && may_alloc && ctas_per_sm == 1 && p.tri == 0 && q.ksplit == 1 && tiles * 2 <= sms && kt >= 128) {
-        int ks = sms / tiles;
-        if (ks > 8) ks = 8;
-        while (ks > 1 && kt / ks < 64) --ks;                     // at least 64 stages (1024 k) per part
-        if (ks > 1) {
-            const int kchunk = (kt + ks - 1) / ks;
-            ks = (kt + kchunk - 1) / kchunk;
-            static std::atomic<unsigned> turn_all{0};
-            int *flags = ks > 1 ? static_cast<int *>(device_scratch(15, sizeof(int) * kSplitSpan * 8)) : nullptr;
-            if (flags) {
-                flags += kSplitSpan * (turn_all.fetch_add(1, std::memory_order_relaxed) % 8);
-                ULMB_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)tiles, st));
-                q.split_first = 0; q.ksplit = ks; q.kchunk = kchunk; q.flags = flags;
-            }
-        }
-    }
-    const int64_t units = (int64_t)q.split_first + (int64_t)(tiles - q.split_first) * q.ksplit;
-    const int grid = (int)(units < (int64_t)sms * ctas_per_sm ? units : (int64_t)sms * ctas_per_sm);
-    // tile counter: one of 60 words next to the error word, taken round-robin so that launches
-    // in flight on different streams do not share one
-    static std::atomic<unsigned> rr{0};
-    const unsigned turn = rr.fetch_add(1, std::memory_order_relaxed);
-    q.tile_counter = p.err + 1 + (turn % 60);
-    // The counter only matters when there is more work than CTAs.  Otherwise every CTA just learns
-    // from it that nothing is left, which any non-negative value tells it -- so small products skip
-    // the memset launch (except now and then, to keep the word from creeping towards overflow).
-    if (units > grid || (turn & 1023u) < 60u) ULMB_CUDA(cudaMemsetAsync(q.tile_counter, 0, sizeof(int), st));
+    const int64_t units = (int64_t)q.split_first + q.nsu;
+    const int grid = (int)(units < slots ? units : slots);
+    // More units than CTAs: they are handed out through the stream's counter word.  Without
+    // scheduler words (none left for this stream) the CTAs stride through the units instead.
+    q.dynamic = (units > grid && p.sched) ? 1 : 0;
+    trace("dgemm kernel tile %dx%d %s grid %d units %lld (whole %d, shared tiles %d over %d CTAs) kt %d",
+          BM, BN, q.dynamic ? "dynamic" : "static", grid, (long long)units, q.split_first, q.region_tiles, q.nsu, kt);
     kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, q);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
@@ -673,20 +664,26 @@ static int launch_ldg(cudaStream_t st, const GemmParams &p)
 }
 
 template <int MAJOR_A, int MAJOR_B>
-static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, int force_tile, int force_path)
+static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
 {
-    // Large tiles once they fill the machine; small tiles for small problems.
+    const Settings &cfg = settings();
+    // Large tiles once they fill the machine, or whenever the inner dimension is long enough for
+    // the last tiles' stages to be shared out evenly; small tiles (two CTAs per SM) for products
+    // that are small in every dimension.
     const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
-    bool big = t128 >= (int64_t)sm_count() * 3 / 4;
-    // few tiles but a long inner dimension: large tiles cut along K fill the machine better than
-    // small tiles do (768 x 768 x 8192: 30.2 TFLOP/s against 24.9 with 64 x 64 tiles); parts shorter
-    // than 1024 k do not pay (1024^3 is faster on small tiles)
-    if (p.tri == 0 && tma_ok && p.ksplit != 0 && split_allowed() && t128 * 2 <= sm_count() && p.k >= 128 * kBK &&
-        t128 * (p.k / (64 * kBK)) >= sm_count() / 2)
-        big = true;
-    if (force_tile == 128) big = true;
-    if (force_tile == 64) big = false;
-    if (force_path == 1) tma_ok = false;
+    const int kt = (int)((p.k + kBK - 1) / kBK);
+    const int sms = sm_count();
+    bool big = t128 >= (int64_t)sms * 3 / 4;
+    if (!big && tma_ok && may_share && p.sched && cfg.dgemm_split != 0) {
+        // shared: every CTA gets an equal share of t128 * kt stages; worth it when a share is at
+        // least a few stages long and the padding of the large tiles stays moderate
+        const double waste = (double)(t128 * 128 * 128) / ((double)p.m * (double)p.n);
+        const int64_t share = (t128 * kt + sms - 1) / sms;
+        if (share >= 8 && waste <= 1.35) big = true;
+    }
+    if (cfg.dgemm_tile == 128) big = true;
+    if (cfg.dgemm_tile == 64) big = false;
+    if (cfg.dgemm_ldg) tma_ok = false;
     if (big) {
         p.tiles_m = (int)((p.m + 127) / 128);
         p.tiles_n = (int)((p.n + 127) / 128);
@@ -694,7 +691,7 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, int force_tile, 
             // Three stages of 32 KB, not four: with both operands K-major (op(A) = A^T, op(B) = B)
             // a four-deep ring measured 6% slower (33.3 against 35.6 TFLOP/s at 8192^3); the other
             // three modes are within 1% either way.
-            int r = launch_tma<128, 128, 2, 4, MAJOR_A, MAJOR_B, 3, 1>(st, p, p.A, p.B);
+            int r = launch_tma<128, 128, 2, 4, MAJOR_A, MAJOR_B, 3, 1>(st, p, p.A, p.B, may_share);
             if (r >= 0) return r;
         }
         return launch_ldg<128, 128, 2, 4, MAJOR_A, MAJOR_B>(st, p);
@@ -702,20 +699,10 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, int force_tile, 
     p.tiles_m = (int)((p.m + 63) / 64);
     p.tiles_n = (int)((p.n + 63) / 64);
     if (tma_ok) {
-        int r = launch_tma<64, 64, 2, 2, MAJOR_A, MAJOR_B, 4, 2>(st, p, p.A, p.B);
+        int r = launch_tma<64, 64, 2, 2, MAJOR_A, MAJOR_B, 4, 2>(st, p, p.A, p.B, false);
         if (r >= 0) return r;
     }
     return launch_ldg<64, 64, 2, 2, MAJOR_A, MAJOR_B>(st, p);
-}
-
-// Test hooks (environment, read per call so tests can flip them):
-//   ULMB200_DGEMM_TILE = 64 | 128   force a tile shape
-//   ULMB200_DGEMM_PATH = ldg        force the non-TMA kernel
-static void read_overrides(int &tile, int &path)
-{
-    tile = 0; path = 0;
-    if (const char *t = getenv("ULMB200_DGEMM_TILE")) tile = atoi(t);
-    if (const char *s = getenv("ULMB200_DGEMM_PATH")) path = (s[0] == 'l') ? 1 : 0;
 }
 
 int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n,
@@ -734,25 +721,26 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     GemmParams p;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
-    p.tiles_m = p.tiles_n = 0; p.tri = tri; p.tile_counter = nullptr;
-    // ksplit = 0 on the way in: the caller brought its own error word because it must not allocate
-    // device memory, so the tail split (which takes flag words from the scratch cache) stays off
-    p.split_first = 0; p.ksplit = err_word ? 0 : 1; p.kchunk = 0; p.flags = nullptr;
+    p.tiles_m = p.tiles_n = 0; p.tri = tri;
+    p.split_first = 0; p.nsu = 0; p.region_tiles = 0; p.dynamic = 0;
+    // A caller that brings its own error word must not allocate device memory: its launches take the
+    // two words after the error word as tile counter and never share tiles (no fold flags there).
+    // Such callers keep their calls on one device from overlapping, so the words are theirs alone.
+    const bool may_share = err_word == nullptr;
     p.err = err_word ? err_word : device_error_word();
     if (!p.err) return set_status(ULMB200_CUDA_ERROR);
+    p.sched = err_word ? err_word + 1 : sched_words(st);
 
     // TMA needs 16-byte aligned bases and row pitches, and 32-bit coordinates.
     const bool tma_ok = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
                         (lda % 2 == 0) && (ldb % 2 == 0) && m < (1ll << 31) - 256 &&
                         n < (1ll << 31) - 256 && k < (1ll << 31) - 256 &&
                         lda < (1ll << 36) && ldb < (1ll << 36);
-    int ftile, fpath;
-    read_overrides(ftile, fpath);
     int r;
-    if (!transA && !transB)      r = dispatch<MN_MAJOR, K_MAJOR>(st, p, tma_ok, ftile, fpath);
-    else if (!transA && transB)  r = dispatch<MN_MAJOR, MN_MAJOR>(st, p, tma_ok, ftile, fpath);
-    else if (transA && !transB)  r = dispatch<K_MAJOR, K_MAJOR>(st, p, tma_ok, ftile, fpath);
-    else                         r = dispatch<K_MAJOR, MN_MAJOR>(st, p, tma_ok, ftile, fpath);
+    if (!transA && !transB)      r = dispatch<MN_MAJOR, K_MAJOR>(st, p, tma_ok, may_share);
+    else if (!transA && transB)  r = dispatch<MN_MAJOR, MN_MAJOR>(st, p, tma_ok, may_share);
+    else if (transA && !transB)  r = dispatch<K_MAJOR, K_MAJOR>(st, p, tma_ok, may_share);
+    else                         r = dispatch<K_MAJOR, MN_MAJOR>(st, p, tma_ok, may_share);
     return set_status(r);
 }
 

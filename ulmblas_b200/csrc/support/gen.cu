@@ -1,6 +1,7 @@
 // Device and host fills built on the counter-based generator in gen.h, plus a
 // few element-wise helpers the tests and the bench use on device buffers.
-#include "common.h"
+#include "../common.h"
+#include "../../../include/ulmb200_benchsupport.h"
 #include "gen.h"
 
 namespace ulmb200 {

@@ -3,7 +3,8 @@
 // trusted on a power-capped, shared machine, so they are measured: each probe
 // keeps every SM busy with one kind of arithmetic instruction on register
 // operands (no memory traffic) and reports flop/s.
-#include "common.h"
+#include "../common.h"
+#include "../../../include/ulmb200_benchsupport.h"
 
 namespace ulmb200 {
 
@@ -140,6 +141,16 @@ extern "C" int ulmb200_selftest_wait_timeout(void)
     if (int e = check_cuda(cudaGetLastError(), "wait_probe_kernel", __FILE__, __LINE__)) return e;
     if (int e = check_cuda(cudaDeviceSynchronize(), "synchronize", __FILE__, __LINE__)) return e;
     return set_status(poll_device_error());        // ULMB200_KERNEL_FAULT is the expected answer
+}
+
+extern "C" int ulmb200_selftest_wait_timeout_noalloc_word(void)
+{
+    if (int s = ensure_device()) return set_status(s);
+    int *err = registered_error_word(0);
+    if (!err) return set_status(ULMB200_BAD_ARGUMENT);
+    wait_probe_kernel<<<1, 32>>>(err, 20000);
+    count_launch();
+    return set_status(check_cuda(cudaGetLastError(), "wait_probe_kernel", __FILE__, __LINE__));
 }
 
 extern "C" int ulmb200_peak_probe(int which, int iters, double *tflops, double *ms_out)

@@ -29,6 +29,7 @@
 // No cudaMalloc, cudaFree or allocating library routine is reached from here.
 #include "common.h"
 
+#include <atomic>
 #include <mutex>
 
 namespace ulmb200 {
@@ -47,7 +48,7 @@ static __device__ __align__(256) int g_noalloc_err[64];
 struct NoAllocDevice {
     double *work = nullptr;
     int *err = nullptr;
-    bool ready = false;
+    std::atomic<bool> ready{false};
 };
 static NoAllocDevice g_noalloc[kMaxDevices];
 static std::mutex g_noalloc_mu;
@@ -57,9 +58,9 @@ static int noalloc_setup(NoAllocDevice **out)
 {
     const int dev = current_device();
     NoAllocDevice &d = g_noalloc[dev];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lk(g_noalloc_mu);
-        if (!d.ready) {
+        if (!d.ready.load(std::memory_order_relaxed)) {
             void *w = nullptr, *e = nullptr;
             cudaError_t rc = cudaGetSymbolAddress(&w, g_noalloc_work);
             if (rc != cudaSuccess) return check_cuda(rc, "cudaGetSymbolAddress(work area)", __FILE__, __LINE__);
@@ -67,7 +68,9 @@ static int noalloc_setup(NoAllocDevice **out)
             if (rc != cudaSuccess) return check_cuda(rc, "cudaGetSymbolAddress(error word)", __FILE__, __LINE__);
             d.work = static_cast<double *>(w);
             d.err = static_cast<int *>(e);
-            d.ready = true;
+            // ulmb200_check_device_error() reads this word too (a plain copy, no allocation)
+            register_error_word(d.err);
+            d.ready.store(true, std::memory_order_release);
         }
     }
     *out = &d;
@@ -97,9 +100,12 @@ extern "C" int ulmb200_dtrsm_noalloc(void *stream, int side, int lower, int tran
     NoAllocDevice *d = nullptr;
     if (int s = noalloc_setup(&d)) return set_status(s);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // the error word must start at zero; the block inverses and the leaf tile are fully rewritten
-    // by the kernels before anything reads them
-    if (int s = check_cuda(cudaMemsetAsync(d->err, 0, sizeof(int), st), "cudaMemsetAsync", __FILE__, __LINE__))
+    // The block inverses and the leaf tile are fully rewritten by the kernels before anything reads
+    // them.  The words behind the error word (the GEMM launches' tile counter) are put back to zero
+    // by the kernels themselves; they are cleared here as well in case an earlier call gave up half
+    // way.  The error word itself is left alone, so that a fault stays visible until
+    // ulmb200_check_device_error() has reported it.
+    if (int s = check_cuda(cudaMemsetAsync(d->err + 1, 0, 8 * sizeof(int), st), "cudaMemsetAsync", __FILE__, __LINE__))
         return set_status(s);
     return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, dA, ldA, dB, ldB, d->work,
                                          d->work + kNoAllocInvDoubles, d->err));
