@@ -287,6 +287,67 @@ int ulmb200_strsm(void *stream, int side, int lower, int transA, int unit,
                   int64_t m, int64_t n, float alpha,
                   const float *dA, int64_t ldA, float *dB, int64_t ldB);
 
+/* ------------------------------------------------------------------------ */
+/* 3. One product over the GPUs of a box: C split by column blocks            */
+/* ------------------------------------------------------------------------ */
+/* One process per GPU; every rank makes the same calls in the same order.  Rank r owns columns
+ * [j0, j1) of B and C (ulmb200_mg_column_block: near-equal blocks starting on multiples of 128);
+ * A starts on the root and reaches the other ranks by NCCL broadcast in K panels, each panel's
+ * product queued behind its arrival.  There is no reduction: columns of C are independent
+ * (the reference walks C by column blocks in its outermost loop, ulmblas/level3/gemm.tcc:60; it
+ * has no multi-device path of its own).  NCCL is looked up at run time (ULMB200_NCCL_LIB, else a
+ * libnccl.so.2 already in the process, else the system's); one GPU needs none.
+ *
+ * Set-up: rank 0 calls ulmb200_mg_unique_id and hands the 128 bytes to the other ranks by any
+ * means (MPI_Bcast, a file, a socket); every rank, with its device current, calls ulmb200_mg_init.  */
+int ulmb200_mg_unique_id(char id[128]);
+int ulmb200_mg_init(const char id[128], int rank, int world, void **handle);   /* id may be NULL when world == 1 */
+int ulmb200_mg_finalize(void *handle);
+int ulmb200_mg_column_block(int64_t n, int world, int rank, int64_t *j0, int64_t *j1);
+
+/* Device-resident operands.  dA: m x k with ldA == m on every rank; holds A on `root`, receives it
+ * elsewhere.  dB_block / dC_block: this rank's column blocks (k x nr, m x nr).  Asynchronous: the
+ * work is ordered after what `stream` holds at the call and `stream` continues after it.          */
+int ulmb200_mg_dgemm(void *handle, void *stream, int64_t m, int64_t n, int64_t k, double alpha,
+                     double *dA, int64_t ldA, const double *dB_block, int64_t ldB,
+                     double beta, double *dC_block, int64_t ldC, int root);
+
+/* Host-resident operands (page-locked for the copies to overlap): hA is all of A, required on
+ * `root`; hB_block / hC_block are this rank's column blocks; dA, dB_block, dC_block are device
+ * buffers of the shapes above (dA with leading dimension m).  A travels host -> device panel by
+ * panel ahead of its broadcast, the block of B row range by row range with it, and the block of C
+ * returns in column pieces while the last panel is still being multiplied.  every_rank_has_a != 0
+ * promises that every rank passed an hA it can read (a shared mapping, a copy): each rank then
+ * brings its share of every panel over its own PCIe link and an all-gather completes the panels,
+ * instead of the root pushing all of A through one link.                                            */
+int ulmb200_mg_dgemm_host(void *handle, void *stream, int64_t m, int64_t n, int64_t k, double alpha,
+                          const double *hA, int64_t ldhA, const double *hB_block, int64_t ldhB,
+                          double beta, double *hC_block, int64_t ldhC,
+                          double *dA, double *dB_block, int64_t lddB, double *dC_block, int64_t lddC,
+                          int root, int every_rank_has_a);
+
+/* Host-side wait for everything the communicator has queued, at most timeout_ms (negative: no
+ * limit), watching NCCL's asynchronous error state; on an error or a timeout the communicator is
+ * aborted and ULMB200_CUDA_ERROR returned (the handle is then only good for ulmb200_mg_finalize). */
+int ulmb200_mg_wait(void *handle, int timeout_ms);
+
+/* The K-panel plan as a function of sizes and rates (no device needed): widths[p] columns of A per
+ * panel, reserve[p] = 1 where that panel's product leaves a few SMs to the transport.  A short first
+ * panel, a second one just long enough for the rest of A to arrive behind it, one last panel with
+ * the remaining K on the whole GPU.  Returns the number of panels (-1: bad argument).               */
+int ulmb200_mg_plan_panels(int64_t m, int64_t n_block, int64_t k, int world, int64_t first_panel,
+                           double transport_gbs, double gemm_tflops, int64_t *widths, int *reserve, int cap);
+/* Plan of the communicator's last call, and the transport rates it has measured so far (GB/s of A
+ * reaching the ranks: device-resident calls, host calls; 0 = nothing measured yet).                */
+int ulmb200_mg_last_plan(void *handle, int64_t *widths, int *reserve, int cap,
+                         double *device_rate_gbs, double *host_rate_gbs);
+/* Overrides the rates the next plan uses (<= 0 leaves one as it is).                               */
+int ulmb200_mg_set_rates(void *handle, double transport_gbs, double host_gbs, double gemm_tflops);
+/* Per-product device times of the last ulmb200_mg_dgemm call (CUDA events on the compute stream),
+ * recorded while profiling is switched on; read after the call has finished.                       */
+int ulmb200_mg_profile(void *handle, int on);
+int ulmb200_mg_last_gemm_ms(void *handle, double *ms, int cap);
+
 /* The persistent DGEMM grid normally takes every SM.  A caller that runs a collective
  * (e.g. the NCCL broadcast of the next A panel) beside it can ask the following DGEMM
  * launches to leave `sms` SMs free so that the collective's kernels are never starved;

@@ -10,9 +10,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 import oracle  # noqa: E402
-
-EPS64 = 2.0 ** -52      # smallest power of two with 1 + eps != 1, as the reference's tester defines it
-EPS32 = 2.0 ** -23      # (test/F77/dblat3.f:183-193 of the reference)
+from oracle.inputs import EPS32, EPS64, bound_ratio, gemm_gauge, gen_uniform  # noqa: E402,F401
+# EPS: smallest power of two with 1 + eps != 1, as the reference's tester defines it
+# (test/F77/dblat3.f:183-193); bound_ratio: the componentwise parity bound
 ROGUE = -1e10           # padding / unreferenced-triangle fill of the reference's tester (dblat3.f:2365)
 
 
@@ -39,23 +39,6 @@ def padded(values, ld, fill=ROGUE):
     view, base = oracle.fmat(r, c, ld, dtype=values.dtype, fill=fill)
     view[...] = values
     return view, base
-
-
-def gemm_gauge(alpha, opA, opB, beta, C0):
-    """|alpha| * |op(A)| |op(B)| + |beta| * |C0|  (the tester's gauge, dblat3.f:2496-2545)."""
-    g = abs(alpha) * (np.abs(opA).astype(np.float64) @ np.abs(opB).astype(np.float64))
-    if beta != 0:
-        g = g + abs(beta) * np.abs(C0).astype(np.float64)
-    return g
-
-
-def bound_ratio(C, Cref, gauge, k, eps):
-    """max_ij |C - Cref| / (2*k*eps*gauge_ij); parity holds iff the result is <= 1."""
-    err = np.abs(C.astype(np.float64) - Cref.astype(np.float64))
-    lim = 2.0 * max(k, 1) * eps * gauge
-    with np.errstate(divide="ignore", invalid="ignore"):
-        ratio = np.where(lim > 0, err / lim, np.where(err == 0, 0.0, np.inf))
-    return float(ratio.max()) if ratio.size else 0.0
 
 
 _port = None

@@ -37,16 +37,37 @@ def test_k_panels():
     assert PanelPlan(4, 4, 16384, 8, 0, 4096, 1024).panels == [(0, 1024), (1024, 5120), (5120, 9216), (9216, 13312), (13312, 16384)]
 
 
-def test_two_phase_plan_for_end_to_end_runs():
-    from ulmblas_b200.sharded import two_phase_plan
-    pans = PanelPlan(4, 4, 16384, 8, 0, 4096, 1024).panels
-    n1, pieces = two_phase_plan(pans, 16384, 8192)
-    assert n1 == 2 and sum(l1 - l0 for l0, l1 in pans[:n1]) == 5120          # 31 % of K in the first phase
-    assert pieces == [(c, 1024) for c in range(0, 8192, 1024)]
-    n1, pieces = two_phase_plan(pans, 16384, 1000)                            # a narrow block: aligned pieces
-    assert pieces[0] == (0, 128) and pieces[-1] == (896, 104) and sum(c for _, c in pieces) == 1000
-    assert two_phase_plan([(0, 10), (10, 20)], 20, 256)[0] == 1               # one panel is always left for phase 2
-    assert two_phase_plan([(0, 20)], 20, 256)[0] == 0
+def test_the_library_plans_the_k_panels(ulm):
+    """ulmb200_mg_plan_panels (csrc/mg_plan.h): a short first panel whose transfer nothing hides, a second
+    one just long enough for the rest of A to arrive behind its product, and a last panel with the
+    remaining K that needs no SMs left free because nothing travels any more."""
+    from ulmblas_b200.sharded import planned_panels
+    m = n = 65536
+    k = 16384
+    for world in (2, 4, 8):
+        nb = n // world
+        for rate in (40.0, 100.0, 150.0, 250.0, 400.0, 700.0):
+            pans, reserve = planned_panels(m, nb, k, world, 1024, rate, 35.0)
+            assert pans[0] == (0, 1024) and pans[-1][1] == k
+            assert all(a[1] == b[0] for a, b in zip(pans, pans[1:])) and 2 <= len(pans) <= 3
+            assert reserve[-1] == 0 and all(r == 1 for r in reserve[:-1])
+            assert all((l1 - l0) % 256 == 0 for l0, l1 in pans[:-1])
+            # all of A has arrived (at the assumed rate) before the last panel's product starts
+            arrive = 8.0 * m * k / (rate * 1e9)
+            start_last = 1024 * 8.0 * m / (rate * 1e9) + 2.0 * m * nb * pans[-1][0] / 35e12
+            assert start_last >= arrive or len(pans) == 3 and pans[1][1] - pans[1][0] >= 256, (world, rate, pans)
+            # the panels that leave SMs free are a small part of the work once the transport is fast
+            if rate >= 250.0:
+                assert pans[-1][0] <= 2048 * (8 // world if world < 8 else 1) + 1024, (world, rate, pans)
+    assert planned_panels(m, n, k, 1)[0] == [(0, k)]                      # one GPU: one piece, nothing reserved
+    assert planned_panels(m, n, k, 1)[1] == [0]
+    assert planned_panels(100, 100, 300, 4)[0] == [(0, 256), (256, 300)] or planned_panels(100, 100, 300, 4)[0] == [(0, 300)]
+    assert planned_panels(100, 100, 200, 4)[0] == [(0, 200)]             # shorter than a first panel
+    # a slow transport makes the middle panel longer, never the reserved share larger than needed
+    slow = planned_panels(m, 8192, k, 8, 1024, 40.0, 35.0)[0]
+    fast = planned_panels(m, 8192, k, 8, 1024, 400.0, 35.0)[0]
+    assert slow[-1][0] > fast[-1][0]
+    assert PanelPlan(m, n, k, 8, 3).panels[0] == (0, 1024)               # kp = None: the library's plan
 
 
 def test_run_panels_orders_beta_and_waits():

@@ -112,6 +112,21 @@ lib.ulmblas_zgemm.argtypes = [_int, _int, _int, _int, _int, _vp, _vp, _int, _vp,
 for _name in ("zgemm_", "cblas_zgemm", "ulmblas_zgemm"):
     getattr(lib, _name).restype = None
 
+_pi64 = C.POINTER(C.c_int64)
+lib.ulmb200_mg_unique_id.argtypes = [C.c_char_p]
+lib.ulmb200_mg_init.argtypes = [C.c_char_p, _int, _int, C.POINTER(_vp)]
+lib.ulmb200_mg_finalize.argtypes = [_vp]
+lib.ulmb200_mg_column_block.argtypes = [_i64, _int, _int, _pi64, _pi64]
+lib.ulmb200_mg_dgemm.argtypes = [_vp, _vp, _i64, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64, _int]
+lib.ulmb200_mg_dgemm_host.argtypes = [_vp, _vp, _i64, _i64, _i64, _dbl, _vp, _i64, _vp, _i64, _dbl, _vp, _i64,
+                                      _vp, _vp, _i64, _vp, _i64, _int, _int]
+lib.ulmb200_mg_wait.argtypes = [_vp, _int]
+lib.ulmb200_mg_plan_panels.argtypes = [_i64, _i64, _i64, _int, _i64, _dbl, _dbl, _pi64, _pi, _int]
+lib.ulmb200_mg_last_plan.argtypes = [_vp, _pi64, _pi, _int, _pd, _pd]
+lib.ulmb200_mg_set_rates.argtypes = [_vp, _dbl, _dbl, _dbl]
+lib.ulmb200_mg_profile.argtypes = [_vp, _int]
+lib.ulmb200_mg_last_gemm_ms.argtypes = [_vp, _pd, _int]
+
 CblasRowMajor, CblasColMajor = 101, 102
 CblasNoTrans, CblasTrans, CblasConjTrans, AtlasConj = 111, 112, 113, 114
 CblasUpper, CblasLower = 121, 122
@@ -331,6 +346,22 @@ def workspace_bytes():
 
 def release_workspace():
     return lib.ulmb200_release_workspace()
+
+
+def mg_column_block(n, world, rank):
+    """[j0, j1): the columns of B and C that rank `rank` of `world` owns (ulmb200_mg_column_block)."""
+    j0, j1 = C.c_int64(0), C.c_int64(0)
+    _check(lib.ulmb200_mg_column_block(n, world, rank, C.byref(j0), C.byref(j1)), "ulmb200_mg_column_block")
+    return j0.value, j1.value
+
+
+def mg_plan_panels(m, n_block, k, world, first=1024, transport_gbs=150.0, gemm_tflops=35.0):
+    """([width of each K panel], [1 where that panel's product leaves SMs to the transport])."""
+    w, r = (C.c_int64 * 32)(), (C.c_int * 32)()
+    n = lib.ulmb200_mg_plan_panels(m, n_block, k, world, first, transport_gbs, gemm_tflops, w, r, 32)
+    if n < 0:
+        raise ValueError("bad argument to ulmb200_mg_plan_panels")
+    return [int(w[i]) for i in range(n)], [int(r[i]) for i in range(n)]
 
 
 def set_sm_reserve(sms):

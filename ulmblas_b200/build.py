@@ -81,10 +81,12 @@ def build(force=False, verbose=False):
              (SUPPORT_LIB, sobjs, ["-L" + HERE, "-lulmblas_b200", "-Xlinker", "-rpath=$ORIGIN"])]
     for lib, obs, extra in links:
         if force or jobs or _stale(lib, obs):
-            r = subprocess.run([nvcc, "-shared", "-o", lib] + obs + arch + extra, capture_output=True, text=True)
+            tmp = lib + ".tmp"
+            r = subprocess.run([nvcc, "-shared", "-o", tmp] + obs + arch + extra, capture_output=True, text=True)
             if r.returncode != 0:
                 sys.stderr.write(r.stdout + r.stderr)
                 raise RuntimeError("link failed: " + lib)
+            os.replace(tmp, lib)       # a reader never sees a half-written library
     return LIB
 
 

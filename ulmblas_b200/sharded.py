@@ -2,30 +2,36 @@
 
     C[:, J_r] <- alpha * A * B[:, J_r] + beta * C[:, J_r]        on rank r
 
-One process per GPU (``torch.distributed``, NCCL).  Rank r owns the column block J_r of B
-and C for good; A lives on the root rank and reaches the others by NCCL broadcast over
-NVLink, cut into K-panels A[:, l*kp:(l+1)*kp] (contiguous in column-major storage).  The
-broadcasts are queued ahead on NCCL's stream; the product of panel l is queued on the
-compute stream behind "panel l has arrived", so panel l+1 travels while panel l
-multiplies.  There is no reduction and no other exchange: columns of C are independent.
+One process per GPU.  Rank r owns the column block J_r of B and C for good; A lives on the root
+rank and reaches the others by NCCL broadcast over NVLink, cut into K panels A[:, l0:l1]
+(contiguous in column-major storage).  The broadcasts are queued ahead on a communication
+stream; the product of panel l is queued on the compute stream behind "panel l has arrived".
+There is no reduction and no other exchange: columns of C are independent.
 
-The reference has no multi-device path (it is single-threaded CPU code); the partition
-follows its own loop order, which already walks C by column blocks
-(ulmblas/level3/gemm.tcc:60).
+The DGEMM driver itself is C++ behind the library's C ABI (``ulmb200_mg_*`` in
+include/ulmblas_b200.h, csrc/mg_dgemm.cu): partition, K-panel plan, transport and products.
+``ShardedDgemm`` is its binding for torch buffers; ``torch.distributed`` only carries the NCCL
+unique id to the ranks.  ``PanelPlan`` / ``run_panels`` state the same schedule with the
+transport and the arithmetic injected, so that the ordering can be exercised by CPU ranks
+(gloo) in the tests; the triangular solve further down is driven from Python.
 
-The arithmetic is injected (``gemm`` callable) so that the partitioning and the panel
-schedule can be exercised on CPU ranks with the gloo backend by the tests; the product
-path always passes the library's device GEMM.
+The reference has no multi-device path (it is single-threaded CPU code); the partition follows
+its own loop order, which already walks C by column blocks (ulmblas/level3/gemm.tcc:60).
 """
+import ctypes as C
 from dataclasses import dataclass
 
 ALIGN = 128          # column blocks start on CTA-tile boundaries
 
 
 def column_block(n, world, rank, align=ALIGN):
-    """[j0, j1) of rank `rank`: near-equal blocks whose starts are multiples of `align`."""
+    """[j0, j1) of rank `rank`: near-equal blocks whose starts are multiples of `align`
+    (the library's ulmb200_mg_column_block for the default alignment)."""
     if world <= 0 or not (0 <= rank < world):
         raise ValueError("bad world/rank")
+    if align == ALIGN:
+        from . import api
+        return api.mg_column_block(n, world, rank)
     units = (n + align - 1) // align
     base, extra = divmod(units, world)
     u0 = rank * base + min(rank, extra)
@@ -34,8 +40,8 @@ def column_block(n, world, rank, align=ALIGN):
 
 
 def k_panels(k, kp, first=None):
-    """[(l0, l1)] covering [0, k): an optional short first panel (so the first product can start
-    early), then panels of kp (the last may be short)."""
+    """[(l0, l1)] covering [0, k): an optional short first panel, then panels of kp (the last may
+    be short).  The fixed-width walk of the triangular solve and of the tests."""
     if k <= 0:
         return []
     kp = max(1, min(kp, k))
@@ -49,17 +55,15 @@ def k_panels(k, kp, first=None):
     return out
 
 
-def two_phase_plan(panels, k, nr, npieces=8, align=ALIGN):
-    """(number of leading panels applied to the whole column block, [(c0, cn)] column pieces that take the
-    remaining panels one piece at a time).  The first phase covers the first quarter to third of K --
-    about the time the root needs to bring A in -- and always leaves at least one panel for the second."""
-    covered, n1 = 0, 0
-    while n1 < len(panels) - 1 and covered * 4 < k:
-        covered += panels[n1][1] - panels[n1][0]
-        n1 += 1
-    q = max(align, ((nr + npieces - 1) // npieces + align - 1) // align * align)
-    pieces = [(c0, min(q, nr - c0)) for c0 in range(0, nr, q)]
-    return n1, pieces
+def planned_panels(m, n_block, k, world, first=1024, transport_gbs=150.0, gemm_tflops=35.0):
+    """The library's K-panel plan as ([(l0, l1)], [reserve flags]) -- ulmb200_mg_plan_panels."""
+    from . import api
+    widths, reserve = api.mg_plan_panels(m, n_block, k, world, first, transport_gbs, gemm_tflops)
+    out, l0 = [], 0
+    for w in widths:
+        out.append((l0, l0 + w))
+        l0 += w
+    return out, reserve
 
 
 @dataclass
@@ -69,7 +73,7 @@ class PanelPlan:
     k: int
     world: int
     rank: int
-    kp: int
+    kp: int = None          # None: the library's plan; a number: fixed-width panels (tests)
     first: int = None
 
     @property
@@ -81,11 +85,14 @@ class PanelPlan:
         # one GPU needs no transport, so it multiplies in one piece
         if self.world == 1:
             return k_panels(self.k, self.k)
+        if self.kp is None:
+            nb = max(column_block(self.n, self.world, r)[1] - column_block(self.n, self.world, r)[0] for r in range(self.world))
+            return planned_panels(self.m, nb, self.k, self.world, self.first or 1024)[0]
         return k_panels(self.k, self.kp, self.first)
 
 
 def run_panels(plan, alpha, beta, A_panel, recv_panel, gemm):
-    """Drive one sharded product.
+    """Drive one sharded product (the schedule csrc/mg_dgemm.cu implements, with everything injected).
 
     A_panel(l0, l1)      -> handle of the local buffer that holds / will hold A[:, l0:l1]
     recv_panel(h, l0, l1)-> makes that panel present on this rank (broadcast from the root);
@@ -109,15 +116,15 @@ def run_panels(plan, alpha, beta, A_panel, recv_panel, gemm):
 
 
 class ShardedDgemm:
-    """Device-resident sharded DGEMM on torch CUDA buffers (column-major, as the BLAS sees them).
+    """ulmb200_mg_dgemm / ulmb200_mg_dgemm_host on torch buffers (column-major, as the BLAS sees them).
 
-    A  : torch.float64 tensor of shape (k, m) on every rank (column-major m x k, ld = m);
+    A  : torch.float64 CUDA tensor of shape (k, m) on every rank (column-major m x k, ld = m);
          only the root's copy needs to hold data before ``run``.
     Br : (nr, k)  this rank's column block of B  (column-major k x nr, ld = k)
     Cr : (nr, m)  this rank's column block of C  (column-major m x nr, ld = m)
     """
 
-    def __init__(self, m, n, k, kp=4096, first=1024, group=None, root=0, reserve_sms=8, reserve_panels=2):
+    def __init__(self, m, n, k, first=1024, group=None, root=0, reserve_sms=8, **_ignored):
         import torch
         import torch.distributed as dist
         from . import api
@@ -125,162 +132,73 @@ class ShardedDgemm:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.group, self.root = group, root
-        self.plan = PanelPlan(m, n, k, self.world, self.rank, kp, first)
-        self.compute = torch.cuda.Stream()
-        self.comm = torch.cuda.Stream()
-        # when set to a list, run() appends (start_event, end_event, flops) per GEMM launch,
-        # recorded on the launching stream
-        self.kernel_events = None
-        # While panels are still travelling, the GEMMs leave a few SMs free so that NCCL's
-        # kernels can always be scheduled next to the persistent grid (bench.py caps NCCL at
-        # the same number of CTAs); later GEMMs take the whole GPU again.
-        self.reserve_sms = reserve_sms if self.world > 1 else 0
-        self.reserve_panels = reserve_panels
+        self.m, self.n, self.k = m, n, k
+        self.plan = PanelPlan(m, n, k, self.world, self.rank, None, first)
+        ident = None
+        if self.world > 1:
+            box = [None]
+            if self.rank == root:
+                buf = C.create_string_buffer(128)
+                api._check(api.lib.ulmb200_mg_unique_id(buf), "ulmb200_mg_unique_id")
+                box = [buf.raw]
+            dist.broadcast_object_list(box, src=root, group=group)
+            ident = box[0]
+        import os
+        os.environ.setdefault("ULMB200_MG_RESERVE_SMS", str(reserve_sms))
+        os.environ.setdefault("ULMB200_MG_FIRST_PANEL", str(first))
+        self.handle = C.c_void_p()
+        api._check(api.lib.ulmb200_mg_init(ident, self.rank, self.world, C.byref(self.handle)), "ulmb200_mg_init")
 
-    def run(self, alpha, A, Br, beta, Cr, host=None):
-        """One sharded product on device buffers.
+    def close(self):
+        if getattr(self, "handle", None):
+            self.api.lib.ulmb200_mg_finalize(self.handle)
+            self.handle = None
 
-        host = (hA, hB, hC), pinned host tensors shaped like A (root only, else None), Br and Cr, makes it
-        an end-to-end call: the root's A goes host -> device panel by panel, each panel broadcast as soon
-        as it has landed (the first product waits for one panel, not for all of A); every rank copies its
-        own block of B in (and of C, when beta != 0), and its block of C back out in four column pieces,
-        each as soon as the last panel's product of that piece is done.  Returns when the device work
-        is queued; the caller synchronises."""
-        torch, dist, api, p = self.torch, self.dist, self.api, self.plan
-        j0, j1 = p.cols
-        nr = j1 - j0
-        cur = torch.cuda.current_stream()
-        self.compute.wait_stream(cur)
-        self.comm.wait_stream(cur)
-        hA = hB = hC = None
-        if host is not None:
-            hA, hB, hC = host
-            if not hasattr(self, "h2d"):
-                self.h2d, self.d2h = torch.cuda.Stream(), torch.cuda.Stream()
-            self.h2d.wait_stream(cur)
-            self.d2h.wait_stream(cur)
-            with torch.cuda.stream(self.h2d):
-                if nr > 0:
-                    Br.copy_(hB, non_blocking=True)
-                    if beta != 0.0:
-                        Cr.copy_(hC, non_blocking=True)
-            self.compute.wait_stream(self.h2d)       # B (and C) of this rank before its first product
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:      # noqa: BLE001 - interpreter shutdown
+            pass
 
-        def A_panel(l0, l1):
-            return A[l0:l1, :]                      # rows of the (k, m) tensor = columns l0..l1 of A
+    def profile(self, on=True):
+        self.api.lib.ulmb200_mg_profile(self.handle, 1 if on else 0)
 
-        def stage_panel(h, l0, l1):
-            if hA is not None and self.rank == self.root:
-                with torch.cuda.stream(self.h2d):
-                    h.copy_(hA[l0:l1, :], non_blocking=True)
-                self.comm.wait_stream(self.h2d)      # the broadcast (or the product) follows the copy
+    def last_gemm_ms(self):
+        ms = (C.c_double * 32)()
+        n = self.api.lib.ulmb200_mg_last_gemm_ms(self.handle, ms, 32)
+        return [float(ms[i]) for i in range(max(n, 0))]
 
-        def recv_panel(h, l0, l1):
-            stage_panel(h, l0, l1)
-            with torch.cuda.stream(self.comm):
-                return dist.broadcast(h, src=self.root, group=self.group, async_op=True)
+    def last_plan(self):
+        """(widths, reserve flags, measured device transport GB/s, measured host transport GB/s) of the last call."""
+        w, r = (C.c_int64 * 32)(), (C.c_int * 32)()
+        dr, hr = C.c_double(0.0), C.c_double(0.0)
+        n = self.api.lib.ulmb200_mg_last_plan(self.handle, w, r, 32, C.byref(dr), C.byref(hr))
+        return [int(w[i]) for i in range(max(n, 0))], [int(r[i]) for i in range(max(n, 0))], dr.value, hr.value
 
-        launched = [0]
-        npanels = len(p.panels)
+    def wait(self, timeout_ms=-1):
+        return self.api.lib.ulmb200_mg_wait(self.handle, int(timeout_ms))
 
-        def gemm(h, l0, l1, beta_l, w):
-            api.set_sm_reserve(self.reserve_sms if launched[0] < self.reserve_panels else 0)
-            launched[0] += 1
-            last = launched[0] == npanels
-            with torch.cuda.stream(self.compute):
-                if w is not None:
-                    w.wait()                         # compute stream waits for the panel, host does not
-                ev = None
-                if self.kernel_events is not None:
-                    ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                    ev[0].record(self.compute)
-                # the last panel's product goes by column pieces when C returns to the host, so that
-                # each piece can leave while the next is still being multiplied
-                pieces = [(0, nr)]
-                if last and hC is not None and nr >= 4 * ALIGN:
-                    q = ((nr + 3) // 4 + ALIGN - 1) // ALIGN * ALIGN
-                    pieces = [(c0, min(q, nr - c0)) for c0 in range(0, nr, q)]
-                for (c0, cn) in pieces:
-                    api.dev_dgemm(0, 0, p.m, cn, l1 - l0, alpha, h.data_ptr(), p.m,
-                                  Br.data_ptr() + 8 * (l0 + c0 * p.k), p.k, beta_l, Cr.data_ptr() + 8 * c0 * p.m, p.m,
-                                  stream=self.compute.cuda_stream)
-                    if last and hC is not None:
-                        done = torch.cuda.Event()
-                        done.record(self.compute)
-                        self.d2h.wait_event(done)
-                        with torch.cuda.stream(self.d2h):
-                            hC[c0:c0 + cn, :].copy_(Cr[c0:c0 + cn, :], non_blocking=True)
-                if ev is not None:
-                    ev[1].record(self.compute)
-                    self.kernel_events.append((ev[0], ev[1], 2.0 * p.m * nr * (l1 - l0)))
+    def run(self, alpha, A, Br, beta, Cr, host=None, every_rank_has_a=False):
+        """One sharded product, queued behind the current torch stream, which continues after it.
 
-        if self.world == 1:
-            # one piece (or, with host staging, the same panels as the copy of A)
-            if hA is None:
-                run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
-            else:
-                pans = k_panels(p.k, p.kp, p.first)
-                npanels = len(pans)
-                for i, (l0, l1) in enumerate(pans):
-                    h = A_panel(l0, l1)
-                    stage_panel(h, l0, l1)
-                    self.compute.wait_stream(self.h2d)
-                    if nr > 0:
-                        gemm(h, l0, l1, beta if i == 0 else 1.0, None)
-        elif hC is None or nr < 8 * ALIGN or len(p.panels) < 3:
-            run_panels(p, alpha, beta, A_panel, recv_panel, gemm)
+        host = (hA, hB, hC): page-locked host tensors shaped like A (required on the root; on the other
+        ranks too when every_rank_has_a), Br and Cr.  It makes the call end to end: A goes host -> device
+        panel by panel ahead of its transport, this rank's block of B with it, and the block of C
+        returns in column pieces while the last panel is still being multiplied."""
+        torch, api = self.torch, self.api
+        j0, j1 = self.plan.cols
+        s = torch.cuda.current_stream().cuda_stream
+        m, n, k = self.m, self.n, self.k
+        if host is None:
+            st = api.lib.ulmb200_mg_dgemm(self.handle, s, m, n, k, alpha, A.data_ptr(), m, Br.data_ptr(), k, beta,
+                                          Cr.data_ptr(), m, self.root)
         else:
-            self._run_host_two_phase(alpha, beta, A, Br, Cr, hC, A_panel, recv_panel)
-        api.set_sm_reserve(0)
-        cur.wait_stream(self.compute)
-        cur.wait_stream(self.comm)
-        if host is not None:
-            cur.wait_stream(self.h2d)
-            cur.wait_stream(self.d2h)
+            hA, hB, hC = host
+            st = api.lib.ulmb200_mg_dgemm_host(self.handle, s, m, n, k, alpha, hA.data_ptr() if hA is not None else None, m,
+                                               hB.data_ptr(), k, beta, hC.data_ptr(), m, A.data_ptr(), Br.data_ptr(), k,
+                                               Cr.data_ptr(), m, self.root, 1 if every_rank_has_a else 0)
+        api._check(st, "ulmb200_mg_dgemm")
         return j0, j1
-
-
-    def _run_host_two_phase(self, alpha, beta, A, Br, Cr, hC, A_panel, recv_panel):
-        """End-to-end order of the products when C has to go back to the host.
-
-        Panel by panel, C is complete only after the last panel, so its copy back could overlap nothing
-        but that last product.  Here the first panels (about the time A needs to arrive) are still
-        applied to the whole block, and the remaining ones column piece by column piece: piece j is
-        complete -- and leaves for the host -- after (j+1)/J of that second phase, so the copies spread
-        over most of the run."""
-        torch, api, p = self.torch, self.api, self.plan
-        j0, j1 = p.cols
-        nr = j1 - j0
-        pans = list(p.panels)
-        pending = []
-        for (l0, l1) in pans:
-            h = A_panel(l0, l1)
-            pending.append((h, l0, l1, recv_panel(h, l0, l1)))
-        n1, pieces = two_phase_plan(pans, p.k, nr)
-        cs = self.compute.cuda_stream
-
-        def product(h, l0, l1, c0, cn, beta_l):
-            api.dev_dgemm(0, 0, p.m, cn, l1 - l0, alpha, h.data_ptr(), p.m, Br.data_ptr() + 8 * (l0 + c0 * p.k), p.k,
-                          beta_l, Cr.data_ptr() + 8 * c0 * p.m, p.m, stream=cs)
-
-        with torch.cuda.stream(self.compute):
-            for i, (h, l0, l1, w) in enumerate(pending[:n1]):
-                api.set_sm_reserve(self.reserve_sms if i < self.reserve_panels else 0)
-                if w is not None:
-                    w.wait()
-                product(h, l0, l1, 0, nr, beta if i == 0 else 1.0)
-            api.set_sm_reserve(0)
-            for (h, l0, l1, w) in pending[n1:]:
-                if w is not None:
-                    w.wait()                      # all of A is here before the second phase starts
-            for (c0, cn) in pieces:
-                for (h, l0, l1, w) in pending[n1:]:
-                    product(h, l0, l1, c0, cn, 1.0)
-                done = torch.cuda.Event()
-                done.record(self.compute)
-                self.d2h.wait_event(done)
-                with torch.cuda.stream(self.d2h):
-                    hC[c0:c0 + cn, :].copy_(Cr[c0:c0 + cn, :], non_blocking=True)
 
 
 # ---------------------------------------------------------------------------
