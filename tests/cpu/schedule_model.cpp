@@ -19,7 +19,7 @@ static int check(long long nreal, int kt, int slots, bool force)
 {
     const SharePlan sp = plan_shared_tiles(nreal, kt, slots, force);
     if (sp.nsu == 0) return 0;
-    if (sp.region_tiles != nreal % slots || sp.region_tiles > kRegionMax || sp.nsu > slots) {
+    if (sp.region_tiles != nreal % slots || sp.region_tiles > kRegionMax || sp.nsu > slots || sp.nsu < 2) {
         printf("bad plan: nreal %lld kt %d slots %d -> region %d nsu %d\n", nreal, kt, slots, sp.region_tiles, sp.nsu);
         return 1;
     }
@@ -76,9 +76,10 @@ int main()
     bad += check(384, 33, 148, false);       // 3001 x 2047 x 513
     bad += check(2080, 256, 148, false);     // triangle of order 8192, k = 4096
     bad += check(262144, 1024, 148, false);  // 65536 x 65536 x 16384
-    if (plan_shared_tiles(64, 64, 148, false).nsu != 148) { printf("1024^3 is not shared\n"); ++bad; }
+    if (plan_shared_tiles(64, 64, 148, false).nsu != 128) { printf("1024^3 is not cut into halves\n"); ++bad; }
     if (plan_shared_tiles(148, 64, 148, false).nsu != 0) { printf("a full wave is shared\n"); ++bad; }
     if (plan_shared_tiles(100, 4, 148, false).nsu != 0) { printf("a short inner dimension is shared\n"); ++bad; }
+    if (plan_shared_tiles(4, 16, 148, false).nsu > 16) { printf("256^3 is cut into tiny pieces\n"); ++bad; }
     if (bad) { printf("FAILED (%d)\n", bad); return 1; }
     printf("%lld plans checked\nOK\n", plans);
     return 0;

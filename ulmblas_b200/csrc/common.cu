@@ -299,7 +299,7 @@ EncodeTiledFn encode_tiled_fn()
 }
 
 bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base,
-                  uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1)
+                  uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1, CUtensorMapSwizzle swizzle)
 {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return false;
@@ -308,7 +308,7 @@ bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, cons
     cuuint32_t box[2] = {b0, b1};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }

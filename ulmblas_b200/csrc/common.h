@@ -78,9 +78,10 @@ EncodeTiledFn encode_tiled_fn();
 
 // 2-D tensor map over a column-major matrix: dim0 = contiguous dimension
 // (extent d0), dim1 = the strided one (extent d1, stride ld elements), box
-// b0 x b1 elements, 128-byte swizzle.  Returns false if the driver refuses.
+// b0 x b1 elements, 128-byte swizzle unless told otherwise.  Returns false if the driver refuses.
 bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base,
-                  uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1);
+                  uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1,
+                  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 // C <- alpha*op(A)*op(B) + beta*C on device operands (dgemm_sm100.cu).  tri: 0 full, 1 upper
 // triangle only, 2 lower.  err_word: device word a kernel writes when a bounded wait runs out;

@@ -29,7 +29,7 @@ constexpr int kRegionMax = 160;           // most tiles the shared region of a l
 
 // Cost of one epilogue (read-modify-write of a C tile) in units of one pipeline stage of the
 // main loop; only used to decide whether sharing the last tiles pays.
-constexpr int kEpilogueStages = 3;
+constexpr int kEpilogueStages = 2;
 
 struct Piece {
     int r;          // index of the tile within the region
@@ -65,21 +65,39 @@ struct SharePlan {
     int region_tiles, nsu;
 };
 
+// Estimated cost, in pipeline stages, of sharing `rem` tiles of kt stages among nsu stream units.
+// A unit multiplies its share of the stages and writes one partial epilogue per piece it holds;
+// the pieces of a tile fold into C one after the other and the last ones all finish computing at
+// about the same time, so every piece of a tile beyond the first adds one more epilogue at the end.
+inline long long shared_cost(int rem, int kt, int nsu)
+{
+    const long long S = (long long)rem * kt;
+    const long long share = (S + nsu - 1) / nsu;
+    const bool aligned = nsu % rem == 0;                       // unit boundaries fall on tile boundaries
+    const long long pieces = aligned ? nsu / rem : (kt + share - 1) / share + 1;
+    const long long own = aligned ? 1 : 2;                     // epilogues in a unit's own time line
+    return share + (own + (pieces - 1)) * kEpilogueStages;
+}
+
 inline SharePlan plan_shared_tiles(long long nreal, int kt, int slots, bool force)
 {
     SharePlan none = {0, 0};
-    if (slots < 2 || kt < 1) return none;
+    if (slots < 2 || kt < 2) return none;
     const int rem = (int)(nreal % slots);
     if (rem == 0 || rem > kRegionMax) return none;
     const long long S = (long long)rem * kt;
-    const int nsu = (int)(S < slots ? S : slots);
-    if (nsu < 2) return none;
-    const long long share = (S + nsu - 1) / nsu;
-    // one more wave of whole tiles costs kt stages and an epilogue; sharing costs a share of the
-    // stages and, for most CTAs, two partial epilogues and a short wait
-    const bool pays = share + 2 * kEpilogueStages + 1 < kt + kEpilogueStages;
+    // candidates: every CTA takes part, or each tile is cut into p equal pieces (p = 2, 3, ...)
+    int best = (int)(S < slots ? S : slots);
+    long long best_cost = best >= 2 ? shared_cost(rem, kt, best) : (1ll << 60);
+    for (int p = 2; p <= 16 && (long long)rem * p <= slots && p <= kt; ++p) {
+        const long long c = shared_cost(rem, kt, rem * p);
+        if (c < best_cost) { best_cost = c; best = rem * p; }
+    }
+    if (best < 2) return none;
+    // one more wave of whole tiles costs kt stages and an epilogue
+    const bool pays = best_cost < kt + kEpilogueStages;
     if (!pays && !force) return none;
-    SharePlan p = {rem, nsu};
+    SharePlan p = {rem, best};
     return p;
 }
 

@@ -115,75 +115,115 @@ __device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32
 }
 
 // C(row, col) <- alpha*acc + beta*C for the warp's accumulators; rows/cols
-// outside m x n (and outside the requested triangle) are skipped.  Per m16 tile
-// all old values of C are fetched first (independent loads in flight together),
-// then combined and stored.  With M-contiguous A the two rows a lane holds are
-// adjacent (2g, 2g+1), so a 16-byte aligned C moves them as one 16-byte access.
-template <int MAJOR_A, int MAJOR_B, int MT, int NT>
+// outside m x n (and outside the requested triangle) are skipped.  The old values of C
+// of G m16 tiles are fetched first (independent loads in flight together), then combined
+// and stored: the epilogue costs G times fewer memory round trips.  With M-contiguous A the
+// two rows a lane holds are adjacent (2g, 2g+1), so a 16-byte aligned C moves them as one
+// 16-byte access.
+template <int MAJOR_A, int MAJOR_B, int MT, int NT, int G>
 __device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64_t m0, int64_t n0, int wm0,
                                          int wn0, int lane, double (&acc)[MT][NT][4])
 {
+    static_assert(MT % G == 0, "m16 tiles are taken G at a time");
     const double alpha = p.alpha;
     const bool use_c = beta != 0.0;
     const bool vec = MAJOR_A == MN_MAJOR && p.tri == 0 &&
                      ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 2 == 0);
 #pragma unroll
-    for (int i = 0; i < MT; ++i) {
-        const int64_t r0 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 0);
-        const int64_t r1 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 1);
-        if (vec && r1 < p.m) {
-            // rows r0 (even) and r1 = r0 + 1: registers {0,2} of column 2t, {1,3} of column 2t+1
-            double2 old[NT][2];
+    for (int i0 = 0; i0 < MT; i0 += G) {
+        double old[G][NT][4];
+        bool ok[G][NT][4];
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
+        for (int g = 0; g < G; ++g) {
+            const int i = i0 + g;
+            const int64_t r0 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 0);
+            const int64_t r1 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 1);
+            if (vec && r1 < p.m) {
+                // rows r0 (even) and r1 = r0 + 1: registers {0,2} of column 2t, {1,3} of column 2t+1
 #pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
-                    old[j][w] = (use_c && col < p.n)
-                                    ? *reinterpret_cast<const double2 *>(p.C + r0 + col * p.ldc)
-                                    : make_double2(0.0, 0.0);
-                }
+                for (int j = 0; j < NT; ++j)
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
-                    if (col < p.n) {
-                        double2 o;
-                        o.x = alpha * acc[i][j][w];
-                        o.y = alpha * acc[i][j][2 + w];
-                        if (use_c) { o.x = fma(beta, old[j][w].x, o.x); o.y = fma(beta, old[j][w].y, o.y); }
-                        *reinterpret_cast<double2 *>(p.C + r0 + col * p.ldc) = o;
+                    for (int w = 0; w < 2; ++w) {
+                        const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
+                        const bool v = col < p.n;
+                        ok[g][j][w] = ok[g][j][2 + w] = v;
+                        double2 o = make_double2(0.0, 0.0);
+                        if (use_c && v) o = *reinterpret_cast<const double2 *>(p.C + r0 + col * p.ldc);
+                        old[g][j][w] = o.x; old[g][j][2 + w] = o.y;
                     }
-                }
-            continue;
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int64_t row = (e >> 1) ? r1 : r0;
+                        const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
+                        bool v = row < p.m && col < p.n;
+                        if (p.tri == 1) v = v && row <= col;
+                        if (p.tri == 2) v = v && row >= col;
+                        ok[g][j][e] = v;
+                        old[g][j][e] = (v && use_c) ? p.C[row + col * p.ldc] : 0.0;
+                    }
+            }
         }
-        double old[NT][4];
-        bool ok[NT][4];
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+        for (int g = 0; g < G; ++g) {
+            const int i = i0 + g;
+            const int64_t r0 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 0);
+            const int64_t r1 = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, 1);
+            if (vec && r1 < p.m) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int64_t row = (e >> 1) ? r1 : r0;
-                const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
-                bool v = row < p.m && col < p.n;
-                if (p.tri == 1) v = v && row <= col;
-                if (p.tri == 2) v = v && row >= col;
-                ok[j][e] = v;
-                old[j][e] = (v && use_c) ? p.C[row + col * p.ldc] : 0.0;
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
+                        if (ok[g][j][w]) {
+                            double2 o;
+                            o.x = alpha * acc[i][j][w];
+                            o.y = alpha * acc[i][j][2 + w];
+                            if (use_c) { o.x = fma(beta, old[g][j][w], o.x); o.y = fma(beta, old[g][j][2 + w], o.y); }
+                            *reinterpret_cast<double2 *>(p.C + r0 + col * p.ldc) = o;
+                        }
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (ok[g][j][e]) {
+                            const int64_t row = (e >> 1) ? r1 : r0;
+                            const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
+                            double v = alpha * acc[i][j][e];
+                            if (use_c) v = fma(beta, old[g][j][e], v);
+                            p.C[row + col * p.ldc] = v;
+                        }
+                    }
             }
+        }
+    }
+}
+
+// Asks L2 for the lines of C this lane's epilogue will read, long before it reads them (issued
+// when the tile's main loop starts; rows and columns outside the matrix are left alone).
+template <int MAJOR_A, int MAJOR_B, int MT, int NT>
+__device__ __forceinline__ void prefetch_c(const GemmParams &p, int64_t m0, int64_t n0, int wm0, int wn0, int lane)
+{
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+    for (int i = 0; i < MT; ++i) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (ok[j][e]) {
-                    const int64_t row = (e >> 1) ? r1 : r0;
-                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
-                    double v = alpha * acc[i][j][e];
-                    if (use_c) v = fma(beta, old[j][e], v);
-                    p.C[row + col * p.ldc] = v;
+        for (int h = 0; h < 2; ++h) {
+            const int64_t row = m0 + c_row<MAJOR_A>(wm0 + 16 * i, lane, h);
+            // with M-contiguous A the two rows of a lane share a line: one request does
+            if (MAJOR_A == MN_MAJOR && h == 1) continue;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
+                    if (row < p.m && col < p.n)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.C + row + col * p.ldc));
                 }
-            }
+        }
     }
 }
 
@@ -255,6 +295,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     constexpr bool REBALANCE = (NCW == 8 && MIN_CTAS == 1);
     constexpr bool SHARE = (MIN_CTAS == 1);          // only the one-CTA-per-SM shape shares tiles
+    constexpr int EG = 1;   // m16 tiles per round of the epilogue (2 would need more registers than the 168 the kernel is built with)
     if (warp >= NCW) {
         // ---------------- producer warpgroup ----------------
         if (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -394,8 +435,9 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!SHARE || unit < p.split_first) {
             int tm, tn;
             tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
+            if (SHARE && p.beta != 0.0) prefetch_c<MAJOR_A, MAJOR_B, MT, NT>(p, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane);
             if (!run_piece(0, kt, true)) return;
-            epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
+            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
             continue;
         }
         StreamWalk walk(p.region_tiles, p.nsu, unit - p.split_first, kt);
@@ -405,10 +447,11 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int tm, tn;
             tile_coord(region_tile(p, pc.r), p.tiles_m, p.tiles_n, tm, tn);
             const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+            if (pc.kc0 > 0 || p.beta != 0.0) prefetch_c<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane);
             if (!run_piece(pc.kc0, pc.kc1, first)) return;
             first = false;
             if (pc.kc0 == 0 && pc.kc1 == kt) {
-                epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+                epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
                 continue;
             }
             // A shared tile.  Its pieces fold into C in order of k: the head [0, x) applies beta and
@@ -429,7 +472,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (*abort_flag) return;
                 __threadfence();
             }
-            epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, pc.kc0 > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
+            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, pc.kc0 > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
             if (threadIdx.x == 0) atomicExch(flag, pc.kc1 == kt ? 0 : pc.kc1);
@@ -533,7 +576,7 @@ dgemm_ldg_kernel(const GemmParams p)
         }
         __syncthreads();
     }
-    epilogue<MAJOR_A, MAJOR_B, MT, NT>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+    epilogue<MAJOR_A, MAJOR_B, MT, NT, 1>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
 }
 
 // C <- beta*C (beta == 0 assigns zeros), the alpha == 0 / k == 0 quick path
@@ -667,20 +710,27 @@ template <int MAJOR_A, int MAJOR_B>
 static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
 {
     const Settings &cfg = settings();
-    // Large tiles once they fill the machine, or whenever the inner dimension is long enough for
-    // the last tiles' stages to be shared out evenly; small tiles (two CTAs per SM) for products
-    // that are small in every dimension.
+    // Tile shape by estimated time.  Large tiles (128 x 128, one CTA per SM) run the tensor pipe best and
+    // can share the last tiles' stages among all CTAs; small tiles (64 x 64, two CTAs per SM) waste less
+    // on padding and fill the machine with fewer rows and columns.  Per-SM times in microseconds,
+    // measured on this part: one 16-k stage of a large tile 2.09, of a small tile 1.05 when two CTAs
+    // share the SM and 0.70 when one has it alone; an epilogue 3 / 2.
     const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+    const int64_t t64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
     const int kt = (int)((p.k + kBK - 1) / kBK);
     const int sms = sm_count();
-    bool big = t128 >= (int64_t)sms * 3 / 4;
-    if (!big && tma_ok && may_share && p.sched && cfg.dgemm_split != 0) {
-        // shared: every CTA gets an equal share of t128 * kt stages; worth it when a share is at
-        // least a few stages long and the padding of the large tiles stays moderate
-        const double waste = (double)(t128 * 128 * 128) / ((double)p.m * (double)p.n);
-        const int64_t share = (t128 * kt + sms - 1) / sms;
-        if (share >= 8 && waste <= 1.35) big = true;
+    constexpr double kStage128 = 2.09, kStage64Pair = 1.05, kStage64Alone = 0.70, kEpi128 = 3.0, kEpi64 = 2.0;
+    double time128 = (double)((t128 + sms - 1) / sms) * (kt * kStage128 + kEpi128);
+    if (tma_ok && may_share && p.sched && cfg.dgemm_split != 0 && p.tri == 0) {
+        const SharePlan sp = plan_shared_tiles(t128, kt, sms, false);
+        if (sp.nsu > 0)
+            time128 = (double)(t128 / sms) * (kt * kStage128 + kEpi128) +
+                      (double)shared_cost(sp.region_tiles, kt, sp.nsu) * kStage128;
     }
+    const int64_t waves64 = (t64 + 2 * sms - 1) / (2 * sms);
+    const double stage64 = t64 <= sms ? kStage64Alone : kStage64Pair;
+    const double time64 = (double)waves64 * (kt * stage64 + kEpi64);
+    bool big = time128 <= time64;
     if (cfg.dgemm_tile == 128) big = true;
     if (cfg.dgemm_tile == 64) big = false;
     if (cfg.dgemm_ldg) tma_ok = false;

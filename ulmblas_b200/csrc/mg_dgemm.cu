@@ -479,8 +479,8 @@ extern "C" int ulmb200_mg_profile(void *handle, int on)
 {
     MgComm *c = static_cast<MgComm *>(handle);
     if (!c) return set_status(ULMB200_BAD_ARGUMENT);
+    if (on && !c->profile) c->profiled = 0;
     c->profile = on != 0;
-    c->profiled = 0;
     return set_status(ULMB200_OK);
 }
 

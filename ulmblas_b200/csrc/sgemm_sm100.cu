@@ -1,4 +1,7 @@
-// FP32 GEMM on the FP32 FMA pipes:  C <- alpha*op(A)*op(B) + beta*C.
+// FP32 GEMM on the FP32 FMA pipes:  C <- alpha*op(A)*op(B) + beta*C -- the entry point and the
+// plain-load kernel.  Operands that TMA can address (16-byte aligned, leading dimensions that are
+// multiples of 4) take the persistent warp-specialised kernel in sgemm_ws_sm100.cu; this file's
+// kernel, filled by ordinary predicated loads, serves every other alignment and leading dimension.
 //
 // Replaces the float instantiation of the reference's gemm path
 // (ulmblas/level3/gemm.tcc with ukernel/ref/ugemm.tcc, MR=8 NR=4).  The
@@ -16,8 +19,6 @@
 // fma.rn.f32x2 on row pairs, which halves the issue slots they need.
 #include "common.h"
 
-#include <atomic>
-
 namespace ulmb200 {
 
 namespace sg {
@@ -34,10 +35,6 @@ struct SgemmParams {
     float *C;
     int64_t ldc;
     int tiles_m, tiles_n;
-    int tile_first;           // first tile this launch works on
-    int ksplit;               // 1, or the number of K ranges a tile is cut into (tail launch)
-    int64_t kchunk;           // length of a K range (multiple of BK) when ksplit > 1
-    int *flags;               // ksplit > 1: one word per tile of this launch, zeroed beforehand
     int *err;                 // device error word
 };
 
@@ -112,7 +109,7 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
     int tm, tn;
     {
         constexpr int GM = 8;
-        const int id = p.tile_first + (int)blockIdx.x / p.ksplit, per_group = GM * p.tiles_n, group = id / per_group;
+        const int id = (int)blockIdx.x, per_group = GM * p.tiles_n, group = id / per_group;
         const int first = group * GM, gsz = min(GM, p.tiles_m - first), r = id - group * per_group;
         tm = first + r % gsz;
         tn = r / gsz;
@@ -131,11 +128,7 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
 
-    // a tail launch cuts K into ksplit ranges, one per CTA; part 0 applies beta, part i > 0 adds its
-    // share after part i-1 has stored its own (fixed order: the result does not depend on timing)
-    const int part = (int)blockIdx.x % p.ksplit;
-    const int64_t kbeg = p.ksplit > 1 ? part * p.kchunk : 0;
-    const int64_t kend = p.ksplit > 1 ? min(p.k, kbeg + p.kchunk) : p.k;
+    const int64_t kbeg = 0, kend = p.k;
     const int kt = (int)((kend - kbeg + BK - 1) / BK);
     float ra[BM * BK / NT], rb[BN * BK / NT];
     // op(A) is m x k: stored MN-contiguous when not transposed, K-contiguous when transposed.
@@ -198,28 +191,7 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
 
     // epilogue: column-major C, 4 consecutive rows per 16-byte store when legal
     const float alpha = p.alpha;
-    float beta = p.beta;
-    int *flag = nullptr;
-    if (p.ksplit > 1) {
-        flag = p.flags + (int)blockIdx.x / p.ksplit;
-        if (part > 0) {
-            // bounded wait for the previous part of this tile (about a second), then accumulate
-            __shared__ int s_ok;
-            if (threadIdx.x == 0) {
-                int ok = 0;
-                for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
-                    ok = (*reinterpret_cast<volatile int *>(flag) == part);
-                    if (!ok) __nanosleep(256);
-                }
-                if (!ok) atomicExch(p.err, 201);
-                s_ok = ok;
-            }
-            __syncthreads();
-            if (!s_ok) return;
-            __threadfence();
-            beta = 1.0f;
-        }
-    }
+    const float beta = p.beta;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int64_t col = n0 + bn + (j & 3) + (j >> 2) * 16;
@@ -250,11 +222,6 @@ __global__ void __launch_bounds__(sg::NT, 1) sgemm_fp32_kernel(const SgemmParams
                 }
             }
         }
-    }
-    if (flag) {
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) atomicExch(flag, part + 1);
     }
 }
 
@@ -288,6 +255,9 @@ static int launch_fp32(cudaStream_t st, const SgemmParams &p, int grid)
 int sgemm_3xtf32_device(cudaStream_t st, int transA, int transB, int64_t m, int64_t n, int64_t k,
                         float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
                         float beta, float *C, int64_t ldc);
+// the persistent TMA kernel (sgemm_ws_sm100.cu); -1 when the operands do not qualify for it
+int sgemm_ws_device(cudaStream_t st, int transA, int transB, int64_t m, int64_t n, int64_t k, float alpha,
+                    const float *A, int64_t lda, const float *B, int64_t ldb, float beta, float *C, int64_t ldc);
 
 int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, int64_t n,
                  int64_t k, float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
@@ -313,6 +283,10 @@ int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, i
     if (mode == ULMB200_SGEMM_3XTF32)
         return set_status(sgemm_3xtf32_device(st, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc));
 
+    if (!settings().sgemm_path) {
+        const int r = sgemm_ws_device(st, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        if (r >= 0) return set_status(r);
+    }
     SgemmParams p;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
@@ -320,55 +294,16 @@ int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, i
     p.tiles_n = (int)((n + sg::BN - 1) / sg::BN);
     const bool vec = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
                      lda % 4 == 0 && ldb % 4 == 0;
-    p.tile_first = 0; p.ksplit = 1; p.kchunk = 0; p.flags = nullptr;
     p.err = device_error_word();
     if (!p.err) return set_status(ULMB200_CUDA_ERROR);
-    // Wave quantisation: with one CTA per SM, tiles beyond the last full wave leave most SMs idle for
-    // a whole tile time (4096^3: 512 tiles = 3.46 waves of 148).  When that remainder is at most
-    // half a wave, it gets its own launch in which every tile is shared by ksplit CTAs, each taking
-    // one K range, so the tail costs 1/ksplit of a tile time.
-    const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
-    const int rem = tiles % sms;
-    // cut s ways (all parts resident at once: rem * s <= SMs), the last wave costs 1/s of a tile time
-    // plus a chain of s short epilogues: take the cheapest s whose K ranges are still worth a launch
-    int ksplit = 1;
-    if (tiles > sms && rem > 0) {
-        double best = 0.8;
-        for (int cand = 2; cand <= 8 && k / cand >= 8 * sg::BK && rem * cand <= sms; ++cand) {
-            const double cost = (double)((rem * cand + sms - 1) / sms) / cand + 0.01 * cand;
-            if (cost < best) { best = cost; ksplit = cand; }
-        }
-    }
-    static const int allow_split = [] { const char *e = getenv("ULMB200_SGEMM_SPLITK"); return e ? atoi(e) : 1; }();
-    if (!allow_split) ksplit = 1;
+    const int tiles = p.tiles_m * p.tiles_n;
     int r;
-#define ULMB_SG_LAUNCH(TA_, TB_, GRID_)                                            \
-    r = vec ? launch_fp32<TA_, TB_, true>(st, p, GRID_) : launch_fp32<TA_, TB_, false>(st, p, GRID_)
-#define ULMB_SG(TA_, TB_)                                                          \
-    do {                                                                           \
-        if (ksplit == 1) { ULMB_SG_LAUNCH(TA_, TB_, tiles); break; }               \
-        ULMB_SG_LAUNCH(TA_, TB_, tiles - rem);                                     \
-        if (r != ULMB200_OK) break;                                                \
-        p.tile_first = tiles - rem; p.ksplit = ksplit;                             \
-        p.kchunk = ((k + ksplit - 1) / ksplit + sg::BK - 1) / sg::BK * sg::BK;     \
-        p.flags = flags;                                                           \
-        ULMB_SG_LAUNCH(TA_, TB_, rem * ksplit);                                    \
-    } while (0)
-    int *flags = nullptr;
-    if (ksplit > 1) {
-        // eight flag areas taken in turn: launches in flight on different streams never share one
-        static std::atomic<unsigned> turn{0};
-        flags = static_cast<int *>(device_scratch(14, sizeof(int) * 256 * 8));
-        if (!flags) return set_status(ULMB200_CUDA_ERROR);
-        flags += 256 * (turn.fetch_add(1, std::memory_order_relaxed) % 8);
-        ULMB_CUDA(cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)rem, st));
-    }
+#define ULMB_SG(TA_, TB_) r = vec ? launch_fp32<TA_, TB_, true>(st, p, tiles) : launch_fp32<TA_, TB_, false>(st, p, tiles)
     if (!transA && !transB)      { ULMB_SG(false, false); }
     else if (!transA && transB)  { ULMB_SG(false, true); }
     else if (transA && !transB)  { ULMB_SG(true, false); }
     else                         { ULMB_SG(true, true); }
 #undef ULMB_SG
-#undef ULMB_SG_LAUNCH
     return set_status(r);
 }
 
