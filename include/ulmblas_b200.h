@@ -337,11 +337,13 @@ int ulmb200_mg_wait(void *handle, int timeout_ms);
  * the remaining K on the whole GPU.  Returns the number of panels (-1: bad argument).               */
 int ulmb200_mg_plan_panels(int64_t m, int64_t n_block, int64_t k, int world, int64_t first_panel,
                            double transport_gbs, double gemm_tflops, int64_t *widths, int *reserve, int cap);
-/* Plan of the communicator's last call, and the transport rates it has measured so far (GB/s of A
- * reaching the ranks: device-resident calls, host calls; 0 = nothing measured yet).                */
+/* Plan of the communicator's last call, and the transport rates (GB/s of A reaching the ranks:
+ * device-resident calls, host calls; 0 = nothing measured yet).  Every rank measures; on the second
+ * and on the fourth call of a kind the ranks agree on the smallest measurement (their plans must be
+ * identical) with one tiny all-reduce and a host-side wait, and keep that value afterwards.          */
 int ulmb200_mg_last_plan(void *handle, int64_t *widths, int *reserve, int cap,
                          double *device_rate_gbs, double *host_rate_gbs);
-/* Overrides the rates the next plan uses (<= 0 leaves one as it is).                               */
+/* Overrides the rates the next plan uses (<= 0 leaves one as it is); every rank must pass the same.  */
 int ulmb200_mg_set_rates(void *handle, double transport_gbs, double host_gbs, double gemm_tflops);
 /* Per-product device times of the last ulmb200_mg_dgemm call (CUDA events on the compute stream),
  * recorded while profiling is switched on; read after the call has finished.                       */

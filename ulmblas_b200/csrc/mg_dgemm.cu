@@ -22,7 +22,8 @@
 // little of the work: a short first panel (its transfer is the only one nothing hides), a
 // second panel just long enough for the rest of A to arrive behind it, and one last panel
 // with all the remaining K, which runs on the whole GPU because nothing travels any more.
-// The transport rate the plan needs is measured on every call and used by the next.
+// The transport rate the plan needs is measured by every rank; the ranks agree on one value (their
+// collectives must match, so must their plans) early on and keep it.
 #include "common.h"
 #include "mg_plan.h"
 
@@ -41,7 +42,7 @@ namespace ulmb200 {
 typedef struct ncclComm *ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 typedef int ncclResult_t;                       // 0 = ncclSuccess
-constexpr int kNcclFloat64 = 8, kNcclInt8 = 0;
+constexpr int kNcclFloat64 = 8, kNcclMin = 3;
 
 struct NcclApi {
     void *dl = nullptr;
@@ -52,6 +53,7 @@ struct NcclApi {
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     ncclResult_t (*Broadcast)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
@@ -84,6 +86,7 @@ static NcclApi *nccl_api()
         api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
         api.Broadcast = reinterpret_cast<decltype(api.Broadcast)>(sym("ncclBroadcast"));
         api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
         api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
         api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
         api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
@@ -110,7 +113,10 @@ struct MgComm {
     cudaEvent_t t0 = nullptr, t1 = nullptr;      // transport timing: first panel queued .. last panel landed
     bool timed = false;
     double timed_bytes = 0.0;
-    double rate_gbs[2] = {0.0, 0.0};             // measured transport rate: [0] device-resident, [1] host staging
+    double rate_gbs[2] = {0.0, 0.0};             // transport rate the plans use: [0] device-resident, [1] host staging
+    double seen_gbs[2] = {0.0, 0.0};             // what this rank has measured itself since the ranks last agreed
+    int calls[2] = {0, 0};
+    double *agree = nullptr;                     // one double in device memory for the ranks' agreement
     double gemm_tflops = 35.0;
     int reserve_sms = 8;
     int64_t first = 1024;
@@ -124,16 +130,32 @@ struct MgComm {
     int last_reserve[kMgMaxPanels] = {};
 };
 
-static void fold_rate(MgComm *c, int which)
+// The K-panel plan must be the same on every rank -- the ranks' collectives have to match -- so the
+// rate it is computed from is never a rank's own measurement.  Each rank measures the transport of its
+// calls; on the second and on the fourth call of a kind the ranks agree on the smallest of their
+// measurements (one tiny all-reduce and a host-side wait), and that value stands from then on.
+static int fold_rate(MgComm *c, int which, NcclApi *N)
 {
-    // the transport of the previous call has long finished; its duration refines the estimate
-    if (!c->timed) return;
-    c->timed = false;
-    float ms = 0.f;
-    if (cudaEventElapsedTime(&ms, c->t0, c->t1) != cudaSuccess) { cudaGetLastError(); return; }
-    if (ms <= 0.f) return;
-    const double gbs = c->timed_bytes / (ms * 1e-3) * 1e-9;
-    c->rate_gbs[which] = c->rate_gbs[which] > 0.0 ? 0.5 * (c->rate_gbs[which] + gbs) : gbs;
+    const int call = c->calls[which]++;
+    if (c->timed) {
+        // the transport of the previous call has long finished
+        c->timed = false;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, c->t0, c->t1) == cudaSuccess && ms > 0.f)
+            c->seen_gbs[which] = c->timed_bytes / (ms * 1e-3) * 1e-9;
+        else
+            cudaGetLastError();
+    }
+    if (c->world <= 1 || !N || !c->agree || (call != 1 && call != 3)) return ULMB200_OK;
+    double mine = c->seen_gbs[which] > 0.0 ? c->seen_gbs[which] : 1e9;       // "no opinion"
+    ULMB_CUDA(cudaMemcpyAsync(c->agree, &mine, sizeof mine, cudaMemcpyHostToDevice, c->comm_stream));
+    if (int s = check_nccl(N, N->AllReduce(c->agree, c->agree, 1, kNcclFloat64, kNcclMin, c->comm, c->comm_stream), "ncclAllReduce"))
+        return s;
+    double all = 0.0;
+    ULMB_CUDA(cudaMemcpyAsync(&all, c->agree, sizeof all, cudaMemcpyDeviceToHost, c->comm_stream));
+    ULMB_CUDA(cudaStreamSynchronize(c->comm_stream));
+    if (all > 0.0 && all < 1e8) c->rate_gbs[which] = all;
+    return ULMB200_OK;
 }
 
 static int next_event(MgComm *c, int &cursor, cudaEvent_t *out)
@@ -186,7 +208,7 @@ static int mg_dgemm_device(MgComm *c, cudaStream_t user, int64_t m, int64_t n, i
         mg_column_block(n, c->world, r, &a, &b);
         nr_max = std::max(nr_max, b - a);
     }
-    fold_rate(c, 0);
+    MG_TRY(fold_rate(c, 0, N));
     int64_t widths[kMgMaxPanels];
     int reserve[kMgMaxPanels];
     const int np = plan_for(c, m, nr_max, k, 0, widths, reserve);
@@ -259,7 +281,7 @@ static int mg_dgemm_host(MgComm *c, cudaStream_t user, int64_t m, int64_t n, int
     }
     if (c->rank == root && !hA) return set_status(ULMB200_BAD_ARGUMENT);
     const bool slabs = c->world > 1 && all_have_a && hA != nullptr;
-    fold_rate(c, 1);
+    MG_TRY(fold_rate(c, 1, N));
     int64_t widths[kMgMaxPanels];
     int reserve[kMgMaxPanels];
     int np;
@@ -403,6 +425,7 @@ extern "C" int ulmb200_mg_init(const char id[128], int rank, int world, void **h
         e = cudaEventCreate(&c->g0[i]);
         if (e == cudaSuccess) e = cudaEventCreate(&c->g1[i]);
     }
+    if (e == cudaSuccess && world > 1) e = cudaMalloc(&c->agree, 64);
     if (e == cudaSuccess) e = cudaEventCreate(&c->t0);
     if (e == cudaSuccess) e = cudaEventCreate(&c->t1);
     if (e != cudaSuccess) { check_cuda(e, "stream/event creation", __FILE__, __LINE__); return fail(ULMB200_CUDA_ERROR); }
@@ -427,6 +450,7 @@ extern "C" int ulmb200_mg_finalize(void *handle)
         if (c->g0[i]) cudaEventDestroy(c->g0[i]);
         if (c->g1[i]) cudaEventDestroy(c->g1[i]);
     }
+    if (c->agree) cudaFree(c->agree);
     if (c->t0) cudaEventDestroy(c->t0);
     if (c->t1) cudaEventDestroy(c->t1);
     delete c;
@@ -470,8 +494,8 @@ extern "C" int ulmb200_mg_last_plan(void *handle, int64_t *widths, int *reserve,
         if (widths) widths[i] = c->last_widths[i];
         if (reserve) reserve[i] = c->last_reserve[i];
     }
-    if (device_rate_gbs) *device_rate_gbs = c->rate_gbs[0];
-    if (host_rate_gbs) *host_rate_gbs = c->rate_gbs[1];
+    if (device_rate_gbs) *device_rate_gbs = c->rate_gbs[0] > 0.0 ? c->rate_gbs[0] : c->seen_gbs[0];
+    if (host_rate_gbs) *host_rate_gbs = c->rate_gbs[1] > 0.0 ? c->rate_gbs[1] : c->seen_gbs[1];
     return c->last_npanels;
 }
 
