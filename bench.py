@@ -808,10 +808,11 @@ def tables(a):
     if a.sgemm:
         sz = a.sgemm
         A, B, C = D.buf(sz, sz, f32, 7, 0), D.buf(sz, sz, f32, 7, 1), D.buf(sz, sz, f32, 7, 2)
-        for mode, name in ((0, "fp32"), (1, "3xtf32")):
-            ms = D.time(lambda: u.dev_sgemm(mode, 1, 0, sz, sz, sz, 1.0, A.data_ptr(), sz, B.data_ptr(), sz, 0.0,
-                                            C.data_ptr(), sz, stream=s), 3, warm=2)
-            add(f"sgemm TN {sz}^3 {name}", 2.0 * sz ** 3, ms, peak32)
+        for mode, name, tt in ((0, "fp32", ((1, 0), (0, 0), (0, 1), (1, 1))), (1, "3xtf32", ((1, 0),))):
+            for ta, tb in tt:
+                ms = D.time(lambda: u.dev_sgemm(mode, ta, tb, sz, sz, sz, 1.0, A.data_ptr(), sz, B.data_ptr(), sz, 0.0,
+                                                C.data_ptr(), sz, stream=s), 3, warm=2)
+                add(f"sgemm {'NT'[ta]}{'NT'[tb]} {sz}^3 {name}", 2.0 * sz ** 3, ms, peak32)
         return show()
     if a.lu:
         m = a.lu

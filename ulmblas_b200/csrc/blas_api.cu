@@ -16,8 +16,11 @@
 #include <algorithm>
 #include <cctype>
 #include <cstdarg>
+#include <condition_variable>
 #include <cstring>
+#include <deque>
 #include <mutex>
+#include <thread>
 #include <time.h>
 #include <vector>
 
@@ -122,11 +125,182 @@ struct HostPin {
     ~HostPin() { if (p) cudaHostUnregister(p); }
 };
 
+// ---- pageable host memory: staged through page-locked bounce buffers by worker threads ---------
+// A caller of the reference hands over plain malloc'ed / Fortran arrays.  Copied directly, such
+// memory moves at the speed of one driver thread's staging copy and does not overlap anything.
+// Here a few worker threads copy column chunks into (out of) page-locked bounce buffers, from
+// (to) which the copy engines run asynchronously: the host-side copies of different chunks run in
+// parallel and overlap the transfers and the arithmetic.
+class Stager {
+public:
+    struct Batch {
+        std::mutex m;
+        std::condition_variable cv;
+        int pending = 0;
+        cudaError_t err = cudaSuccess;
+        void add(int n) { std::lock_guard<std::mutex> lk(m); pending += n; }
+        void done(cudaError_t e)
+        {
+            std::lock_guard<std::mutex> lk(m);
+            if (e != cudaSuccess && err == cudaSuccess) err = e;
+            if (--pending == 0) cv.notify_all();
+        }
+        cudaError_t wait()
+        {
+            std::unique_lock<std::mutex> lk(m);
+            cv.wait(lk, [&] { return pending == 0; });
+            const cudaError_t e = err;
+            err = cudaSuccess;
+            return e;
+        }
+    };
+    struct Task {
+        int dev;
+        bool in;                    // host -> device
+        cudaStream_t st;
+        char *dptr; size_t dpitch;  // device block
+        char *hptr; size_t hpitch;  // caller's block
+        size_t width, cols;         // bytes per column, columns
+        Batch *batch;
+    };
+    static constexpr size_t kChunk = (size_t)16 << 20;
+
+    static Stager &get()
+    {
+        static Stager *s = new Stager;     // never destroyed: the workers live until the process ends
+        return *s;
+    }
+    bool usable()
+    {
+        std::call_once(once_, [this] { start(); });
+        return !workers_.empty();
+    }
+    void submit(const Task &t)
+    {
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            queue_.push_back(t);
+        }
+        cv_.notify_one();
+    }
+
+private:
+    struct Worker {
+        std::thread th;
+        char *buf[2] = {nullptr, nullptr};
+        cudaEvent_t ev[2][kMaxDevices] = {};
+        int last_dev[2] = {-1, -1};       // device whose stream used the buffer last
+    };
+    std::once_flag once_;
+    std::mutex mu_;
+    std::condition_variable cv_;
+    std::deque<Task> queue_;
+    std::vector<Worker *> workers_;
+
+    void start()
+    {
+        unsigned hc = std::thread::hardware_concurrency();
+        int n = hc >= 16 ? 8 : (hc >= 8 ? 4 : 2);
+        if (const char *e = getenv("ULMB200_STAGING_THREADS")) n = std::max(0, std::min(32, atoi(e)));
+        for (int i = 0; i < n; ++i) {
+            Worker *w = new Worker;
+            if (cudaHostAlloc(&w->buf[0], kChunk, cudaHostAllocPortable) != cudaSuccess ||
+                cudaHostAlloc(&w->buf[1], kChunk, cudaHostAllocPortable) != cudaSuccess) {
+                cudaGetLastError();
+                delete w;
+                break;
+            }
+            workers_.push_back(w);
+            w->th = std::thread([this, w] { run(w); });
+            w->th.detach();
+        }
+    }
+    void run(Worker *w)
+    {
+        int cur_dev = -1, which = 0;
+        for (;;) {
+            Task t;
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return !queue_.empty(); });
+                t = queue_.front();
+                queue_.pop_front();
+            }
+            cudaError_t e = cudaSuccess;
+            if (t.dev != cur_dev) { e = cudaSetDevice(t.dev); cur_dev = t.dev; }
+            const int b = which;
+            which ^= 1;
+            // the buffer's previous transfer (possibly on another device's stream) must have finished
+            if (e == cudaSuccess && w->last_dev[b] >= 0) e = cudaEventSynchronize(w->ev[b][w->last_dev[b]]);
+            if (e == cudaSuccess && !w->ev[b][t.dev]) e = cudaEventCreateWithFlags(&w->ev[b][t.dev], cudaEventDisableTiming);
+            if (e == cudaSuccess && t.in) {
+                for (size_t c = 0; c < t.cols; ++c) memcpy(w->buf[b] + c * t.width, t.hptr + c * t.hpitch, t.width);
+                e = cudaMemcpy2DAsync(t.dptr, t.dpitch, w->buf[b], t.width, t.width, t.cols, cudaMemcpyHostToDevice, t.st);
+                if (e == cudaSuccess) e = cudaEventRecord(w->ev[b][t.dev], t.st);
+                if (e == cudaSuccess) w->last_dev[b] = t.dev;
+            } else if (e == cudaSuccess) {
+                e = cudaMemcpy2DAsync(w->buf[b], t.width, t.dptr, t.dpitch, t.width, t.cols, cudaMemcpyDeviceToHost, t.st);
+                if (e == cudaSuccess) e = cudaEventRecord(w->ev[b][t.dev], t.st);
+                if (e == cudaSuccess) { w->last_dev[b] = t.dev; e = cudaEventSynchronize(w->ev[b][t.dev]); }
+                if (e == cudaSuccess)
+                    for (size_t c = 0; c < t.cols; ++c) memcpy(t.hptr + c * t.hpitch, w->buf[b] + c * t.width, t.width);
+            }
+            if (e != cudaSuccess) cudaGetLastError();
+            t.batch->done(e);
+        }
+    }
+};
+
+// copies back to pageable memory that the current blocking call still has in flight
+static thread_local Stager::Batch t_out_batch;
+
+static bool pageable(const void *p)
+{
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return true;
+    }
+    return a.type == cudaMemoryTypeUnregistered;
+}
+
+// true if the block went (or is going) through the bounce buffers
+static bool staged_copy(bool in, char *d, size_t dpitch, char *h, size_t hpitch, size_t width, size_t cols,
+                        cudaStream_t st, cudaError_t *err)
+{
+    *err = cudaSuccess;
+    if (g_pin_host || width * cols < ((size_t)8 << 20) || width == 0 || width > Stager::kChunk || !pageable(h)) return false;
+    Stager &sg = Stager::get();
+    if (!sg.usable()) return false;
+    const size_t per = std::max<size_t>(1, Stager::kChunk / width);
+    const int chunks = (int)((cols + per - 1) / per);
+    Stager::Batch local;
+    Stager::Batch *batch = in ? &local : &t_out_batch;
+    batch->add(chunks);
+    for (size_t c0 = 0; c0 < cols; c0 += per) {
+        Stager::Task t;
+        t.dev = current_device(); t.in = in; t.st = st;
+        t.dptr = d + c0 * dpitch; t.dpitch = dpitch;
+        t.hptr = h + c0 * hpitch; t.hpitch = hpitch;
+        t.width = width; t.cols = std::min(per, cols - c0);
+        t.batch = batch;
+        sg.submit(t);
+    }
+    // inbound: return once every chunk's transfer is queued on the stream, so that what the caller
+    // queues next is ordered behind them; outbound chunks are waited for at the end of the call
+    if (in) *err = local.wait();
+    return true;
+}
+
 template <typename T>
 static cudaError_t copy_in(T *d, int64_t ldd, const T *h, int64_t ldh, int64_t rows, int64_t cols,
                            cudaStream_t st)
 {
     if (rows <= 0 || cols <= 0) return cudaSuccess;
+    cudaError_t e;
+    if (staged_copy(true, reinterpret_cast<char *>(d), ldd * sizeof(T), reinterpret_cast<char *>(const_cast<T *>(h)),
+                    ldh * sizeof(T), rows * sizeof(T), (size_t)cols, st, &e))
+        return e;
     return cudaMemcpy2DAsync(d, ldd * sizeof(T), h, ldh * sizeof(T), rows * sizeof(T), cols,
                              cudaMemcpyHostToDevice, st);
 }
@@ -136,6 +310,10 @@ static cudaError_t copy_out(T *h, int64_t ldh, const T *d, int64_t ldd, int64_t 
                             cudaStream_t st)
 {
     if (rows <= 0 || cols <= 0) return cudaSuccess;
+    cudaError_t e;
+    if (staged_copy(false, reinterpret_cast<char *>(const_cast<T *>(d)), ldd * sizeof(T), reinterpret_cast<char *>(h),
+                    ldh * sizeof(T), rows * sizeof(T), (size_t)cols, st, &e))
+        return e;
     return cudaMemcpy2DAsync(h, ldh * sizeof(T), d, ldd * sizeof(T), rows * sizeof(T), cols,
                              cudaMemcpyDeviceToHost, st);
 }
@@ -151,6 +329,10 @@ static size_t span_bytes(int64_t rows, int64_t cols, int64_t ld)
 
 static int finish(Streams *s)
 {
+    // blocks on their way back through the bounce buffers first: their transfers may not even be
+    // queued yet
+    const cudaError_t staged = t_out_batch.wait();
+    if (staged != cudaSuccess) return check_cuda(staged, "staged copy to host", __FILE__, __LINE__);
     cudaError_t e = cudaStreamSynchronize(s->in);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->run);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s->out);

@@ -89,6 +89,10 @@ bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, cons
 int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n, int64_t k,
                  double alpha, const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
                  double *C, int64_t ldc, int *err_word = nullptr);
+// X <- alpha * op(T) * X (left) or alpha * X * op(T) (right) in place, T block triangular of order dim <= 256 with a
+// truly zero off-diagonal block (dgemm_sm100.cu); -1 when the operands do not qualify
+int dgemm_leaf_inplace(cudaStream_t st, int left, int lower_op, int transT, int64_t dim, int64_t other, double alpha,
+                       const double *T, int64_t ldt, double *X, int64_t ldx, int *err_word);
 // sets the number of SMs the persistent DGEMM grid leaves free; returns the previous value
 int sm_reserve_swap(int sms);
 int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri);

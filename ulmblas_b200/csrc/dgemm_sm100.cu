@@ -46,7 +46,30 @@ struct GemmParams {
     // last full wave are shared evenly by all CTAs instead of idling most of them.
     int split_first, nsu, region_tiles;
     unsigned short rtile[kRegionMax];   // tri != 0: tile id - split_first of region tile r
+    // In-place product with a block-triangular first or second operand (the leaf of the triangular
+    // solver and multiply: C is the very block of B that is being read).  pair = 1: two tile rows over
+    // each tile column, pair = 2: two tile columns over each tile row.  Unit 2q is the tile of pair q
+    // that needs all of K; unit 2q+1 is tile number pair_half of the pair, which only meets its own
+    // diagonal block of the triangular operand (stages [8*pair_half, ...)) and whose output region
+    // the other tile still reads: it stores only after the other tile's loads have all landed
+    // (flag q of the scheduler words).  0: off.
+    int pair, pair_half;
 };
+
+// pair mode: unit -> tile coordinates and the range of pipeline stages it multiplies
+__device__ __forceinline__ void pair_decode(const GemmParams &p, int unit, int kt, int &tm, int &tn, int &kc0, int &kc1)
+{
+    const int q = unit >> 1, late = unit & 1;
+    const int which = late ? p.pair_half : 1 - p.pair_half;
+    if (p.pair == 1) { tm = which; tn = q; } else { tm = q; tn = which; }
+    constexpr int HB = 128 / kBK;                    // stages per 128 k = one tile's worth of the triangular operand
+    kc0 = 0; kc1 = kt;
+    if (late) {
+        if (p.pair_half == 0) kc1 = kt < HB ? kt : HB;
+        else kc0 = HB < kt ? HB : kt;
+    }
+}
+
 
 // tile id of region tile r
 __device__ __forceinline__ int region_tile(const GemmParams &p, int r)
@@ -338,7 +361,11 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             };
             int unit = blockIdx.x;
             while (live && unit < num_units) {
-                if (!SHARE || unit < p.split_first) {
+                if (SHARE && p.pair) {
+                    int tm, tn, kc0, kc1;
+                    pair_decode(p, unit, kt, tm, tn, kc0, kc1);
+                    live = load_piece(unit, (int64_t)tm * BM, (int64_t)tn * BN, kc0, kc1);
+                } else if (!SHARE || unit < p.split_first) {
                     int tm, tn;
                     tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
                     const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
@@ -432,6 +459,31 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int unit = tile_slot[it % STAGES];
         if (unit < 0) return;
+        if (SHARE && p.pair) {
+            int tm, tn, kc0, kc1;
+            pair_decode(p, unit, kt, tm, tn, kc0, kc1);
+            if (!run_piece(kc0, kc1, true)) return;
+            int *flag = p.sched + 2 + (unit >> 1);
+            if ((unit & 1) == 0) {
+                // every load of this tile has landed (each stage was waited for): its partner may store
+                if (threadIdx.x == 0) { __threadfence(); atomicExch(flag, 1); }
+            } else {
+                if (threadIdx.x == 0) {
+                    bool ok = false;
+                    for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                        ok = *reinterpret_cast<volatile int *>(flag) == 1;
+                        if (!ok) __nanosleep(64);
+                    }
+                    if (!ok) { *abort_flag = 1; atomicExch(p.err, 104); }
+                    else atomicExch(flag, 0);              // back to zero for the next launch on this stream
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+                if (*abort_flag) return;
+                __threadfence();
+            }
+            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
+            continue;
+        }
         if (!SHARE || unit < p.split_first) {
             int tm, tn;
             tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
@@ -649,7 +701,10 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     // SMs idle for a whole tile time (a SYRK of order 8192: 2080 tiles = 14 waves + 8 tiles; a
     // 1024^3 product: 64 tiles on 148 SMs).  Those tiles' pipeline stages are dealt out evenly to
     // all CTAs instead, whenever that is cheaper than one more wave of whole tiles.
-    if (mode != 0 && may_share && p.sched && ctas_per_sm == 1 && tiles < (1 << 30)) {
+    if (p.pair) {
+        // in-place leaf: two units per pair of tiles, no sharing
+        q.split_first = tiles;
+    } else if (mode != 0 && may_share && p.sched && ctas_per_sm == 1 && tiles < (1 << 30)) {
         auto real = [&](int id) {
             int tm, tn;
             tile_coord(id, p.tiles_m, p.tiles_n, tm, tn);
@@ -676,7 +731,7 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
             }
         }
     }
-    const int64_t units = (int64_t)q.split_first + q.nsu;
+    const int64_t units = p.pair ? (int64_t)tiles : (int64_t)q.split_first + q.nsu;
     const int grid = (int)(units < slots ? units : slots);
     // More units than CTAs: they are handed out through the stream's counter word.  Without
     // scheduler words (none left for this stream) the CTAs stride through the units instead.
@@ -773,6 +828,7 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
     p.tiles_m = p.tiles_n = 0; p.tri = tri;
     p.split_first = 0; p.nsu = 0; p.region_tiles = 0; p.dynamic = 0;
+    p.pair = 0; p.pair_half = 0;
     // A caller that brings its own error word must not allocate device memory: its launches take the
     // two words after the error word as tile counter and never share tiles (no fold flags there).
     // Such callers keep their calls on one device from overlapping, so the words are theirs alone.
@@ -792,6 +848,51 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     else if (transA && !transB)  r = dispatch<K_MAJOR, K_MAJOR>(st, p, tma_ok, may_share);
     else                         r = dispatch<K_MAJOR, MN_MAJOR>(st, p, tma_ok, may_share);
     return set_status(r);
+}
+
+// X <- op(T) * X (left) or X * op(T) (right) in place, T a block-triangular matrix of order dim <= 256
+// whose off-diagonal zero block is really zero (the inverted or zero-filled diagonal blocks of the
+// triangular solver and multiply): the leaf of ulmBLAS's trlsm / trusm / trlmm / trumm recursion
+// (ulmblas/level3/trlsm.tcc:61-74), without their packed copy of the block row.  lower_op: op(T) is
+// lower triangular.  Returns -1 when the operands do not qualify (not TMA-addressable, no scheduler
+// words, too many tiles); the caller then multiplies into a work tile and copies back.
+int dgemm_leaf_inplace(cudaStream_t st, int left, int lower_op, int transT, int64_t dim, int64_t other, double alpha,
+                       const double *T, int64_t ldt, double *X, int64_t ldx, int *err_word)
+{
+    if (dim <= 0 || other <= 0) return ULMB200_OK;
+    if (dim > 256 || err_word) return -1;
+    const int64_t m = left ? dim : other, n = left ? other : dim, k = dim;
+    const bool tma_ok = ((reinterpret_cast<uintptr_t>(T) | reinterpret_cast<uintptr_t>(X)) & 15) == 0 &&
+                        (ldt % 2 == 0) && (ldx % 2 == 0) && other < (1ll << 31) - 256 && ldx < (1ll << 36);
+    if (!tma_ok) return -1;
+    GemmParams p;
+    p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = 0.0;
+    p.A = left ? T : X; p.lda = left ? ldt : ldx;
+    p.B = left ? X : T; p.ldb = left ? ldx : ldt;
+    p.C = X; p.ldc = ldx;
+    p.tiles_m = (int)((m + 127) / 128); p.tiles_n = (int)((n + 127) / 128);
+    p.tri = 0; p.split_first = 0; p.nsu = 0; p.region_tiles = 0; p.dynamic = 0;
+    p.err = device_error_word();
+    p.sched = sched_words(st);
+    if (!p.err || !p.sched) return -1;
+    const int pair_tiles = left ? p.tiles_m : p.tiles_n, pairs = left ? p.tiles_n : p.tiles_m;
+    p.pair = 0; p.pair_half = 0;
+    if (pair_tiles == 2) {
+        if (pairs > kSchedFlags) return -1;
+        p.pair = left ? 1 : 2;
+        // the tile that only meets its own diagonal block: left, X_i = sum_j op(T)_ij X_j -> row block 0 for a lower
+        // op(T); right, X_j = sum_i X_i op(T)_ij -> column block 1 for a lower op(T)
+        p.pair_half = left ? (lower_op ? 0 : 1) : (lower_op ? 1 : 0);
+    }
+    // one tile along the triangular dimension: the tile's loads are all done before its epilogue stores, and no
+    // other tile touches its rows (columns), so plain in-place is safe as long as the tiles are the large ones
+    const int ta = left ? transT : 0, tb = left ? 0 : transT;
+    int r;
+    if (!ta && !tb)      r = launch_tma<128, 128, 2, 4, MN_MAJOR, K_MAJOR, 3, 1>(st, p, p.A, p.B, false);
+    else if (!ta && tb)  r = launch_tma<128, 128, 2, 4, MN_MAJOR, MN_MAJOR, 3, 1>(st, p, p.A, p.B, false);
+    else if (ta && !tb)  r = launch_tma<128, 128, 2, 4, K_MAJOR, K_MAJOR, 3, 1>(st, p, p.A, p.B, false);
+    else                 r = launch_tma<128, 128, 2, 4, K_MAJOR, MN_MAJOR, 3, 1>(st, p, p.A, p.B, false);
+    return r;
 }
 
 int sm_reserve_swap(int sms)

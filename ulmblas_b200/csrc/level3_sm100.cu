@@ -256,6 +256,9 @@ static void solve_left(TrsmCtx &c, int64_t r0, int64_t len)
     if (c.status != ULMB200_OK) return;
     if (len <= c.leaf) {
         const double *iv = c.inv + (r0 / c.leaf) * c.leaf * c.leaf;
+        // in place where the operands allow it, else through the work tile and a copy back
+        const int r = dgemm_leaf_inplace(c.st, 1, c.eff_lower, c.trans, len, c.n, 1.0, iv, c.leaf, c.B + r0, c.ldb, c.err);
+        if (r >= 0) { c.status = r; return; }
         gemm_chk(c, c.trans, 0, len, c.n, len, 1.0, iv, c.leaf, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
         return;
@@ -283,6 +286,8 @@ static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
     if (c.status != ULMB200_OK) return;
     if (len <= c.leaf) {
         const double *iv = c.inv + (c0 / c.leaf) * c.leaf * c.leaf;
+        const int r = dgemm_leaf_inplace(c.st, 0, c.eff_lower, c.trans, len, c.m, 1.0, iv, c.leaf, c.B + c0 * c.ldb, c.ldb, c.err);
+        if (r >= 0) { c.status = r; return; }
         gemm_chk(c, 0, c.trans, c.m, len, len, 1.0, c.B + c0 * c.ldb, c.ldb, iv, c.leaf, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
         return;
@@ -468,6 +473,8 @@ static void mul_left(TrsmCtx &c, double alpha, int64_t r0, int64_t len)
     if (c.status != ULMB200_OK) return;
     if (len <= c.leaf) {
         const double *tb = c.inv + (r0 / c.leaf) * c.leaf * c.leaf;
+        const int r = dgemm_leaf_inplace(c.st, 1, c.eff_lower, c.trans, len, c.n, alpha, tb, c.leaf, c.B + r0, c.ldb, c.err);
+        if (r >= 0) { c.status = r; return; }
         gemm_chk(c, c.trans, 0, len, c.n, len, alpha, tb, c.leaf, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
         return;
@@ -491,6 +498,8 @@ static void mul_right(TrsmCtx &c, double alpha, int64_t c0, int64_t len)
     if (c.status != ULMB200_OK) return;
     if (len <= c.leaf) {
         const double *tb = c.inv + (c0 / c.leaf) * c.leaf * c.leaf;
+        const int r = dgemm_leaf_inplace(c.st, 0, c.eff_lower, c.trans, len, c.m, alpha, tb, c.leaf, c.B + c0 * c.ldb, c.ldb, c.err);
+        if (r >= 0) { c.status = r; return; }
         gemm_chk(c, 0, c.trans, c.m, len, len, alpha, c.B + c0 * c.ldb, c.ldb, tb, c.leaf, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
         return;
