@@ -19,7 +19,7 @@ end-to-end rate of dgemm_ on pageable host memory.
 `--impl reference` times ulmBLAS's own CPU dgemm_ (oracle/_ref, built from the reference's
 sources) on a bounded sample of the same product.
 
-Tables and single-routine runs (one GPU; the commands the summaries under profiles/ name):
+Tables and single-routine runs (one GPU):
     python bench.py --report [--quick]      every routine, device-resident
     python bench.py --modes 4096            one DGEMM per transposition mode
     python bench.py --small                 DGEMM on small and ragged shapes

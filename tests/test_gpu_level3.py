@@ -271,6 +271,29 @@ def test_dtrsm_all_variants(ulm):
     trsm_check(ulm, "L", "L", "N", "N", 390, 33, 0.0, seed + 2)      # alpha == 0 zeroes B
 
 
+@pytest.mark.parametrize("leaf,dim,other", [(512, 1100, 200), (1024, 2200, 136), (2048, 2100, 130)])
+def test_dtrsm_large_inverted_blocks(ulm, monkeypatch, leaf, dim, other):
+    """Diagonal blocks of order 512, 1024 and 2048 inverted (by batched products from the 256-inverses)
+    and applied in place by the leaf kernel, which multiplies only the blocks of the triangle: every
+    side / uplo / trans / diag, a ragged last block, leading dimensions with padding."""
+    monkeypatch.setenv("ULMB200_TRSM_LEAF", str(leaf))
+    ulm.reload_env()
+    seed = 21000 + leaf
+    for side, uplo, tr, diag in itertools.product("LR", "UL", "NT", "NU"):
+        seed += 2
+        m, n = (dim, other) if side == "L" else (other, dim)
+        trsm_check(ulm, side, uplo, tr, diag, m, n, 0.7 if uplo == "U" else 1.0, seed)
+
+
+def test_dtrsm_chosen_block_order_many_strips(ulm):
+    """The library's own choice (order 1024 from 2048 rows and 1024 right-hand sides on) with more
+    leaf tiles than CTAs, so that tiles are handed out while others still wait for their readers."""
+    trsm_check(ulm, "L", "L", "N", "N", 2304, 2700, 1.0, 21900)
+    trsm_check(ulm, "R", "U", "T", "U", 2700, 2304, 0.7, 21902)
+    trsm_check(ulm, "R", "L", "N", "N", 2700, 2100, 1.0, 21904)
+    trsm_check(ulm, "L", "U", "N", "N", 2100, 2700, 1.0, 21906)
+
+
 def test_config4_dtrsm_8192_sampled_columns(ulm, torch_cuda):
     """DTRSM side=L uplo=L trans=N diag=N, m=n=8192, seed 3, device-resident: diagonal uniform[1,2),
     strict lower uniform[-1,1)/n, strict upper rogue.  Columns of X are independent, so the

@@ -49,8 +49,8 @@ int64_t alloc_count();                   // device allocations made by the libra
 // they end, so launches that follow each other on one stream reuse the block without a
 // memset, and launches on different streams never share one.  nullptr when no block is left
 // (more than kSchedSlots streams in use on the device): the caller then schedules statically.
-constexpr int kSchedFlags = 320;
-constexpr int kSchedWords = 384;
+constexpr int kSchedFlags = 4096;
+constexpr int kSchedWords = 4160;
 constexpr int kSchedSlots = 256;
 int *sched_words(cudaStream_t st);
 
@@ -59,12 +59,14 @@ int *sched_words(cudaStream_t st);
 //   ULMB200_SGEMM=fp32|3xtf32    arithmetic of sgemm_ / cblas_sgemm
 //   ULMB200_WORKSPACE_CAP_MB=n   upper limit of the cached device work memory
 //   ULMB200_DGEMM_TILE=64|128, ULMB200_DGEMM_PATH=ldg, ULMB200_DGEMM_SPLITK=0   (test hooks)
+//   ULMB200_TRSM_LEAF=128|256|512|1024|2048   order of the inverted diagonal blocks of dtrsm (test hook)
 struct Settings {
     int trace = 0;
     int sgemm_3xtf32 = 0;
     int64_t workspace_cap = -1;          // bytes, -1 = none
     int dgemm_tile = 0, dgemm_ldg = 0, dgemm_split = 1;
     int sgemm_path = 0;                  // 0 auto, 1 force the plain-load kernel
+    int trsm_leaf = 0;                   // 0 auto
 };
 const Settings &settings();
 void trace(const char *fmt, ...) __attribute__((format(printf, 1, 2)));
@@ -89,18 +91,31 @@ bool make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, cons
 int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, int64_t n, int64_t k,
                  double alpha, const double *A, int64_t lda, const double *B, int64_t ldb, double beta,
                  double *C, int64_t ldc, int *err_word = nullptr);
-// X <- alpha * op(T) * X (left) or alpha * X * op(T) (right) in place, T block triangular of order dim <= 256 with a
-// truly zero off-diagonal block (dgemm_sm100.cu); -1 when the operands do not qualify
+// X <- alpha * op(T) * X (left) or alpha * X * op(T) (right) in place, T triangular of any order with zeros in the
+// other triangle of its 128 x 128 diagonal blocks (dgemm_sm100.cu); -1 when the operands do not qualify
 int dgemm_leaf_inplace(cudaStream_t st, int left, int lower_op, int transT, int64_t dim, int64_t other, double alpha,
                        const double *T, int64_t ldt, double *X, int64_t ldx, int *err_word);
+// Where product b = hi * nlo + lo of a batch finds its blocks: lo * x[0] + hi * x[1] rows or columns past the
+// blocks of product 0, for the rows and columns of the stored A, B and C.
+struct BatchShape {
+    int count, nlo;
+    int a_row[2], a_col[2], b_row[2], b_col[2];
+    int64_t c_row[2], c_col[2];
+};
+// count products C_b <- alpha * A_b * B_b of one shape in one launch (dgemm_sm100.cu); a_rows .. b_cols are the
+// extents of the stored matrices the blocks are cut from (likewise c_rows, c_cols); -1 when the operands do not qualify
+int dgemm_batched(cudaStream_t st, int64_t m, int64_t n, int64_t k, double alpha, const double *A, int64_t lda,
+                  int64_t a_rows, int64_t a_cols, const double *B, int64_t ldb, int64_t b_rows, int64_t b_cols,
+                  double *C, int64_t ldc, int64_t c_rows, int64_t c_cols, const BatchShape &bs);
 // sets the number of SMs the persistent DGEMM grid leaves free; returns the previous value
 int sm_reserve_swap(int sms);
 int scale_matrix_device(cudaStream_t st, double *C, int64_t ldc, int64_t m, int64_t n, double beta, int tri);
 // B <- alpha*op(A)^-1*B (side 0) or alpha*B*op(A)^-1 (side 1) with caller-provided scratch
-// (level3_sm100.cu): inv holds ceil(dim/128)*128*128 doubles, W 128*n (left) or m*128 (right).
+// (level3_sm100.cu): inv holds ceil(dim/leaf)*leaf*leaf doubles, W leaf*n (left) or m*leaf (right);
+// leaf = 128 or 256, or a larger power of two with pairs = ceil(dim/leaf)*leaf*leaf/4 more doubles.
 int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                        double alpha, const double *A, int64_t lda, double *B, int64_t ldb, double *inv,
-                       double *W, int *err_word = nullptr, int leaf = 128);
+                       double *W, int *err_word = nullptr, int leaf = 128, double *pairs = nullptr);
 
 #ifdef __CUDACC__
 // ---- device-side PTX wrappers ---------------------------------------------
@@ -174,6 +189,32 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y),
         "r"(smem_u32(bar))
         : "memory");
+}
+
+// One 2-D TMA tile store from shared memory (rows and columns outside the tensor are clipped); part of
+// the thread's current bulk group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int32_t x, int32_t y, const void *smem_src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// every bulk group of this thread has read its shared-memory source
+__device__ __forceinline__ void bulk_wait_read_all()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// every bulk group of this thread is complete
+__device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map)

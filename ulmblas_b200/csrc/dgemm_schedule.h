@@ -27,9 +27,10 @@ namespace ulmb200 {
 
 constexpr int kRegionMax = 160;           // most tiles the shared region of a launch may hold
 
-// Cost of one epilogue (read-modify-write of a C tile) in units of one pipeline stage of the
-// main loop; only used to decide whether sharing the last tiles pays.
-constexpr int kEpilogueStages = 2;
+// Cost of the epilogue of a piece of a shared tile (the consumers' own read-modify-write of the C
+// tile, about 9 us) in units of one pipeline stage of the main loop (2.1 us); only used to decide
+// whether sharing the last tiles pays.
+constexpr int kEpilogueStages = 4;
 
 struct Piece {
     int r;          // index of the tile within the region

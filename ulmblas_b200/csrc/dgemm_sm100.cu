@@ -46,28 +46,80 @@ struct GemmParams {
     // last full wave are shared evenly by all CTAs instead of idling most of them.
     int split_first, nsu, region_tiles;
     unsigned short rtile[kRegionMax];   // tri != 0: tile id - split_first of region tile r
-    // In-place product with a block-triangular first or second operand (the leaf of the triangular
-    // solver and multiply: C is the very block of B that is being read).  pair = 1: two tile rows over
-    // each tile column, pair = 2: two tile columns over each tile row.  Unit 2q is the tile of pair q
-    // that needs all of K; unit 2q+1 is tile number pair_half of the pair, which only meets its own
-    // diagonal block of the triangular operand (stages [8*pair_half, ...)) and whose output region
-    // the other tile still reads: it stores only after the other tile's loads have all landed
-    // (flag q of the scheduler words).  0: off.
-    int pair, pair_half;
+    // In-place product with a triangular first or second operand (the leaf of the triangular solver
+    // and multiply: C is the very block of B that is being read).  The triangular operand spans T
+    // tiles; the other dimension is cut into strips of one tile.  The tile at place d of a strip
+    // meets only d + 1 (low) or T - d (high) blocks of 128 k, and the rows (columns) it writes are
+    // what the longer tiles of its strip still read.  So the units go out longest first, each tile
+    // counts, per block of k, the loads it has seen land, and a tile stores only when every longer
+    // tile of its strip has counted its block (word [2 + strip * T + d] of the scheduler words; the
+    // storing tile puts it back to zero).  A tile waits only for units handed out before its own.
+    //   1: left,  op(T) lower: tile row d multiplies blocks 0..d, units by falling d
+    //   2: left,  op(T) upper: blocks d..T-1, units by rising d, blocks taken from the last down
+    //   3: right, op(T) upper: tile column d multiplies blocks 0..d
+    //   4: right, op(T) lower: blocks d..T-1
+    int leaf;
+    // Many products of one shape in one launch: product b = hi * bat_nlo + lo of nbatch shifts the tile
+    // coordinates of op(A) by lo * bat_am[0] + hi * bat_am[1] rows and ..ak.. columns (of k), those of
+    // op(B) likewise, and C by bat_c elements.  Whole tiles only; k is a multiple of the stage depth.
+    int nbatch, bat_nlo;
+    int bat_am[2], bat_ak[2], bat_bn[2], bat_bk[2];
+    int64_t bat_c[2];
+    int bat_cr[2], bat_cc[2];     // the same shift of C as rows and columns
+    int c_tma;                    // the third tensor map covers C: whole tiles leave through shared memory
+    // host side only: extents of the stored operands when they differ from the product's (batches)
+    int64_t ext_a_mn, ext_a_k, ext_b_mn, ext_b_k, ext_c_m, ext_c_n;
 };
 
-// pair mode: unit -> tile coordinates and the range of pipeline stages it multiplies
-__device__ __forceinline__ void pair_decode(const GemmParams &p, int unit, int kt, int &tm, int &tn, int &kc0, int &kc1)
+// What the output thread needs to know about a tile that will leave through the buffer.
+struct StashInfo {
+    int row, col;            // first row and column of the tile in C (batch shift included)
+    int load;                // beta != 0: the old tile is fetched into the buffer first
+    int unit;                // -1: no more tiles
+    int wait_idx, expect;    // leaf mode: the counter that must reach expect before C may be written, -1 = none
+};
+
+// leaf mode: unit -> tile coordinates, the range of pipeline stages it multiplies and its place
+struct LeafUnit {
+    int tm, tn, kc0, kc1, d, strip, T, rev, expect;
+};
+__device__ __forceinline__ LeafUnit leaf_decode(const GemmParams &p, int unit, int kt)
 {
-    const int q = unit >> 1, late = unit & 1;
-    const int which = late ? p.pair_half : 1 - p.pair_half;
-    if (p.pair == 1) { tm = which; tn = q; } else { tm = q; tn = which; }
-    constexpr int HB = 128 / kBK;                    // stages per 128 k = one tile's worth of the triangular operand
-    kc0 = 0; kc1 = kt;
-    if (late) {
-        if (p.pair_half == 0) kc1 = kt < HB ? kt : HB;
-        else kc0 = HB < kt ? HB : kt;
-    }
+    constexpr int HB = 128 / kBK;                    // stages per block of 128 k
+    LeafUnit u;
+    const bool left = p.leaf <= 2;
+    const bool low = p.leaf == 1 || p.leaf == 3;
+    u.T = left ? p.tiles_m : p.tiles_n;
+    const int S = left ? p.tiles_n : p.tiles_m;
+    const int r = unit / S;
+    u.strip = unit - r * S;
+    u.d = low ? u.T - 1 - r : r;
+    u.tm = left ? u.d : u.strip;
+    u.tn = left ? u.strip : u.d;
+    if (low) { u.kc0 = 0; u.kc1 = (u.d + 1) * HB < kt ? (u.d + 1) * HB : kt; }
+    else     { u.kc0 = u.d * HB < kt ? u.d * HB : kt; u.kc1 = kt; }
+    u.rev = low ? 0 : 1;
+    u.expect = low ? u.T - 1 - u.d : u.d;            // longer tiles of the strip: they all read block d
+    return u;
+}
+
+// batch mode: coordinate shifts of product b
+struct BatchShift {
+    int am, ak, bn, bk, cr, cc;
+    int64_t c;
+};
+__device__ __forceinline__ BatchShift batch_shift(const GemmParams &p, int b)
+{
+    const int hi = b / p.bat_nlo, lo = b - hi * p.bat_nlo;
+    BatchShift s;
+    s.am = lo * p.bat_am[0] + hi * p.bat_am[1];
+    s.ak = lo * p.bat_ak[0] + hi * p.bat_ak[1];
+    s.bn = lo * p.bat_bn[0] + hi * p.bat_bn[1];
+    s.bk = lo * p.bat_bk[0] + hi * p.bat_bk[1];
+    s.c = lo * p.bat_c[0] + hi * p.bat_c[1];
+    s.cr = lo * p.bat_cr[0] + hi * p.bat_cr[1];
+    s.cc = lo * p.bat_cc[0] + hi * p.bat_cc[1];
+    return s;
 }
 
 
@@ -144,14 +196,14 @@ __device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32
 // two rows a lane holds are adjacent (2g, 2g+1), so a 16-byte aligned C moves them as one
 // 16-byte access.
 template <int MAJOR_A, int MAJOR_B, int MT, int NT, int G>
-__device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64_t m0, int64_t n0, int wm0,
-                                         int wn0, int lane, double (&acc)[MT][NT][4])
+__device__ __forceinline__ void epilogue(const GemmParams &p, double *__restrict__ C, double beta, int64_t m0, int64_t n0,
+                                         int wm0, int wn0, int lane, double (&acc)[MT][NT][4])
 {
     static_assert(MT % G == 0, "m16 tiles are taken G at a time");
     const double alpha = p.alpha;
     const bool use_c = beta != 0.0;
     const bool vec = MAJOR_A == MN_MAJOR && p.tri == 0 &&
-                     ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.ldc % 2 == 0);
+                     ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (p.ldc % 2 == 0);
 #pragma unroll
     for (int i0 = 0; i0 < MT; i0 += G) {
         double old[G][NT][4];
@@ -171,7 +223,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64
                         const bool v = col < p.n;
                         ok[g][j][w] = ok[g][j][2 + w] = v;
                         double2 o = make_double2(0.0, 0.0);
-                        if (use_c && v) o = *reinterpret_cast<const double2 *>(p.C + r0 + col * p.ldc);
+                        if (use_c && v) o = *reinterpret_cast<const double2 *>(C + r0 + col * p.ldc);
                         old[g][j][w] = o.x; old[g][j][2 + w] = o.y;
                     }
             } else {
@@ -185,7 +237,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64
                         if (p.tri == 1) v = v && row <= col;
                         if (p.tri == 2) v = v && row >= col;
                         ok[g][j][e] = v;
-                        old[g][j][e] = (v && use_c) ? p.C[row + col * p.ldc] : 0.0;
+                        old[g][j][e] = (v && use_c) ? C[row + col * p.ldc] : 0.0;
                     }
             }
         }
@@ -205,7 +257,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64
                             o.x = alpha * acc[i][j][w];
                             o.y = alpha * acc[i][j][2 + w];
                             if (use_c) { o.x = fma(beta, old[g][j][w], o.x); o.y = fma(beta, old[g][j][2 + w], o.y); }
-                            *reinterpret_cast<double2 *>(p.C + r0 + col * p.ldc) = o;
+                            *reinterpret_cast<double2 *>(C + r0 + col * p.ldc) = o;
                         }
                     }
             } else {
@@ -218,7 +270,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, double beta, int64
                             const int64_t col = n0 + c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
                             double v = alpha * acc[i][j][e];
                             if (use_c) v = fma(beta, old[g][j][e], v);
-                            p.C[row + col * p.ldc] = v;
+                            C[row + col * p.ldc] = v;
                         }
                     }
             }
@@ -280,7 +332,7 @@ __host__ __device__ __forceinline__ bool tile_skipped(int tri, int64_t m0, int64
 template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B, int STAGES, int MIN_CTAS>
 __global__ void __launch_bounds__((WARPS_M *WARPS_N + 4) * 32, MIN_CTAS)
 dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p)
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p)
 {
     constexpr int NCW = WARPS_M * WARPS_N;          // consumer warps
     constexpr int WM = BM / WARPS_M, WN = BN / WARPS_N;
@@ -293,9 +345,23 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // 1024-byte alignment: the swizzle pattern is a function of the address
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                 ~uintptr_t(1023));
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    // The one-CTA-per-SM shape sends finished tiles out through a tile-sized buffer in shared memory when a
+    // tensor map covers C.  One thread of the producer group fetches the old tile into the buffer by TMA while
+    // the tile is being multiplied (beta != 0), the consumers fold alpha * acc into it and go on with the next
+    // tile, and the same thread stores the buffer by TMA while the tensor pipe is busy again: no consumer
+    // waits for global memory.  Tiles the map cannot serve (a tile across the diagonal of a triangular
+    // update, pieces of shared tiles) are written by the consumers themselves.
+    constexpr bool STASH = (MIN_CTAS == 1);
+    constexpr uint32_t STASH_BYTES = STASH ? BM * BN * 8 : 0;
+    constexpr int CBOX = 32;                                                        // columns per TMA box of C
+    double *stash = reinterpret_cast<double *>(smem + STAGES * STAGE_BYTES);      // column-major BM x BN
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES + STASH_BYTES);
     uint64_t *empty = full + STAGES;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + STAGES);
+    uint64_t *tile_started = empty + STAGES;       // consumers -> output thread: a tile's place is in info[]
+    uint64_t *stash_ready = tile_started + 1;      // output thread -> consumers: buffer free / old tile landed
+    uint64_t *stash_full = stash_ready + 1;        // consumers -> output thread: the new tile is in the buffer
+    StashInfo *info = reinterpret_cast<StashInfo *>(stash_full + 1);               // [2], tiles alternate
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(info + 2);
     volatile int *tile_slot = abort_flag + 1;      // tile id carried by each stage, -1 = no more work
 
     const int warp = threadIdx.x >> 5;
@@ -306,10 +372,14 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NCW);
         }
+        mbar_init(tile_started, 1);
+        mbar_init(stash_ready, 1);
+        mbar_init(stash_full, NCW);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
+        if (STASH && p.c_tma) prefetch_tmap(&tmC);
     }
     __syncthreads();
 
@@ -318,7 +388,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     constexpr bool REBALANCE = (NCW == 8 && MIN_CTAS == 1);
     constexpr bool SHARE = (MIN_CTAS == 1);          // only the one-CTA-per-SM shape shares tiles
-    constexpr int EG = 1;   // m16 tiles per round of the epilogue (2 would need more registers than the 168 the kernel is built with)
+    constexpr int EG = 1;   // m16 tiles whose old C values are fetched together (2 makes the 128 x 128 kernels spill)
     if (warp >= NCW) {
         // ---------------- producer warpgroup ----------------
         if (REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -329,8 +399,10 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // whole grid with a fixed share.
             uint32_t it = 0;
             bool live = true;
-            // loads the stages [kc0, kc1) of the tile at (m0, n0); false once the kernel has given up
-            auto load_piece = [&](int unit, int64_t m0, int64_t n0, int kc0, int kc1) -> bool {
+            // loads the stages [kc0, kc1) of the tile at (m0, n0), from the last down if rev; ak and bk
+            // shift the k coordinate of either operand (batches); false once the kernel has given up
+            auto load_piece = [&](int unit, int64_t m0, int64_t n0, int kc0, int kc1, bool rev = false, int ak = 0,
+                                  int bk = 0) -> bool {
                 for (int kc = kc0; kc < kc1; ++kc, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
@@ -341,30 +413,35 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     tile_slot[s] = unit;
                     uint8_t *sa = smem + s * STAGE_BYTES, *sb = sa + A_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    const int k0 = kc * kBK;
+                    const int k0 = (rev ? kc0 + kc1 - 1 - kc : kc) * kBK;
                     if (MAJOR_A == K_MAJOR) {
-                        tma_load_2d(sa, &tmA, k0, (int)m0, &full[s]);
+                        tma_load_2d(sa, &tmA, k0 + ak, (int)m0, &full[s]);
                     } else {
 #pragma unroll
                         for (int b = 0; b < BM / 16; ++b)
-                            tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0, &full[s]);
+                            tma_load_2d(sa + b * 2048, &tmA, (int)m0 + 16 * b, k0 + ak, &full[s]);
                     }
                     if (MAJOR_B == K_MAJOR) {
-                        tma_load_2d(sb, &tmB, k0, (int)n0, &full[s]);
+                        tma_load_2d(sb, &tmB, k0 + bk, (int)n0, &full[s]);
                     } else {
 #pragma unroll
                         for (int b = 0; b < BN / 16; ++b)
-                            tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0, &full[s]);
+                            tma_load_2d(sb + b * 2048, &tmB, (int)n0 + 16 * b, k0 + bk, &full[s]);
                     }
                 }
                 return true;
             };
             int unit = blockIdx.x;
             while (live && unit < num_units) {
-                if (SHARE && p.pair) {
-                    int tm, tn, kc0, kc1;
-                    pair_decode(p, unit, kt, tm, tn, kc0, kc1);
-                    live = load_piece(unit, (int64_t)tm * BM, (int64_t)tn * BN, kc0, kc1);
+                if (SHARE && p.leaf) {
+                    const LeafUnit u = leaf_decode(p, unit, kt);
+                    live = load_piece(unit, (int64_t)u.tm * BM, (int64_t)u.tn * BN, u.kc0, u.kc1, u.rev != 0);
+                } else if (SHARE && p.nbatch > 1) {
+                    const int per = p.tiles_m * p.tiles_n, b = unit / per;
+                    int tm, tn;
+                    tile_coord(unit - b * per, p.tiles_m, p.tiles_n, tm, tn);
+                    const BatchShift sh = batch_shift(p, b);
+                    live = load_piece(unit, (int64_t)tm * BM + sh.am, (int64_t)tn * BN + sh.bn, 0, kt, false, sh.ak, sh.bk);
                 } else if (!SHARE || unit < p.split_first) {
                     int tm, tn;
                     tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
@@ -410,6 +487,57 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         __nanosleep(256);
             }
         }
+        if (STASH && warp == NCW + 1 && lane == 0 && p.c_tma) {
+            // ---------------- output thread ----------------
+            for (uint32_t nt = 0;; ++nt) {
+                const StashInfo *I = info + (nt & 1);
+                if (*abort_flag) break;
+                if (!mbar_wait(tile_started, nt & 1)) {
+                    if (!*abort_flag) {                    // not merely left behind by consumers that gave up
+                        *abort_flag = 1;
+                        atomicExch(p.err, 105);
+                    }
+                    break;
+                }
+                if (I->unit < 0) break;
+                const int row = I->row, col = I->col;
+                const int wait_idx = I->wait_idx, expect = I->expect;
+                // the buffer is free: the stores of the tile before this one have read it (end of the loop body)
+                if (I->load) {
+                    mbar_expect_tx(stash_ready, BM * BN * 8);
+#pragma unroll
+                    for (int b = 0; b < BN / CBOX; ++b)
+                        tma_load_2d(stash + b * CBOX * BM, &tmC, row, col + CBOX * b, stash_ready);
+                } else {
+                    mbar_arrive(stash_ready);
+                }
+                if (!mbar_wait(stash_full, nt & 1)) {
+                    if (!*abort_flag) {
+                        *abort_flag = 1;
+                        atomicExch(p.err, 105);
+                    }
+                    break;
+                }
+                if (wait_idx >= 0) {
+                    // in-place leaf: the longer tiles of the strip must have read these rows (columns) first
+                    int *cnt = p.sched + 2 + wait_idx;
+                    bool ok = false;
+                    for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                        ok = *reinterpret_cast<volatile int *>(cnt) == expect;
+                        if (!ok) __nanosleep(64);
+                    }
+                    if (!ok) { *abort_flag = 1; atomicExch(p.err, 104); break; }
+                    atomicExch(cnt, 0);                    // back to zero for the next launch on this stream
+                    __threadfence();
+                }
+#pragma unroll
+                for (int b = 0; b < BN / CBOX; ++b)
+                    tma_store_2d(&tmC, row, col + CBOX * b, stash + b * CBOX * BM);
+                bulk_commit_group();
+                bulk_wait_read_all();
+            }
+            bulk_wait_all();
+        }
         return;
     }
 
@@ -447,6 +575,71 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         return true;
     };
 
+    // A tile leaves through the buffer if the tensor map of C can serve it: not a tile across the diagonal
+    // of a triangular update, whose other half must stay untouched.
+    auto through_stash = [&](int m0, int n0) -> bool {
+        if (!STASH || !p.c_tma) return false;
+        if (p.tri == 1) return m0 + BM - 1 <= n0;
+        if (p.tri == 2) return m0 >= n0 + BN - 1;
+        return true;
+    };
+    // Tells the output thread where the tile that is about to be multiplied goes (unit < 0: no more tiles).
+    uint32_t nstash = 0;
+    auto announce_tile = [&](int unit, int row, int col, bool load, int wait_idx, int expect) {
+        if (threadIdx.x == 0) {
+            StashInfo *I = info + (nstash & 1);
+            I->row = row; I->col = col; I->load = load ? 1 : 0;
+            I->unit = unit; I->wait_idx = wait_idx; I->expect = expect;
+            mbar_arrive(tile_started);
+        }
+    };
+    // Folds the finished tile into the buffer (alpha * acc + beta * old) and hands it to the output thread;
+    // false once the kernel has given up.
+    auto stash_tile = [&](double beta) -> bool {
+        if (*abort_flag || !mbar_wait(stash_ready, nstash & 1)) {
+            *abort_flag = 1;
+            atomicExch(p.err, 106);
+            return false;
+        }
+        ++nstash;
+        const double alpha = p.alpha;
+        const bool use_c = beta != 0.0;
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                if (MAJOR_A == MN_MAJOR) {
+                    // the two rows a lane holds are adjacent: one 16-byte access per column
+                    const int r0 = c_row<MAJOR_A>(wm0 + 16 * i, lane, 0);
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        const int col = c_col<MAJOR_B>(wn0 + 8 * j, lane, w);
+                        double2 *at = reinterpret_cast<double2 *>(stash + col * BM + r0);
+                        double2 v = make_double2(alpha * acc[i][j][w], alpha * acc[i][j][2 + w]);
+                        if (use_c) {
+                            const double2 o = *at;
+                            v.x = fma(beta, o.x, v.x);
+                            v.y = fma(beta, o.y, v.y);
+                        }
+                        *at = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int row = c_row<MAJOR_A>(wm0 + 16 * i, lane, e >> 1);
+                        const int col = c_col<MAJOR_B>(wn0 + 8 * j, lane, e & 1);
+                        double v = alpha * acc[i][j][e];
+                        if (use_c) v = fma(beta, stash[col * BM + row], v);
+                        stash[col * BM + row] = v;
+                    }
+                }
+            }
+        fence_proxy_async();                 // the TMA store reads what this thread has just written
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stash_full);
+        return true;
+    };
+
     for (;;) {
         // the first stage of a unit tells which unit it is
         {
@@ -458,38 +651,67 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
         }
         const int unit = tile_slot[it % STAGES];
-        if (unit < 0) return;
-        if (SHARE && p.pair) {
-            int tm, tn, kc0, kc1;
-            pair_decode(p, unit, kt, tm, tn, kc0, kc1);
-            if (!run_piece(kc0, kc1, true)) return;
-            int *flag = p.sched + 2 + (unit >> 1);
-            if ((unit & 1) == 0) {
-                // every load of this tile has landed (each stage was waited for): its partner may store
-                if (threadIdx.x == 0) { __threadfence(); atomicExch(flag, 1); }
-            } else {
-                if (threadIdx.x == 0) {
-                    bool ok = false;
-                    for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
-                        ok = *reinterpret_cast<volatile int *>(flag) == 1;
-                        if (!ok) __nanosleep(64);
-                    }
-                    if (!ok) { *abort_flag = 1; atomicExch(p.err, 104); }
-                    else atomicExch(flag, 0);              // back to zero for the next launch on this stream
+        if (unit < 0) {
+            if (STASH && p.c_tma) announce_tile(-1, 0, 0, false, -1, 0);      // the output thread leaves after the last tile
+            return;
+        }
+        if (SHARE && p.leaf) {
+            constexpr int HB = 128 / kBK;
+            const LeafUnit u = leaf_decode(p, unit, kt);
+            int *cnt = p.sched + 2 + u.strip * u.T;
+            // the output thread stores once every longer tile of the strip has counted block d
+            announce_tile(unit, u.tm * BM, u.tn * BN, false, u.expect > 0 ? u.strip * u.T + u.d : -1, u.expect);
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0;
+            for (int kc = u.kc0; kc < u.kc1; ++kc, ++it) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (kc != u.kc0 && (*abort_flag || !mbar_wait(&full[s], ph))) {
+                    *abort_flag = 1;
+                    atomicExch(p.err, 102);
+                    return;
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-                if (*abort_flag) return;
-                __threadfence();
+                // the last stage of a block of k has landed: the tile that will overwrite those rows
+                // (columns) of the strip has one reader less to wait for
+                if (threadIdx.x == 0) {
+                    const int kk = u.rev ? u.kc0 + u.kc1 - 1 - kc : kc;
+                    const int blk = kk / HB;
+                    const bool last_of_block = u.rev ? (kk % HB == 0 || kc + 1 == u.kc1) : (kk % HB == HB - 1 || kc + 1 == u.kc1);
+                    if (last_of_block && blk != u.d) atomicAdd(cnt + blk, 1);
+                }
+                const uint32_t sA = smem_base + s * STAGE_BYTES;
+                mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
             }
-            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
+            if (!stash_tile(0.0)) return;
+            continue;
+        }
+        if (SHARE && p.nbatch > 1) {
+            const int per = p.tiles_m * p.tiles_n, b = unit / per;
+            int tm, tn;
+            tile_coord(unit - b * per, p.tiles_m, p.tiles_n, tm, tn);
+            const BatchShift sh = batch_shift(p, b);
+            announce_tile(unit, tm * BM + sh.cr, tn * BN + sh.cc, false, -1, 0);
+            if (!run_piece(0, kt, true)) return;
+            if (!stash_tile(0.0)) return;
             continue;
         }
         if (!SHARE || unit < p.split_first) {
             int tm, tn;
             tile_coord(unit, p.tiles_m, p.tiles_n, tm, tn);
+            if (through_stash(tm * BM, tn * BN)) {
+                announce_tile(unit, tm * BM, tn * BN, p.beta != 0.0, -1, 0);
+                if (!run_piece(0, kt, true)) return;
+                if (!stash_tile(p.beta)) return;
+                continue;
+            }
             if (SHARE && p.beta != 0.0) prefetch_c<MAJOR_A, MAJOR_B, MT, NT>(p, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane);
             if (!run_piece(0, kt, true)) return;
-            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
+            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.C, p.beta, (int64_t)tm * BM, (int64_t)tn * BN, wm0, wn0, lane, acc);
             continue;
         }
         StreamWalk walk(p.region_tiles, p.nsu, unit - p.split_first, kt);
@@ -499,11 +721,19 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int tm, tn;
             tile_coord(region_tile(p, pc.r), p.tiles_m, p.tiles_n, tm, tn);
             const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
+            const bool whole = pc.kc0 == 0 && pc.kc1 == kt;
+            if (whole && through_stash((int)m0, (int)n0)) {
+                announce_tile(unit, (int)m0, (int)n0, p.beta != 0.0, -1, 0);
+                if (!run_piece(pc.kc0, pc.kc1, first)) return;
+                first = false;
+                if (!stash_tile(p.beta)) return;
+                continue;
+            }
             if (pc.kc0 > 0 || p.beta != 0.0) prefetch_c<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane);
             if (!run_piece(pc.kc0, pc.kc1, first)) return;
             first = false;
-            if (pc.kc0 == 0 && pc.kc1 == kt) {
-                epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+            if (whole) {
+                epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.C, p.beta, m0, n0, wm0, wn0, lane, acc);
                 continue;
             }
             // A shared tile.  Its pieces fold into C in order of k: the head [0, x) applies beta and
@@ -524,7 +754,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (*abort_flag) return;
                 __threadfence();
             }
-            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, pc.kc0 > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
+            epilogue<MAJOR_A, MAJOR_B, MT, NT, EG>(p, p.C, pc.kc0 > 0 ? 1.0 : p.beta, m0, n0, wm0, wn0, lane, acc);
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
             if (threadIdx.x == 0) atomicExch(flag, pc.kc1 == kt ? 0 : pc.kc1);
@@ -628,7 +858,7 @@ dgemm_ldg_kernel(const GemmParams p)
         }
         __syncthreads();
     }
-    epilogue<MAJOR_A, MAJOR_B, MT, NT, 1>(p, p.beta, m0, n0, wm0, wn0, lane, acc);
+    epilogue<MAJOR_A, MAJOR_B, MT, NT, 1>(p, p.C, p.beta, m0, n0, wm0, wn0, lane, acc);
 }
 
 // C <- beta*C (beta == 0 assigns zeros), the alpha == 0 / k == 0 quick path
@@ -671,17 +901,31 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     CUtensorMap tmA, tmB;
     bool ok;
     // K-major: dim0 = k (contiguous), dim1 = m|n, box 16 x BM|BN.  MN-major: dim0 = m|n, dim1 = k, box 16 x 16.
+    const int64_t am = p.ext_a_mn ? p.ext_a_mn : p.m, ak = p.ext_a_k ? p.ext_a_k : p.k;
+    const int64_t bn = p.ext_b_mn ? p.ext_b_mn : p.n, bk = p.ext_b_k ? p.ext_b_k : p.k;
     if (MAJOR_A == K_MAJOR)
-        ok = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, A, p.k, p.m, p.lda, kBK, BM);
+        ok = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, A, ak, am, p.lda, kBK, BM);
     else
-        ok = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, A, p.m, p.k, p.lda, 16, kBK);
+        ok = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, A, am, ak, p.lda, 16, kBK);
     if (MAJOR_B == K_MAJOR)
-        ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, p.k, p.n, p.ldb, kBK, BN);
+        ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, bk, bn, p.ldb, kBK, BN);
     else
-        ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, p.n, p.k, p.ldb, 16, kBK);
+        ok = ok && make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, B, bn, bk, p.ldb, 16, kBK);
     if (!ok) return -1;   // caller falls back to the ldg kernel
+    // C for the one-CTA-per-SM shape: boxes of BM rows x 32 columns, no swizzle.  Without a map (odd ldc,
+    // unaligned C) the consumers write C themselves.
+    GemmParams q = p;
+    CUtensorMap tmC = tmA;
+    q.c_tma = 0;
+    if (ctas_per_sm == 1 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 2 == 0 && p.ldc < (1ll << 36)) {
+        const int64_t cm = p.ext_c_m ? p.ext_c_m : p.m, cn = p.ext_c_n ? p.ext_c_n : p.n;
+        q.c_tma = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.C, cm, cn, p.ldc, BM, 32,
+                               CU_TENSOR_MAP_SWIZZLE_NONE) ? 1 : 0;
+    }
+    if ((p.leaf || p.nbatch > 1) && !q.c_tma) return -1;     // those tiles only leave through the buffer
 
-    constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * 128 + 2 * STAGES * 8 + 16 + 4 * STAGES + 1024;
+    constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * 128 + (CTAS_PER_SM == 1 ? (size_t)BM * BN * 8 : 0) +
+                            (2 * STAGES + 3) * 8 + 2 * sizeof(StashInfo) + 16 + 4 * STAGES + 1024;
     auto kern = dgemm_tma_kernel<BM, BN, WARPS_M, WARPS_N, MAJOR_A, MAJOR_B, STAGES, CTAS_PER_SM>;
     static bool attr_done[kMaxDevices] = {};
     const int dev = current_device();
@@ -689,11 +933,10 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
         ULMB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
         attr_done[dev] = true;
     }
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int tiles = p.tiles_m * p.tiles_n * (p.nbatch > 1 ? p.nbatch : 1);
     int sms = sm_count() - g_sm_reserve.load(std::memory_order_relaxed);
     if (sms < 1) sms = 1;
     const int slots = sms * ctas_per_sm;
-    GemmParams q = p;
     q.split_first = tiles; q.nsu = 0; q.region_tiles = 0;
     const int kt = (int)((p.k + kBK - 1) / kBK);
     const int mode = settings().dgemm_split;
@@ -701,8 +944,8 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     // SMs idle for a whole tile time (a SYRK of order 8192: 2080 tiles = 14 waves + 8 tiles; a
     // 1024^3 product: 64 tiles on 148 SMs).  Those tiles' pipeline stages are dealt out evenly to
     // all CTAs instead, whenever that is cheaper than one more wave of whole tiles.
-    if (p.pair) {
-        // in-place leaf: two units per pair of tiles, no sharing
+    if (p.leaf || p.nbatch > 1) {
+        // in-place leaf, batch: one unit per tile, no sharing
         q.split_first = tiles;
     } else if (mode != 0 && may_share && p.sched && ctas_per_sm == 1 && tiles < (1 << 30)) {
         auto real = [&](int id) {
@@ -731,14 +974,14 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
             }
         }
     }
-    const int64_t units = p.pair ? (int64_t)tiles : (int64_t)q.split_first + q.nsu;
+    const int64_t units = (int64_t)q.split_first + q.nsu;
     const int grid = (int)(units < slots ? units : slots);
     // More units than CTAs: they are handed out through the stream's counter word.  Without
     // scheduler words (none left for this stream) the CTAs stride through the units instead.
     q.dynamic = (units > grid && p.sched) ? 1 : 0;
     trace("dgemm kernel tile %dx%d %s grid %d units %lld (whole %d, shared tiles %d over %d CTAs) kt %d",
           BM, BN, q.dynamic ? "dynamic" : "static", grid, (long long)units, q.split_first, q.region_tiles, q.nsu, kt);
-    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, q);
+    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, tmC, q);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
     return ULMB200_OK;
@@ -768,13 +1011,14 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
     // Tile shape by estimated time.  Large tiles (128 x 128, one CTA per SM) run the tensor pipe best and
     // can share the last tiles' stages among all CTAs; small tiles (64 x 64, two CTAs per SM) waste less
     // on padding and fill the machine with fewer rows and columns.  Per-SM times in microseconds,
-    // measured on this part: one 16-k stage of a large tile 2.09, of a small tile 1.05 when two CTAs
-    // share the SM and 0.70 when one has it alone; an epilogue 3 / 2.
+    // measured on this part: one 16-k stage of a large tile 2.09, of a small tile 1.15 when two CTAs
+    // share the SM (their operand traffic from L2 is twice the large tiles') and 0.70 when one has it
+    // alone; an epilogue 1 (large tiles leave through shared memory beside the next tile's main loop) / 2.
     const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
     const int64_t t64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
     const int kt = (int)((p.k + kBK - 1) / kBK);
     const int sms = sm_count();
-    constexpr double kStage128 = 2.09, kStage64Pair = 1.05, kStage64Alone = 0.70, kEpi128 = 3.0, kEpi64 = 2.0;
+    constexpr double kStage128 = 2.09, kStage64Pair = 1.15, kStage64Alone = 0.70, kEpi128 = 1.0, kEpi64 = 2.0;
     double time128 = (double)((t128 + sms - 1) / sms) * (kt * kStage128 + kEpi128);
     if (tma_ok && may_share && p.sched && cfg.dgemm_split != 0 && p.tri == 0) {
         const SharePlan sp = plan_shared_tiles(t128, kt, sms, false);
@@ -823,12 +1067,13 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
 
     if (alpha == 0.0 || k == 0) return set_status(scale_matrix_device(st, C, ldc, m, n, beta, tri));
 
-    GemmParams p;
+    GemmParams p = {};
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = beta;
     p.A = A; p.B = B; p.lda = lda; p.ldb = ldb; p.C = C; p.ldc = ldc;
     p.tiles_m = p.tiles_n = 0; p.tri = tri;
     p.split_first = 0; p.nsu = 0; p.region_tiles = 0; p.dynamic = 0;
-    p.pair = 0; p.pair_half = 0;
+    p.leaf = 0; p.nbatch = 0; p.bat_nlo = 1;
+    p.ext_a_mn = p.ext_a_k = p.ext_b_mn = p.ext_b_k = p.ext_c_m = p.ext_c_n = 0;
     // A caller that brings its own error word must not allocate device memory: its launches take the
     // two words after the error word as tile counter and never share tiles (no fold flags there).
     // Such callers keep their calls on one device from overlapping, so the words are theirs alone.
@@ -850,42 +1095,39 @@ int dgemm_device(cudaStream_t st, int tri, int transA, int transB, int64_t m, in
     return set_status(r);
 }
 
-// X <- op(T) * X (left) or X * op(T) (right) in place, T a block-triangular matrix of order dim <= 256
-// whose off-diagonal zero block is really zero (the inverted or zero-filled diagonal blocks of the
+// X <- op(T) * X (left) or X * op(T) (right) in place, T a triangular matrix of order dim whose 128 x 128
+// diagonal blocks hold zeros in the other triangle (the inverted or zero-filled diagonal blocks of the
 // triangular solver and multiply): the leaf of ulmBLAS's trlsm / trusm / trlmm / trumm recursion
 // (ulmblas/level3/trlsm.tcc:61-74), without their packed copy of the block row.  lower_op: op(T) is
-// lower triangular.  Returns -1 when the operands do not qualify (not TMA-addressable, no scheduler
-// words, too many tiles); the caller then multiplies into a work tile and copies back.
+// lower triangular.  Blocks of T beyond the diagonal ones in the other triangle are never read.
+// Returns -1 when the operands do not qualify (not TMA-addressable, no scheduler words, more tiles
+// than counters); the caller then multiplies into a work tile and copies back.
 int dgemm_leaf_inplace(cudaStream_t st, int left, int lower_op, int transT, int64_t dim, int64_t other, double alpha,
                        const double *T, int64_t ldt, double *X, int64_t ldx, int *err_word)
 {
     if (dim <= 0 || other <= 0) return ULMB200_OK;
-    if (dim > 256 || err_word) return -1;
+    if (err_word) return -1;
     const int64_t m = left ? dim : other, n = left ? other : dim, k = dim;
     const bool tma_ok = ((reinterpret_cast<uintptr_t>(T) | reinterpret_cast<uintptr_t>(X)) & 15) == 0 &&
-                        (ldt % 2 == 0) && (ldx % 2 == 0) && other < (1ll << 31) - 256 && ldx < (1ll << 36);
+                        (ldt % 2 == 0) && (ldx % 2 == 0) && other < (1ll << 31) - 256 && dim < (1ll << 31) - 256 &&
+                        ldx < (1ll << 36) && ldt < (1ll << 36);
     if (!tma_ok) return -1;
-    GemmParams p;
+    GemmParams p = {};
     p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = 0.0;
     p.A = left ? T : X; p.lda = left ? ldt : ldx;
     p.B = left ? X : T; p.ldb = left ? ldx : ldt;
     p.C = X; p.ldc = ldx;
     p.tiles_m = (int)((m + 127) / 128); p.tiles_n = (int)((n + 127) / 128);
     p.tri = 0; p.split_first = 0; p.nsu = 0; p.region_tiles = 0; p.dynamic = 0;
+    p.nbatch = 0; p.bat_nlo = 1;
+    p.ext_a_mn = p.ext_a_k = p.ext_b_mn = p.ext_b_k = p.ext_c_m = p.ext_c_n = 0;
     p.err = device_error_word();
     p.sched = sched_words(st);
     if (!p.err || !p.sched) return -1;
-    const int pair_tiles = left ? p.tiles_m : p.tiles_n, pairs = left ? p.tiles_n : p.tiles_m;
-    p.pair = 0; p.pair_half = 0;
-    if (pair_tiles == 2) {
-        if (pairs > kSchedFlags) return -1;
-        p.pair = left ? 1 : 2;
-        // the tile that only meets its own diagonal block: left, X_i = sum_j op(T)_ij X_j -> row block 0 for a lower
-        // op(T); right, X_j = sum_i X_i op(T)_ij -> column block 1 for a lower op(T)
-        p.pair_half = left ? (lower_op ? 0 : 1) : (lower_op ? 1 : 0);
-    }
-    // one tile along the triangular dimension: the tile's loads are all done before its epilogue stores, and no
-    // other tile touches its rows (columns), so plain in-place is safe as long as the tiles are the large ones
+    if ((int64_t)p.tiles_m * p.tiles_n > kSchedFlags) return -1;
+    // left: X_i = sum_j op(T)_ij X_j, a lower op(T) meets blocks j <= i; right: X_j = sum_i X_i op(T)_ij, an
+    // upper op(T) meets blocks i <= j
+    p.leaf = left ? (lower_op ? 1 : 2) : (lower_op ? 4 : 3);
     const int ta = left ? transT : 0, tb = left ? 0 : transT;
     int r;
     if (!ta && !tb)      r = launch_tma<128, 128, 2, 4, MN_MAJOR, K_MAJOR, 3, 1>(st, p, p.A, p.B, false);
@@ -893,6 +1135,46 @@ int dgemm_leaf_inplace(cudaStream_t st, int left, int lower_op, int transT, int6
     else if (ta && !tb)  r = launch_tma<128, 128, 2, 4, K_MAJOR, K_MAJOR, 3, 1>(st, p, p.A, p.B, false);
     else                 r = launch_tma<128, 128, 2, 4, K_MAJOR, MN_MAJOR, 3, 1>(st, p, p.A, p.B, false);
     return r;
+}
+
+// nbatch products C_b <- alpha * A_b * B_b (no transposes, beta = 0) of one shape m x n x k in one launch.
+// A_b, B_b, C_b are blocks of three stored matrices; block b = hi * nlo + lo starts lo * s[0] + hi * s[1]
+// rows / columns further on, s being the pair given for that coordinate.  m and n are multiples of 128,
+// k of 16; the blocks of different products do not overlap; a_rows .. c_cols are the extents of the stored
+// matrices.  Returns -1 when TMA cannot address the operands.
+int dgemm_batched(cudaStream_t st, int64_t m, int64_t n, int64_t k, double alpha, const double *A, int64_t lda,
+                  int64_t a_rows, int64_t a_cols, const double *B, int64_t ldb, int64_t b_rows, int64_t b_cols,
+                  double *C, int64_t ldc, int64_t c_rows, int64_t c_cols, const BatchShape &bs)
+{
+    if (m <= 0 || n <= 0 || k <= 0 || bs.count <= 0) return ULMB200_OK;
+    if (m % 128 || n % 128 || k % kBK) return -1;
+    const bool tma_ok = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
+                        (lda % 2 == 0) && (ldb % 2 == 0) && a_rows < (1ll << 31) - 256 && a_cols < (1ll << 31) - 256 &&
+                        b_rows < (1ll << 31) - 256 && b_cols < (1ll << 31) - 256 && lda < (1ll << 36) && ldb < (1ll << 36);
+    if (!tma_ok) return -1;
+    GemmParams p = {};
+    p.m = m; p.n = n; p.k = k; p.alpha = alpha; p.beta = 0.0;
+    p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
+    p.tiles_m = (int)(m / 128); p.tiles_n = (int)(n / 128);
+    p.tri = 0; p.split_first = 0; p.nsu = 0; p.region_tiles = 0; p.dynamic = 0; p.leaf = 0;
+    p.nbatch = bs.count > 1 ? bs.count : 0; p.bat_nlo = bs.nlo > 0 ? bs.nlo : 1;
+    for (int i = 0; i < 2; ++i) {
+        p.bat_am[i] = bs.a_row[i]; p.bat_ak[i] = bs.a_col[i];
+        p.bat_bk[i] = bs.b_row[i]; p.bat_bn[i] = bs.b_col[i];
+        p.bat_c[i] = bs.c_row[i] + bs.c_col[i] * ldc;
+        p.bat_cr[i] = (int)bs.c_row[i]; p.bat_cc[i] = (int)bs.c_col[i];
+    }
+    p.ext_a_mn = a_rows; p.ext_a_k = a_cols; p.ext_b_mn = b_cols; p.ext_b_k = b_rows;
+    p.ext_c_m = c_rows; p.ext_c_n = c_cols;
+    if (c_rows >= (1ll << 31) - 256 || c_cols >= (1ll << 31) - 256) return -1;
+    p.err = device_error_word();
+    p.sched = sched_words(st);
+    if (!p.err) return -1;
+    if (bs.count == 1) {
+        // one product: the shifts of block (0, 0) are zero, a plain launch with the stored extents
+        p.nbatch = 0;
+    }
+    return launch_tma<128, 128, 2, 4, MN_MAJOR, K_MAJOR, 3, 1>(st, p, p.A, p.B, false);
 }
 
 int sm_reserve_swap(int sms)

@@ -52,7 +52,7 @@ constexpr int kTrtriThreads = 256;
 constexpr int kTrtriLeaf = 16;
 
 __global__ void __launch_bounds__(kTrtriThreads)
-trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *inv, int paired)
+trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *inv, int ldo)
 {
     extern __shared__ double trtri_smem[];
     double *M = trtri_smem;                   // M[p*kNB + i] = L(i, p)
@@ -65,15 +65,27 @@ trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int un
 
     // the lower view: strictly upper part zero, identity beyond len; the stored block is walked
     // column by column, and its unreferenced triangle is never read
-    for (int e = t; e < kNB * kNB; e += kTrtriThreads) {
-        const int a = e % kNB, b = e / kNB;               // stored element (a, b) of the block
-        const int i = lower ? a : b, p = lower ? b : a;   // its place in the lower view
-        double v = 0.0;
-        if (i >= p) {
-            if (i < len) v = (unit && i == p) ? 1.0 : __ldg(Ab + a + (int64_t)b * lda);
-            else if (i == p) v = 1.0;
+    // eight loads in flight per thread: the walk is a chain of global-memory latencies otherwise
+    for (int e0 = t; e0 < kNB * kNB; e0 += 8 * kTrtriThreads) {
+        double v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int e = e0 + u * kTrtriThreads;
+            const int a = e % kNB, b = e / kNB;               // stored element (a, b) of the block
+            const int i = lower ? a : b, p = lower ? b : a;   // its place in the lower view
+            v[u] = 0.0;
+            if (i >= p) {
+                if (i < len) v[u] = (unit && i == p) ? 1.0 : __ldg(Ab + a + (int64_t)b * lda);
+                else if (i == p) v[u] = 1.0;
+            }
         }
-        M[p * kNB + i] = v;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int e = e0 + u * kTrtriThreads;
+            const int a = e % kNB, b = e / kNB;
+            const int i = lower ? a : b, p = lower ? b : a;
+            M[p * kNB + i] = v[u];
+        }
     }
     __syncthreads();
 
@@ -137,11 +149,12 @@ trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int un
         __syncthreads();
     }
 
-    // the full kNB x kNB block goes out (zeros outside len x len and outside the triangle)
-    // paired: block blk is a diagonal block of the 256 x 256 inverse of blocks (blk & ~1, blk | 1)
-    const int old_ = paired ? 2 * kNB : kNB;
-    double *out = paired ? inv + (int64_t)(blk >> 1) * (2 * kNB) * (2 * kNB) + (blk & 1) * (kNB * old_ + kNB)
-                         : inv + (int64_t)blk * kNB * kNB;
+    // the full kNB x kNB block goes out (zeros outside len x len and outside the triangle).  The inverses
+    // of ldo x ldo diagonal blocks lie one after the other, each with leading dimension ldo: block blk
+    // is the diagonal block at row and column (blk * kNB) % ldo of number blk * kNB / ldo.
+    const int old_ = ldo;
+    const int64_t at = (int64_t)blk * kNB;
+    double *out = inv + (at / ldo) * ldo * ldo + (at % ldo) * (ldo + 1);
     for (int e = t; e < kNB * kNB; e += kTrtriThreads) {
         const int i = e % kNB, j = e / kNB;           // lower view (i, j)
         const double v = (i < len && j < len && j <= i) ? M[j * kNB + i] : 0.0;
@@ -159,15 +172,16 @@ trtri_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int un
 constexpr int kPairStrip = 16;
 
 __global__ void __launch_bounds__(256) trtri_pair_kernel(const double *A, int64_t lda, int64_t dim, int lower,
-                                                         double *inv)
+                                                         double *inv, int ldo)
 {
     __shared__ double Ws[kPairStrip][kNB + 1];
     const int pair = blockIdx.x / (kNB / kPairStrip), strip = blockIdx.x % (kNB / kPairStrip);
     const int t = threadIdx.x, i = t & (kNB - 1), half = t >> 7;         // row i, 8 of the 16 columns
-    constexpr int LD = 2 * kNB;
-    double *blk = inv + (int64_t)pair * LD * LD;
+    const int LD = ldo;                                                  // the pair is a diagonal block of an ldo x ldo one
+    const int64_t at = (int64_t)pair * 2 * kNB;
+    double *blk = inv + (at / ldo) * ldo * ldo + (at % ldo) * (ldo + 1);
     const double *Ai = blk, *Bi = blk + kNB * LD + kNB;                  // A' and B'
-    const int64_t r0 = (int64_t)pair * LD;                               // first row/column of the pair in the matrix
+    const int64_t r0 = at;                                               // first row/column of the pair in the matrix
     // C as stored: lower -> rows r0+128.., columns r0..; upper -> rows r0.., columns r0+128..
     const int64_t cr = lower ? r0 + kNB : r0, cc = lower ? r0 : r0 + kNB;
     const double *inner = lower ? Ai : Bi;                               // right factor of the inner product
@@ -177,10 +191,15 @@ __global__ void __launch_bounds__(256) trtri_pair_kernel(const double *A, int64_
 #pragma unroll
     for (int u = 0; u < 8; ++u) acc[u] = 0.0;
     const bool row_ok = cr + i < dim;
-    for (int p = 0; p < kNB; ++p) {
-        const double c = (row_ok && cc + p < dim) ? __ldg(A + cr + i + (cc + p) * lda) : 0.0;
+    for (int p0 = 0; p0 < kNB; p0 += 16) {
+        // sixteen elements of the row of C at a time, so that their latencies overlap
+        double c[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) acc[u] += c * inner[(j0 + u) * LD + p];
+        for (int q = 0; q < 16; ++q) c[q] = (row_ok && cc + p0 + q < dim) ? __ldg(A + cr + i + (cc + p0 + q) * lda) : 0.0;
+#pragma unroll
+        for (int q = 0; q < 16; ++q)
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] += c[q] * inner[(j0 + u) * LD + p0 + q];
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) Ws[half * 8 + u][i] = acc[u];
@@ -259,6 +278,7 @@ static void solve_left(TrsmCtx &c, int64_t r0, int64_t len)
         // in place where the operands allow it, else through the work tile and a copy back
         const int r = dgemm_leaf_inplace(c.st, 1, c.eff_lower, c.trans, len, c.n, 1.0, iv, c.leaf, c.B + r0, c.ldb, c.err);
         if (r >= 0) { c.status = r; return; }
+        if (c.leaf > 2 * kNB) { c.status = ULMB200_CUDA_ERROR; return; }     // only the leaf kernel skips the unwritten blocks
         gemm_chk(c, c.trans, 0, len, c.n, len, 1.0, iv, c.leaf, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
         return;
@@ -288,6 +308,7 @@ static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
         const double *iv = c.inv + (c0 / c.leaf) * c.leaf * c.leaf;
         const int r = dgemm_leaf_inplace(c.st, 0, c.eff_lower, c.trans, len, c.m, 1.0, iv, c.leaf, c.B + c0 * c.ldb, c.ldb, c.err);
         if (r >= 0) { c.status = r; return; }
+        if (c.leaf > 2 * kNB) { c.status = ULMB200_CUDA_ERROR; return; }
         gemm_chk(c, 0, c.trans, c.m, len, len, 1.0, c.B + c0 * c.ldb, c.ldb, iv, c.leaf, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
         return;
@@ -309,13 +330,51 @@ static void solve_right(TrsmCtx &c, int64_t c0, int64_t len)
     }
 }
 
+// Doubles the order of the inverted diagonal blocks from h to 2h, for every pair whose second half
+// exists: lower-stored [[A,0],[C,B]]^-1 = [[A',0],[-B' C A',B']], upper-stored [[A,C],[0,B]]^-1 =
+// [[A',-A' C B'],[0,B']].  All pairs go through two batched products (inner factor into the work
+// matrix pairs_w, h x h per pair side by side, then the outer one into its place).  The inverses of
+// the L x L blocks lie one after the other with leading dimension L.
+static int trtri_double(cudaStream_t st, const double *A, int64_t lda, int64_t dim, int lower, double *inv, int L,
+                        int h, double *pairs_w)
+{
+    if (dim <= h) return ULMB200_OK;
+    const int64_t nQ = (dim + L - 1) / L;
+    BatchShape bs;
+    bs.count = (int)((dim - h + 2 * h - 1) / (2 * h));
+    bs.nlo = L / (2 * h);
+    const int64_t wide = (int64_t)L * nQ;               // the inverses as one L x wide matrix
+    const int two_h = 2 * h;
+    auto set = [](int (&x)[2], int lo, int hi) { x[0] = lo; x[1] = hi; };
+    // 1. pairs_w_q = C_q * A'_q (lower) or C_q * B'_q (upper)
+    set(bs.a_row, two_h, L); set(bs.a_col, two_h, L);     // C_q walks down the diagonal of the matrix
+    set(bs.b_row, two_h, 0); set(bs.b_col, two_h, L);     // a diagonal block of inverse number hi
+    bs.c_row[0] = bs.c_row[1] = 0; bs.c_col[0] = h; bs.c_col[1] = (int64_t)h * bs.nlo;
+    const double *C0 = lower ? A + h : A + (int64_t)h * lda;
+    const int64_t c_rows = lower ? dim - h : dim, c_cols = lower ? dim : dim - h;
+    const double *in0 = lower ? inv : inv + h + (int64_t)h * L;
+    const int64_t in_rows = lower ? L : L - h, in_cols = lower ? wide : wide - h;
+    int r = dgemm_batched(st, h, h, h, 1.0, C0, lda, c_rows, c_cols, in0, L, in_rows, in_cols, pairs_w, h, h, (int64_t)h * bs.count, bs);
+    if (r != ULMB200_OK) return r;
+    // 2. X_q = -B'_q * pairs_w_q (lower) or -A'_q * pairs_w_q (upper)
+    set(bs.a_row, two_h, 0); set(bs.a_col, two_h, L);
+    set(bs.b_row, 0, 0); set(bs.b_col, h, h * bs.nlo);
+    bs.c_row[0] = two_h; bs.c_row[1] = 0; bs.c_col[0] = two_h; bs.c_col[1] = L;
+    const double *out0 = lower ? inv + h + (int64_t)h * L : inv;
+    const int64_t out_rows = lower ? L - h : L, out_cols = lower ? wide - h : wide;
+    double *X0 = lower ? inv + h : inv + (int64_t)h * L;
+    const int64_t x_rows = lower ? L - h : L, x_cols = lower ? wide : wide - h;
+    return dgemm_batched(st, h, h, h, -1.0, out0, L, out_rows, out_cols, pairs_w, h, h, (int64_t)h * bs.count, X0, L, x_rows, x_cols, bs);
+}
+
 // Shared by the allocating entry point and any caller that brings its own
 // scratch, with leaf = 128: inv holds ceil(dim/128) * 128 * 128 doubles, W 128*n (left) or m*128 (right);
 // with leaf = 256 (inverses completed pairwise, half as many and larger leaf products):
-// inv holds ceil(dim/256) * 256 * 256 doubles, W 256*n or m*256.
+// inv holds ceil(dim/256) * 256 * 256 doubles, W 256*n or m*256.  Larger leaves (512, 1024, ...: the
+// inverses doubled again by batched products) need pairs as well, ceil(dim/leaf) * leaf * leaf / 4 doubles.
 int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m,
                        int64_t n, double alpha, const double *A, int64_t lda, double *B,
-                       int64_t ldb, double *inv, double *W, int *err_word, int leaf)
+                       int64_t ldb, double *inv, double *W, int *err_word, int leaf, double *pairs)
 {
     const int left = (side == 0);
     const int64_t dim = left ? m : n;
@@ -333,21 +392,30 @@ int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int uni
         ULMB_CUDA(cudaFuncSetAttribute(trtri_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done[dev] = true;
     }
-    const int paired = leaf == 2 * kNB;
-    trtri_blocks_kernel<<<nblk, kTrtriThreads, smem, st>>>(A, lda, dim, lower, unit, inv, paired);
+    const int64_t nleaf = (dim + leaf - 1) / leaf;
+    if (leaf > 2 * kNB) {
+        // the blocks above (below) the diagonal that no kernel writes are read as zeros by the batched products
+        // of the next doubling step, and so is what a last block holds beyond the triangle
+        ULMB_CUDA(cudaMemsetAsync(inv, 0, sizeof(double) * (size_t)nleaf * leaf * leaf, st));
+    }
+    trtri_blocks_kernel<<<nblk, kTrtriThreads, smem, st>>>(A, lda, dim, lower, unit, inv, leaf);
     count_launch();
-    if (paired) {
+    if (leaf >= 2 * kNB) {
         // an odd last block has no partner: its pair is completed against an all-zero second block,
         // which the first kernel never wrote, so clear that corner first
         const int npair = (nblk + 1) / 2;
-        if (nblk & 1) {
+        if ((nblk & 1) && leaf == 2 * kNB) {
             double *last = inv + (int64_t)(npair - 1) * leaf * leaf;
             ULMB_CUDA(cudaMemset2DAsync(last + kNB * leaf + kNB, sizeof(double) * leaf, 0, sizeof(double) * kNB, kNB, st));
         }
-        trtri_pair_kernel<<<npair * (kNB / kPairStrip), 256, 0, st>>>(A, lda, dim, lower, inv);
+        trtri_pair_kernel<<<npair * (kNB / kPairStrip), 256, 0, st>>>(A, lda, dim, lower, inv, leaf);
         count_launch();
     }
     ULMB_CUDA(cudaGetLastError());
+    for (int h = 2 * kNB; h < leaf; h *= 2) {
+        const int r = trtri_double(st, A, lda, dim, lower, inv, leaf, h, pairs);
+        if (r != ULMB200_OK) return r < 0 ? ULMB200_BAD_ARGUMENT : r;
+    }
 
     TrsmCtx c;
     c.st = st; c.left = left; c.lower = lower; c.trans = transA;
@@ -362,6 +430,32 @@ int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int uni
     return c.status;
 }
 
+// Order of the inverted diagonal blocks.  Small triangles keep 128 or 256; large ones with many right-hand
+// sides take 1024, so that the products below the top of the recursion are few and large: a leaf of order
+// 1024 is one launch that multiplies only the blocks of its triangle, where 256-leaves solve the same rows in
+// seven launches too short to fill the machine.  The larger blocks need TMA-addressable operands for the
+// batched products that build them.
+static int trsm_leaf_order(cudaStream_t st, int64_t dim, int64_t other, const double *A, int64_t lda, const double *B,
+                           int64_t ldb)
+{
+    int leaf = dim > 2 * kNB ? 2 * kNB : kNB;
+    // what the batched products and the in-place leaf need; beyond 256 nothing else can apply the inverses,
+    // whose blocks above (below) the diagonal are never written
+    auto large_ok = [&](int L) {
+        const int64_t tiles = ((L < dim ? L : dim) + 127) / 128 * ((other + 127) / 128);
+        return ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 && lda % 2 == 0 &&
+               ldb % 2 == 0 && dim < (1ll << 31) - 4096 && other < (1ll << 31) - 4096 && lda < (1ll << 36) &&
+               ldb < (1ll << 36) && tiles <= kSchedFlags && sched_words(st) != nullptr;
+    };
+    if (dim >= 2048 && other >= 1024 && large_ok(1024)) leaf = 1024;
+    const int forced = settings().trsm_leaf;
+    if (forced == 128 || forced == 256 || ((forced == 512 || forced == 1024 || forced == 2048) && large_ok(forced))) {
+        leaf = forced;
+        while (leaf > kNB && leaf / 2 >= dim) leaf /= 2;     // no larger than the triangle needs
+    }
+    return leaf;
+}
+
 int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int64_t m, int64_t n,
                  double alpha, const double *A, int64_t lda, double *B, int64_t ldb)
 {
@@ -370,14 +464,21 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
     if (lda < (dim > 1 ? dim : 1) || ldb < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s = ensure_device()) return set_status(s);
-    // 256-leaves once the triangle spans several of them; small triangles keep the 128 ones
-    const int leaf = dim > 2 * kNB ? 2 * kNB : kNB;
+    const int leaf = trsm_leaf_order(st, dim, side == 0 ? n : m, A, lda, B, ldb);
     const int64_t nblk = (dim + leaf - 1) / leaf;
     double *inv = static_cast<double *>(device_scratch(3, (size_t)nblk * leaf * leaf * sizeof(double)));
-    const int64_t wel = (side == 0) ? (int64_t)leaf * n : m * (int64_t)leaf;
-    double *W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
-    if (!inv || !W) return set_status(ULMB200_CUDA_ERROR);
-    return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, A, lda, B, ldb, inv, W, nullptr, leaf));
+    double *W = nullptr, *pairs = nullptr;
+    if (leaf > 2 * kNB) {
+        // the large leaves are applied in place only: no work tile, but room for the batched products
+        pairs = static_cast<double *>(device_scratch(5, (size_t)nblk * leaf * leaf / 4 * sizeof(double)));
+        if (!pairs) return set_status(ULMB200_CUDA_ERROR);
+    } else {
+        const int64_t wel = (side == 0) ? (int64_t)leaf * n : m * (int64_t)leaf;
+        W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
+        if (!W) return set_status(ULMB200_CUDA_ERROR);
+    }
+    if (!inv) return set_status(ULMB200_CUDA_ERROR);
+    return set_status(dtrsm_with_scratch(st, side, lower, transA, unit, m, n, alpha, A, lda, B, ldb, inv, W, nullptr, leaf, pairs));
 }
 
 // ---------------------------------------------------------------------------

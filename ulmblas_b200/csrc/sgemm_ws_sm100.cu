@@ -107,6 +107,17 @@ __device__ __forceinline__ void sw_store_row(uint8_t *tile, int r, const float4 
     }
 }
 
+// A producer's wait for a free stage: the ring holds several microseconds of work, so the waiter
+// can sleep between polls and leave the issue slots to the consumers.  Bounded like every wait.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t *bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 4) __nanosleep(256);
+    }
+    return false;
+}
+
 __device__ __forceinline__ void mbar_expect_tx_only(uint64_t *bar, uint32_t bytes)
 {
     asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -120,6 +131,9 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     using namespace sw;
     constexpr bool A_TMA = !TA, B_TMA = TB;
     constexpr uint32_t TX_BYTES = (A_TMA ? A_BYTES : 0u) + (B_TMA ? B_BYTES : 0u);
+    // producer threads that have work: all of them when an operand is transposed on the way in, one
+    // (the TMA issuer) when both operands arrive by TMA -- the others leave at once instead of polling
+    constexpr int NPROD = (A_TMA && B_TMA) ? 1 : PRODUCERS;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -133,8 +147,8 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            // every producer thread arrives once per stage (the TMA-issuing one with the byte count)
-            mbar_init(&full[s], PRODUCERS);
+            // every working producer thread arrives once per stage
+            mbar_init(&full[s], NPROD);
             mbar_init(&empty[s], CONSUMERS / 32);
         }
         *abort_flag = 0;
@@ -152,12 +166,13 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // ------------------------------ producers ------------------------------
         asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
         const int t = threadIdx.x - CONSUMERS;
+        if (t >= NPROD) return;
         uint32_t it = 0;
         bool live = true;
         auto load_piece = [&](int unit, int64_t m0, int64_t n0, int kc0, int kc1) -> bool {
             for (int kc = kc0; kc < kc1; ++kc, ++it) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
+                if (*abort_flag || !mbar_wait_idle(&empty[s], ph ^ 1)) {
                     *abort_flag = 1;
                     atomicExch(p.err, 211);
                     return false;
@@ -209,7 +224,9 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
             if (!live) break;
-            if (p.dynamic) {
+            if (p.dynamic && NPROD == 1) {
+                unit = (int)gridDim.x + atomicAdd(p.sched, 1);
+            } else if (p.dynamic) {
                 // Thread 0 draws the next unit and publishes it; the others pick it up with a bounded
                 // wait (no block barrier: a thread that has given up must not strand the rest).  Thread 0
                 // is never more than STAGES units ahead of any other producer thread, so 8 slots do.
@@ -243,7 +260,7 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (live) {
             // one empty stage carries the end mark
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-            if (*abort_flag || !mbar_wait(&empty[s], ph ^ 1)) {
+            if (*abort_flag || !mbar_wait_idle(&empty[s], ph ^ 1)) {
                 *abort_flag = 1;
                 atomicExch(p.err, 211);
             } else {
