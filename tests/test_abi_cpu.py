@@ -205,6 +205,15 @@ def test_work_schedule_model(tmp_path):
     assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout
 
 
+def test_inplace_leaf_protocol_model(tmp_path):
+    """CPU model of the in-place triangular leaf: units in the kernel's order on few or many CTAs of uneven
+    speed; no block is overwritten before its readers are through, nothing waits in a cycle."""
+    exe = str(tmp_path / "leaf_model")
+    subprocess.run(["g++", "-O1", "-std=c++17", "-o", exe, os.path.join(ROOT, "tests", "cpu", "leaf_model.cpp")], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip().startswith("OK"), r.stdout
+
+
 def test_trace_and_environment_reload(ulm, monkeypatch, capfd):
     """ULMB200_TRACE=1 prints one line per call; the environment is read once and again on request."""
     A = np.ones((4, 4), order="F")

@@ -100,21 +100,46 @@ def test_tester_grid_small_shapes(ulm):
     assert count == 360
 
 
-@pytest.mark.parametrize("tile,path", [("64", ""), ("128", ""), ("64", "ldg"), ("128", "ldg")])
+@pytest.mark.parametrize("tile,path", [("64", ""), ("128", ""), ("12864", ""), ("64", "ldg"), ("128", "ldg")])
 def test_every_kernel_variant(ulm, tile, path, monkeypatch):
-    """Force each tile shape on each load path (TMA / plain loads) over all four transpositions,
-    on shapes with ragged edges in m, n and k."""
+    """Force each tile shape (64 x 64, 128 x 128, 128 x 64) on each load path (TMA / plain loads) over all
+    four transpositions, on shapes with ragged edges in m, n and k."""
     monkeypatch.setenv("ULMB200_DGEMM_TILE", tile)
     if path:
         monkeypatch.setenv("ULMB200_DGEMM_PATH", path)
     ulm.reload_env()
     seed = 5000
-    for (m, n, k) in [(300, 260, 100), (129, 65, 17), (64, 64, 16), (200, 1, 33)]:
+    for (m, n, k) in [(300, 260, 100), (129, 65, 17), (64, 64, 16), (200, 1, 33), (1100, 1300, 270)]:
         for ta, tb in itertools.product("NT", "NT"):
             seed += 3
             ra = (m if ta == "N" else k)
             rb = (k if tb == "N" else n)
             check_case(ulm, ta, tb, m, n, k, 1.25, -0.5, seed, lda=ra + (ra % 2), ldb=rb + (rb % 2), ldc=m + 4)
+
+
+@pytest.mark.parametrize("tile", ["128", "12864"])
+def test_device_c_without_tensor_map(ulm, torch_cuda, tile, monkeypatch):
+    """Device-resident operands whose C has an odd leading dimension, or starts 8 bytes off a 16-byte
+    boundary: TMA can feed A and B but cannot address C, so the consumers write the tiles themselves
+    instead of sending them out through shared memory.  Padding rows of C stay as they were."""
+    torch = torch_cuda
+    monkeypatch.setenv("ULMB200_DGEMM_TILE", tile)
+    ulm.reload_env()
+    m, n, k = 700, 900, 150
+    A, B = det_uniform(77, m, k), det_uniform(78, k, n)
+    dA, dB = torch.from_numpy(A.T.copy()).cuda(), torch.from_numpy(B.T.copy()).cuda()      # column-major on the device
+    for ldc, off in [(m + 1, 0), (m + 2, 1)]:
+        C0 = det_uniform(79 + ldc, ldc, n + 1)
+        want = reference_dgemm("N", "N", m, n, k, -0.7, A, B, 1.3, np.asfortranarray(C0[off:off + m, :n]), m)
+        dC = torch.from_numpy(C0.T.copy()).cuda()
+        ulm.dev_dgemm(0, 0, m, n, k, -0.7, dA.data_ptr(), m, dB.data_ptr(), k, 1.3, dC.data_ptr() + 8 * off, ldc)
+        torch.cuda.synchronize()
+        assert ulm.check_device_error() == 0
+        got = dC.cpu().numpy().T
+        assert np.array_equal(got[off + m:, :], C0[off + m:, :]) and np.array_equal(got[:off, :], C0[:off, :])
+        assert np.array_equal(got[:, n:], C0[:, n:])
+        ratio = bound_ratio(got[off:off + m, :n], want[:m, :n], gemm_gauge(-0.7, A, B, 1.3, C0[off:off + m, :n]), k, EPS64)
+        assert ratio <= 1.0, (tile, ldc, off, ratio)
 
 
 def test_golden_fixture_cases_on_gpu(ulm):

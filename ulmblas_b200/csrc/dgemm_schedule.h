@@ -68,8 +68,10 @@ struct SharePlan {
 
 // Estimated cost, in pipeline stages, of sharing `rem` tiles of kt stages among nsu stream units.
 // A unit multiplies its share of the stages and writes one partial epilogue per piece it holds;
-// the pieces of a tile fold into C one after the other and the last ones all finish computing at
-// about the same time, so every piece of a tile beyond the first adds one more epilogue at the end.
+// the pieces of a tile fold into C one after the other, so every piece of a tile beyond the first
+// adds one more epilogue at the end.  With unit boundaries on tile boundaries the pieces of a tile
+// all finish computing at the same moment and the whole chain is exposed: measured, such plans run
+// about 15 % over this count (1024^3 in two halves per tile, 200 x 3000 x 1000 in thirds).
 inline long long shared_cost(int rem, int kt, int nsu)
 {
     const long long S = (long long)rem * kt;
@@ -77,7 +79,8 @@ inline long long shared_cost(int rem, int kt, int nsu)
     const bool aligned = nsu % rem == 0;                       // unit boundaries fall on tile boundaries
     const long long pieces = aligned ? nsu / rem : (kt + share - 1) / share + 1;
     const long long own = aligned ? 1 : 2;                     // epilogues in a unit's own time line
-    return share + (own + (pieces - 1)) * kEpilogueStages;
+    const long long cost = share + (own + (pieces - 1)) * kEpilogueStages;
+    return aligned ? (cost * 115 + 99) / 100 : cost;
 }
 
 inline SharePlan plan_shared_tiles(long long nreal, int kt, int slots, bool force)
@@ -100,6 +103,45 @@ inline SharePlan plan_shared_tiles(long long nreal, int kt, int slots, bool forc
     if (!pays && !force) return none;
     SharePlan p = {rem, best};
     return p;
+}
+
+// In-place product with a triangular operand (leaf mode 1..4 of the GEMM kernel): unit -> tile
+// coordinates, the range of pipeline stages it multiplies, and its place.  The triangular operand
+// spans T tiles of 128; the other dimension is cut into strips of one tile.  The tile at place d of a
+// strip multiplies blocks 0..d of k (low: modes 1 and 3) or d..T-1 (high: modes 2 and 4, taken from the
+// last block down), and units go out longest first: all strips of the longest place, then the next.
+constexpr int kLeafBlockStages = 8;       // pipeline stages per block of 128 k
+struct LeafUnit {
+    int tm, tn, kc0, kc1, d, strip, T, rev, expect;
+};
+ULMB_SCHED_HD LeafUnit leaf_decode(int leaf, int tiles_m, int tiles_n, int unit, int kt)
+{
+    constexpr int HB = kLeafBlockStages;
+    LeafUnit u;
+    const bool left = leaf <= 2;
+    const bool low = leaf == 1 || leaf == 3;
+    u.T = left ? tiles_m : tiles_n;
+    const int S = left ? tiles_n : tiles_m;
+    const int r = unit / S;
+    u.strip = unit - r * S;
+    u.d = low ? u.T - 1 - r : r;
+    u.tm = left ? u.d : u.strip;
+    u.tn = left ? u.strip : u.d;
+    if (low) { u.kc0 = 0; u.kc1 = (u.d + 1) * HB < kt ? (u.d + 1) * HB : kt; }
+    else     { u.kc0 = u.d * HB < kt ? u.d * HB : kt; u.kc1 = kt; }
+    u.rev = low ? 0 : 1;
+    u.expect = low ? u.T - 1 - u.d : u.d;            // longer tiles of the strip: they all read block d
+    return u;
+}
+// The block of k that stage number i (0 = first taken) of a unit belongs to, and whether it is the last
+// stage of that block the unit takes.
+ULMB_SCHED_HD int leaf_block_of(const LeafUnit &u, int i, bool &last_of_block)
+{
+    constexpr int HB = kLeafBlockStages;
+    const int kc = u.kc0 + i;
+    const int kk = u.rev ? u.kc0 + u.kc1 - 1 - kc : kc;
+    last_of_block = u.rev ? (kk % HB == 0 || kc + 1 == u.kc1) : (kk % HB == HB - 1 || kc + 1 == u.kc1);
+    return kk / HB;
 }
 
 }  // namespace ulmb200

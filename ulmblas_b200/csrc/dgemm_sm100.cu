@@ -79,30 +79,6 @@ struct StashInfo {
     int wait_idx, expect;    // leaf mode: the counter that must reach expect before C may be written, -1 = none
 };
 
-// leaf mode: unit -> tile coordinates, the range of pipeline stages it multiplies and its place
-struct LeafUnit {
-    int tm, tn, kc0, kc1, d, strip, T, rev, expect;
-};
-__device__ __forceinline__ LeafUnit leaf_decode(const GemmParams &p, int unit, int kt)
-{
-    constexpr int HB = 128 / kBK;                    // stages per block of 128 k
-    LeafUnit u;
-    const bool left = p.leaf <= 2;
-    const bool low = p.leaf == 1 || p.leaf == 3;
-    u.T = left ? p.tiles_m : p.tiles_n;
-    const int S = left ? p.tiles_n : p.tiles_m;
-    const int r = unit / S;
-    u.strip = unit - r * S;
-    u.d = low ? u.T - 1 - r : r;
-    u.tm = left ? u.d : u.strip;
-    u.tn = left ? u.strip : u.d;
-    if (low) { u.kc0 = 0; u.kc1 = (u.d + 1) * HB < kt ? (u.d + 1) * HB : kt; }
-    else     { u.kc0 = u.d * HB < kt ? u.d * HB : kt; u.kc1 = kt; }
-    u.rev = low ? 0 : 1;
-    u.expect = low ? u.T - 1 - u.d : u.d;            // longer tiles of the strip: they all read block d
-    return u;
-}
-
 // batch mode: coordinate shifts of product b
 struct BatchShift {
     int am, ak, bn, bk, cr, cc;
@@ -434,7 +410,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int unit = blockIdx.x;
             while (live && unit < num_units) {
                 if (SHARE && p.leaf) {
-                    const LeafUnit u = leaf_decode(p, unit, kt);
+                    const LeafUnit u = leaf_decode(p.leaf, p.tiles_m, p.tiles_n, unit, kt);
                     live = load_piece(unit, (int64_t)u.tm * BM, (int64_t)u.tn * BN, u.kc0, u.kc1, u.rev != 0);
                 } else if (SHARE && p.nbatch > 1) {
                     const int per = p.tiles_m * p.tiles_n, b = unit / per;
@@ -656,8 +632,8 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             return;
         }
         if (SHARE && p.leaf) {
-            constexpr int HB = 128 / kBK;
-            const LeafUnit u = leaf_decode(p, unit, kt);
+            static_assert(kLeafBlockStages * kBK == 128, "a block of k is one tile of the triangular operand");
+            const LeafUnit u = leaf_decode(p.leaf, p.tiles_m, p.tiles_n, unit, kt);
             int *cnt = p.sched + 2 + u.strip * u.T;
             // the output thread stores once every longer tile of the strip has counted block d
             announce_tile(unit, u.tm * BM, u.tn * BN, false, u.expect > 0 ? u.strip * u.T + u.d : -1, u.expect);
@@ -677,9 +653,8 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 // the last stage of a block of k has landed: the tile that will overwrite those rows
                 // (columns) of the strip has one reader less to wait for
                 if (threadIdx.x == 0) {
-                    const int kk = u.rev ? u.kc0 + u.kc1 - 1 - kc : kc;
-                    const int blk = kk / HB;
-                    const bool last_of_block = u.rev ? (kk % HB == 0 || kc + 1 == u.kc1) : (kk % HB == HB - 1 || kc + 1 == u.kc1);
+                    bool last_of_block;
+                    const int blk = leaf_block_of(u, kc - u.kc0, last_of_block);
                     if (last_of_block && blk != u.d) atomicAdd(cnt + blk, 1);
                 }
                 const uint32_t sA = smem_base + s * STAGE_BYTES;
@@ -1009,31 +984,41 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
 {
     const Settings &cfg = settings();
     // Tile shape by estimated time.  Large tiles (128 x 128, one CTA per SM) run the tensor pipe best and
-    // can share the last tiles' stages among all CTAs; small tiles (64 x 64, two CTAs per SM) waste less
-    // on padding and fill the machine with fewer rows and columns.  Per-SM times in microseconds,
-    // measured on this part: one 16-k stage of a large tile 2.09, of a small tile 1.15 when two CTAs
+    // can share the last tiles' stages among all CTAs; half tiles (128 x 64, one CTA per SM) put a product of
+    // few large tiles on twice as many SMs; small tiles (64 x 64, two CTAs per SM) waste least on padding
+    // and fill the machine with the fewest rows and columns.  Per-SM times in microseconds, measured on
+    // this part: one 16-k stage of a large tile 2.09, of a half tile 1.2, of a small tile 1.15 when two CTAs
     // share the SM (their operand traffic from L2 is twice the large tiles') and 0.70 when one has it
-    // alone; an epilogue 1 (large tiles leave through shared memory beside the next tile's main loop) / 2.
+    // alone; an epilogue 1 (large and half tiles leave through shared memory beside the next tile's
+    // main loop) / 2.
     const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+    const int64_t thalf = ((p.m + 127) / 128) * ((p.n + 63) / 64);
     const int64_t t64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
     const int kt = (int)((p.k + kBK - 1) / kBK);
     const int sms = sm_count();
-    constexpr double kStage128 = 2.09, kStage64Pair = 1.15, kStage64Alone = 0.70, kEpi128 = 1.0, kEpi64 = 2.0;
-    double time128 = (double)((t128 + sms - 1) / sms) * (kt * kStage128 + kEpi128);
-    if (tma_ok && may_share && p.sched && cfg.dgemm_split != 0 && p.tri == 0) {
-        const SharePlan sp = plan_shared_tiles(t128, kt, sms, false);
-        if (sp.nsu > 0)
-            time128 = (double)(t128 / sms) * (kt * kStage128 + kEpi128) +
-                      (double)shared_cost(sp.region_tiles, kt, sp.nsu) * kStage128;
-    }
+    constexpr double kStage128 = 2.09, kStageHalf = 1.2, kStage64Pair = 1.15, kStage64Alone = 0.70, kEpi128 = 1.0,
+                     kEpi64 = 2.0;
+    const bool sharing = tma_ok && may_share && p.sched && cfg.dgemm_split != 0 && p.tri == 0;
+    // one CTA per SM: whole waves, the last one shared among all CTAs where that is cheaper
+    auto one_per_sm = [&](int64_t tiles, double stage) {
+        double t = (double)((tiles + sms - 1) / sms) * (kt * stage + kEpi128);
+        if (sharing) {
+            const SharePlan sp = plan_shared_tiles(tiles, kt, sms, false);
+            if (sp.nsu > 0)
+                t = (double)(tiles / sms) * (kt * stage + kEpi128) + (double)shared_cost(sp.region_tiles, kt, sp.nsu) * stage;
+        }
+        return t;
+    };
+    const double time128 = one_per_sm(t128, kStage128);
+    const double time_half = one_per_sm(thalf, kStageHalf);
     const int64_t waves64 = (t64 + 2 * sms - 1) / (2 * sms);
     const double stage64 = t64 <= sms ? kStage64Alone : kStage64Pair;
     const double time64 = (double)waves64 * (kt * stage64 + kEpi64);
-    bool big = time128 <= time64;
-    if (cfg.dgemm_tile == 128) big = true;
-    if (cfg.dgemm_tile == 64) big = false;
-    if (cfg.dgemm_ldg) tma_ok = false;
-    if (big) {
+    int shape = time128 <= time64 ? 128 : 64;
+    if (tma_ok && p.tri == 0 && time_half < (shape == 128 ? time128 : time64)) shape = 12864;
+    if (cfg.dgemm_tile == 128 || cfg.dgemm_tile == 64 || (cfg.dgemm_tile == 12864 && tma_ok)) shape = cfg.dgemm_tile;
+    if (cfg.dgemm_ldg) { tma_ok = false; if (shape == 12864) shape = 128; }
+    if (shape == 128) {
         p.tiles_m = (int)((p.m + 127) / 128);
         p.tiles_n = (int)((p.n + 127) / 128);
         if (tma_ok) {
@@ -1044,6 +1029,12 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
             if (r >= 0) return r;
         }
         return launch_ldg<128, 128, 2, 4, MAJOR_A, MAJOR_B>(st, p);
+    }
+    if (shape == 12864) {
+        p.tiles_m = (int)((p.m + 127) / 128);
+        p.tiles_n = (int)((p.n + 63) / 64);
+        int r = launch_tma<128, 64, 2, 4, MAJOR_A, MAJOR_B, 4, 1>(st, p, p.A, p.B, may_share);
+        if (r >= 0) return r;
     }
     p.tiles_m = (int)((p.m + 63) / 64);
     p.tiles_n = (int)((p.n + 63) / 64);

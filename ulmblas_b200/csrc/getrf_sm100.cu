@@ -895,6 +895,13 @@ int dlaswp_pairs_device(cudaStream_t st, double *A, int64_t lda, int64_t ncols, 
     return check_cuda(cudaGetLastError(), "laswp_pairs_kernel", __FILE__, __LINE__);
 }
 
+// Occupies its stream for about ns nanoseconds (nothing is waited for: a fixed number of short sleeps).
+constexpr unsigned kHeadStartNs = 12000;
+__global__ void lu_head_start_kernel(unsigned ns)
+{
+    for (unsigned waited = 0; waited < ns; waited += 500) __nanosleep(500);
+}
+
 int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda, int *d_piv, int *d_info)
 {
     if (m < 0 || n < 0 || lda < (m > 1 ? m : 1)) return set_status(ULMB200_BAD_ARGUMENT);
@@ -1052,7 +1059,10 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
     static cudaEvent_t la_ev[kMaxDevices][2] = {};
     bool la = use_la != 0 && mn > kLuNB;
     if (la && !la_stream[dev]) {
-        if (cudaStreamCreateWithFlags(&la_stream[dev], cudaStreamNonBlocking) != cudaSuccess ||
+        // the panel is the critical path: its blocks go ahead of the trailing update's whenever both wait for SMs
+        int prio_lo = 0, prio_hi = 0;
+        cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+        if (cudaStreamCreateWithPriority(&la_stream[dev], cudaStreamNonBlocking, prio_hi) != cudaSuccess ||
             cudaEventCreateWithFlags(&la_ev[dev][0], cudaEventDisableTiming) != cudaSuccess ||
             cudaEventCreateWithFlags(&la_ev[dev][1], cudaEventDisableTiming) != cudaSuccess) {
             cudaGetLastError();
@@ -1110,6 +1120,15 @@ int dgetrf_device(cudaStream_t st, int64_t m, int64_t n, double *A, int64_t lda,
                         if (int sp = factor_panel(st, jn, jb2)) return set_status(sp);
                     }
                     if (ncols > jb2) {
+                        // Both the panel and the update become ready when the event above fires.  The update must
+                        // not take its SMs first: its 132 persistent CTAs would leave the 16 free SMs scattered
+                        // over all GPCs and the panel's cluster, which needs 16 SMs of one GPC, would wait for the
+                        // whole update.  A few microseconds' head start lets the cluster settle on its GPC; the
+                        // update then fills the other SMs and both hold their places until they are done.
+                        if (la) {
+                            lu_head_start_kernel<<<1, 32, 0, st>>>(kHeadStartNs);
+                            count_launch();
+                        }
                         const int old = la ? sm_reserve_swap(kClu) : 0;
                         s = dgemm_device(st, 0, 0, 0, mrows, ncols - jb2, jb, -1.0, L21, lda, U12 + (int64_t)jb2 * lda, lda,
                                          1.0, A22 + (int64_t)jb2 * lda, lda);
