@@ -142,6 +142,39 @@ def test_device_c_without_tensor_map(ulm, torch_cuda, tile, monkeypatch):
         assert ratio <= 1.0, (tile, ldc, off, ratio)
 
 
+@pytest.mark.parametrize("tile", ["", "128", "12864"])
+def test_device_padding_below_an_odd_number_of_rows(ulm, torch_cuda, tile, monkeypatch):
+    """Device-resident C with an odd number of rows and padding rows below them, operands TMA can address:
+    whole tiles leave through shared memory and a TMA store, which clips rows in units of 16 bytes, so the
+    last row needs its own care.  Padding rows (rogue values, also in A and B) stay bit for bit."""
+    torch = torch_cuda
+    if tile:
+        monkeypatch.setenv("ULMB200_DGEMM_TILE", tile)
+    ulm.reload_env()
+    seed = 300
+    for (m, n, k, ta, tb, beta) in [(1025, 700, 130, "N", "N", 1.3), (1025, 700, 130, "T", "T", 0.0), (3001, 2047, 65, "N", "T", 1.3),
+                                    (257, 129, 513, "T", "N", 0.0), (1, 300, 40, "N", "N", 0.5)]:
+        seed += 5
+        ra, ca = (m, k) if ta == "N" else (k, m)
+        rb, cb = (k, n) if tb == "N" else (n, k)
+        lda, ldb, ldc = ra + 2 + (ra % 2), rb + 4 + (rb % 2), m + 7
+        A, B, C0 = det_uniform(seed, ra, ca), det_uniform(seed + 1, rb, cb), det_uniform(seed + 2, m, n)
+
+        def dev(h, ld):
+            t = torch.full((h.shape[1], ld), ROGUE, dtype=torch.float64, device="cuda")
+            t[:, :h.shape[0]] = torch.from_numpy(np.ascontiguousarray(h.T)).cuda()
+            return t
+        dA, dB, dC = dev(A, lda), dev(B, ldb), dev(C0, ldc)
+        ulm.dev_dgemm(ta == "T", tb == "T", m, n, k, -0.7, dA.data_ptr(), lda, dB.data_ptr(), ldb, beta, dC.data_ptr(), ldc)
+        torch.cuda.synchronize()
+        assert ulm.check_device_error() == 0
+        got = dC.cpu().numpy().T
+        assert (got[m:, :] == ROGUE).all(), (tile, m, n, k, ta, tb, "padding rows of C were written")
+        want = reference_dgemm(ta, tb, m, n, k, -0.7, A, B, beta, C0, m)
+        ratio = bound_ratio(got[:m, :], want, gemm_gauge(-0.7, op(A, ta), op(B, tb), beta, C0), k, EPS64)
+        assert ratio <= 1.0, (tile, m, n, k, ta, tb, beta, ratio)
+
+
 def test_golden_fixture_cases_on_gpu(ulm):
     """The committed outputs of the compiled reference, reproduced on the GPU within the bound."""
     for name, c in load_golden().items():

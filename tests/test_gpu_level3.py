@@ -294,6 +294,39 @@ def test_dtrsm_chosen_block_order_many_strips(ulm):
     trsm_check(ulm, "L", "U", "N", "N", 2100, 2700, 1.0, 21906)
 
 
+def test_dtrsm_device_resident_odd_orders_keep_padding(ulm, torch_cuda):
+    """Device-resident B with an odd number of rows and rogue padding rows below them (leading dimensions
+    even, so TMA addresses everything): the in-place leaves store whole tiles by TMA, whose row clipping
+    works in units of 16 bytes.  Padding stays bit for bit, the solution satisfies the tester's bound."""
+    torch = torch_cuda
+    seed = 22000
+    for (side, uplo, tr, m, n) in [("L", "L", "N", 2201, 1301), ("R", "U", "T", 1301, 2201), ("L", "U", "T", 301, 77),
+                                   ("R", "L", "N", 2049, 2048)]:
+        seed += 2
+        na = m if side == "L" else n
+        A = tri_matrix(seed, na, uplo)
+        B = det_uniform(seed + 1, m, n)
+        lda, ldb = na + 2 + (na % 2), m + 4 + (m % 2)
+
+        def dev(h, ld):
+            t = torch.full((h.shape[1], ld), ROGUE, dtype=torch.float64, device="cuda")
+            t[:, :h.shape[0]] = torch.from_numpy(np.ascontiguousarray(h.T)).cuda()
+            return t
+        dA, dB = dev(A, lda), dev(B, ldb)
+        ulm.dev_dtrsm(0 if side == "L" else 1, uplo == "L", tr == "T", 0, m, n, 1.0, dA.data_ptr(), lda, dB.data_ptr(), ldb)
+        torch.cuda.synchronize()
+        assert ulm.check_device_error() == 0
+        got = dB.cpu().numpy().T
+        assert (got[m:, :] == ROGUE).all(), (side, uplo, tr, m, n, "padding rows of B were written")
+        X = got[:m, :]
+        assert np.isfinite(X).all()
+        T = op(np.tril(A) if uplo == "L" else np.triu(A), tr)
+        lhs = T @ X if side == "L" else X @ T
+        gauge = (np.abs(T) @ np.abs(X) if side == "L" else np.abs(X) @ np.abs(T)) + np.abs(B)
+        resid = bound_ratio(lhs, B, gauge, na, EPS64)
+        assert resid <= 1.0, (side, uplo, tr, m, n, resid)
+
+
 def test_config4_dtrsm_8192_sampled_columns(ulm, torch_cuda):
     """DTRSM side=L uplo=L trans=N diag=N, m=n=8192, seed 3, device-resident: diagonal uniform[1,2),
     strict lower uniform[-1,1)/n, strict upper rogue.  Columns of X are independent, so the

@@ -66,7 +66,8 @@ struct GemmParams {
     int bat_am[2], bat_ak[2], bat_bn[2], bat_bk[2];
     int64_t bat_c[2];
     int bat_cr[2], bat_cc[2];     // the same shift of C as rows and columns
-    int c_tma;                    // the third tensor map covers C: whole tiles leave through shared memory
+    int c_tma;                    // the tensor maps of C are valid: whole tiles leave through shared memory
+    int64_t c_m, c_n;             // rows and columns of the stored C those maps describe
     // host side only: extents of the stored operands when they differ from the product's (batches)
     int64_t ext_a_mn, ext_a_k, ext_b_mn, ext_b_k, ext_c_m, ext_c_n;
 };
@@ -308,7 +309,7 @@ __host__ __device__ __forceinline__ bool tile_skipped(int tri, int64_t m0, int64
 template <int BM, int BN, int WARPS_M, int WARPS_N, int MAJOR_A, int MAJOR_B, int STAGES, int MIN_CTAS>
 __global__ void __launch_bounds__((WARPS_M *WARPS_N + 4) * 32, MIN_CTAS)
 dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const GemmParams p)
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmCs, const GemmParams p)
 {
     constexpr int NCW = WARPS_M * WARPS_N;          // consumer warps
     constexpr int WM = BM / WARPS_M, WN = BN / WARPS_N;
@@ -355,7 +356,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_barrier_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
-        if (STASH && p.c_tma) prefetch_tmap(&tmC);
+        if (STASH && p.c_tma) { prefetch_tmap(&tmC); prefetch_tmap(&tmCs); }
     }
     __syncthreads();
 
@@ -506,10 +507,18 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     atomicExch(cnt, 0);                    // back to zero for the next launch on this stream
                     __threadfence();
                 }
+                // A TMA store clips the rows of a tile in units of 16 bytes: with an odd number of rows it would
+                // write the element below the last one as well.  The store map therefore ends at the last even
+                // row, and the one row it leaves out is written here.
 #pragma unroll
                 for (int b = 0; b < BN / CBOX; ++b)
-                    tma_store_2d(&tmC, row, col + CBOX * b, stash + b * CBOX * BM);
+                    tma_store_2d(&tmCs, row, col + CBOX * b, stash + b * CBOX * BM);
                 bulk_commit_group();
+                if ((p.c_m & 1) && (int64_t)row + BM >= p.c_m) {
+                    const int r = (int)(p.c_m - 1 - row);
+                    double *last = p.C + (p.c_m - 1) + (int64_t)col * p.ldc;
+                    for (int c = 0; c < BN && col + c < p.c_n; ++c) last[(int64_t)c * p.ldc] = stash[c * BM + r];
+                }
                 bulk_wait_read_all();
             }
             bulk_wait_all();
@@ -890,12 +899,18 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     // C for the one-CTA-per-SM shape: boxes of BM rows x 32 columns, no swizzle.  Without a map (odd ldc,
     // unaligned C) the consumers write C themselves.
     GemmParams q = p;
-    CUtensorMap tmC = tmA;
+    CUtensorMap tmC = tmA, tmCs = tmA;
     q.c_tma = 0;
+    q.c_m = p.ext_c_m ? p.ext_c_m : p.m;
+    q.c_n = p.ext_c_n ? p.ext_c_n : p.n;
     if (ctas_per_sm == 1 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 2 == 0 && p.ldc < (1ll << 36)) {
-        const int64_t cm = p.ext_c_m ? p.ext_c_m : p.m, cn = p.ext_c_n ? p.ext_c_n : p.n;
-        q.c_tma = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.C, cm, cn, p.ldc, BM, 32,
-                               CU_TENSOR_MAP_SWIZZLE_NONE) ? 1 : 0;
+        // one map to fetch old tiles, one to store new ones that ends at the last even row (see the output thread)
+        const int64_t even_rows = q.c_m & ~1ll;
+        q.c_tma = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.C, q.c_m, q.c_n, p.ldc, BM, 32,
+                               CU_TENSOR_MAP_SWIZZLE_NONE) &&
+                  (even_rows == 0 || make_tmap_2d(&tmCs, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 8, p.C, even_rows, q.c_n, p.ldc, BM, 32,
+                                                  CU_TENSOR_MAP_SWIZZLE_NONE)) ? 1 : 0;
+        if (even_rows == 0) q.c_tma = 0;              // a single row: the consumers write it themselves
     }
     if ((p.leaf || p.nbatch > 1) && !q.c_tma) return -1;     // those tiles only leave through the buffer
 
@@ -956,7 +971,7 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     q.dynamic = (units > grid && p.sched) ? 1 : 0;
     trace("dgemm kernel tile %dx%d %s grid %d units %lld (whole %d, shared tiles %d over %d CTAs) kt %d",
           BM, BN, q.dynamic ? "dynamic" : "static", grid, (long long)units, q.split_first, q.region_tiles, q.nsu, kt);
-    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, tmC, q);
+    kern<<<grid, (WARPS_M * WARPS_N + 4) * 32, SMEM, st>>>(tmA, tmB, tmC, tmCs, q);
     count_launch();
     ULMB_CUDA(cudaGetLastError());
     return ULMB200_OK;
