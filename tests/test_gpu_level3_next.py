@@ -56,12 +56,10 @@ def test_dsymm_all_variants(ulm):
                 assert ratio <= 1.0, (side, uplo, m, n, alpha, beta, ratio)
 
 
-def test_dtrmm_all_variants(ulm):
-    seed = 50000
+def trmm_cases(ulm, shapes, seed, variants=None):
     R = ref("plain")
-    # the last two shapes have several 256-wide diagonal blocks and a ragged last one
-    for (m, n) in [(1, 1), (7, 5), (31, 12), (130, 70), (300, 129), (257, 260), (1100, 33), (33, 1300)]:
-        for side, uplo, tr, diag in itertools.product("LR", "UL", "NT", "NU"):
+    for (m, n) in shapes:
+        for side, uplo, tr, diag in (variants or itertools.product("LR", "UL", "NT", "NU")):
             seed += 2
             alpha = 0.7 if (m + n) % 2 else 1.0
             na = m if side == "L" else n
@@ -87,11 +85,34 @@ def test_dtrmm_all_variants(ulm):
             assert np.isfinite(got[:m, :n]).all(), "the unreferenced triangle of A was read"
             ratio = bound_ratio(got[:m, :n], want, gauge, na, EPS64)
             assert ratio <= 1.0, (side, uplo, tr, diag, m, n, ratio)
+
+
+def test_dtrmm_all_variants(ulm):
+    # the last two shapes have several 256-wide diagonal blocks and a ragged last one
+    trmm_cases(ulm, [(1, 1), (7, 5), (31, 12), (130, 70), (300, 129), (257, 260), (1100, 33), (33, 1300)], 50000)
     # alpha == 0 zeroes B
     Bv, Bb = padded(det_uniform(1, 9, 4), 11)
     A = np.asfortranarray(np.eye(9))
     assert ulm.dtrmm("L", "L", "N", "N", 9, 4, 0.0, A, Bv) == ulm.OK
     assert np.all(Bv == 0.0)
+
+
+@pytest.mark.parametrize("leaf,dim,other", [(512, 1100, 150), (1024, 2200, 136), (2048, 2100, 130)])
+def test_dtrmm_large_leaves(ulm, monkeypatch, leaf, dim, other):
+    """Leaves of order 512, 1024 and 2048: zero-filled copies of the diagonal blocks multiplied in place by the
+    triangular leaf of the GEMM kernel, a ragged last block, every side / uplo / trans / diag."""
+    monkeypatch.setenv("ULMB200_TRSM_LEAF", str(leaf))
+    ulm.reload_env()
+    for side in "LR":
+        m, n = (dim, other) if side == "L" else (other, dim)
+        trmm_cases(ulm, [(m, n)], 51000 + leaf + ord(side), [(side,) + v for v in itertools.product("UL", "NT", "NU")])
+
+
+def test_dtrmm_chosen_leaf_order_many_strips(ulm):
+    """The library's own choice (1024 from 2048 rows, 2048 from 4096 rows on, with at least 1024 columns)."""
+    trmm_cases(ulm, [(2304, 1500)], 52000, [("L", "L", "N", "N"), ("L", "U", "T", "U")])
+    trmm_cases(ulm, [(1500, 2304)], 52100, [("R", "U", "N", "N"), ("R", "L", "T", "N")])
+    trmm_cases(ulm, [(4200, 1100)], 52200, [("L", "U", "N", "N")])
 
 
 def test_dsyr2k_all_variants(ulm):

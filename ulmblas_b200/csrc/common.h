@@ -59,7 +59,7 @@ int *sched_words(cudaStream_t st);
 //   ULMB200_SGEMM=fp32|3xtf32    arithmetic of sgemm_ / cblas_sgemm
 //   ULMB200_WORKSPACE_CAP_MB=n   upper limit of the cached device work memory
 //   ULMB200_DGEMM_TILE=64|128, ULMB200_DGEMM_PATH=ldg, ULMB200_DGEMM_SPLITK=0   (test hooks)
-//   ULMB200_TRSM_LEAF=128|256|512|1024|2048   order of the inverted diagonal blocks of dtrsm (test hook)
+//   ULMB200_TRSM_LEAF=128|256|512|1024|2048   order of the diagonal blocks (leaves) of dtrsm and dtrmm (test hook)
 struct Settings {
     int trace = 0;
     int sgemm_3xtf32 = 0;

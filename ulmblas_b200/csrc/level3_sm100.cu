@@ -435,21 +435,26 @@ int dtrsm_with_scratch(cudaStream_t st, int side, int lower, int transA, int uni
 // 1024 is one launch that multiplies only the blocks of its triangle, where 256-leaves solve the same rows in
 // seven launches too short to fill the machine.  The larger blocks need TMA-addressable operands for the
 // batched products that build them.
+// What a leaf of order L > 256 needs: TMA-addressable operands and a reader counter per leaf tile.
+static bool large_leaf_ok(cudaStream_t st, int L, int64_t dim, int64_t other, const double *A, int64_t lda, const double *B,
+                          int64_t ldb)
+{
+    const int64_t tiles = ((L < dim ? L : dim) + 127) / 128 * ((other + 127) / 128);
+    return ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 && lda % 2 == 0 &&
+           ldb % 2 == 0 && dim < (1ll << 31) - 4096 && other < (1ll << 31) - 4096 && lda < (1ll << 36) &&
+           ldb < (1ll << 36) && tiles <= kSchedFlags && sched_words(st) != nullptr;
+}
+
 static int trsm_leaf_order(cudaStream_t st, int64_t dim, int64_t other, const double *A, int64_t lda, const double *B,
                            int64_t ldb)
 {
     int leaf = dim > 2 * kNB ? 2 * kNB : kNB;
-    // what the batched products and the in-place leaf need; beyond 256 nothing else can apply the inverses,
-    // whose blocks above (below) the diagonal are never written
-    auto large_ok = [&](int L) {
-        const int64_t tiles = ((L < dim ? L : dim) + 127) / 128 * ((other + 127) / 128);
-        return ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 && lda % 2 == 0 &&
-               ldb % 2 == 0 && dim < (1ll << 31) - 4096 && other < (1ll << 31) - 4096 && lda < (1ll << 36) &&
-               ldb < (1ll << 36) && tiles <= kSchedFlags && sched_words(st) != nullptr;
-    };
-    if (dim >= 2048 && other >= 1024 && large_ok(1024)) leaf = 1024;
+    // beyond 256 only the triangular leaf can apply the inverses, whose blocks above (below) the diagonal
+    // are never written
+    if (dim >= 2048 && other >= 1024 && large_leaf_ok(st, 1024, dim, other, A, lda, B, ldb)) leaf = 1024;
     const int forced = settings().trsm_leaf;
-    if (forced == 128 || forced == 256 || ((forced == 512 || forced == 1024 || forced == 2048) && large_ok(forced))) {
+    if (forced == 128 || forced == 256 ||
+        ((forced == 512 || forced == 1024 || forced == 2048) && large_leaf_ok(st, forced, dim, other, A, lda, B, ldb))) {
         leaf = forced;
         while (leaf > kNB && leaf / 2 >= dim) leaf /= 2;     // no larger than the triangle needs
     }
@@ -549,24 +554,44 @@ int dsymm_device(cudaStream_t st, int side, int lower, int64_t m, int64_t n, dou
 // are plain GEMM updates on rows/columns of B not yet overwritten, the diagonal blocks (256 x
 // 256) are multiplied from zero-filled copies and go through the leaf tile.
 // ---------------------------------------------------------------------------
-// nbt = size of the diagonal blocks = threads per CTA (128 or 256)
-__global__ void __launch_bounds__(512)
+// nbt = order of the diagonal blocks.  A CTA of min(nbt, 256) threads copies that many rows of kCleanCols
+// columns of one block (grid: blocks x row parts, column chunks), all loads of a thread in flight together.
+constexpr int kCleanCols = 16;
+__global__ void __launch_bounds__(256)
 trclean_blocks_kernel(const double *A, int64_t lda, int64_t dim, int lower, int unit, double *out, int nbt)
 {
-    const int blk = blockIdx.x, j = threadIdx.x;
+    const int parts = (nbt + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int blk = blockIdx.x / parts, j = (blockIdx.x % parts) * (int)blockDim.x + threadIdx.x;
+    if (j >= nbt) return;
     const int64_t r0 = (int64_t)blk * nbt;
     const int len = (int)((dim - r0) < nbt ? (dim - r0) : nbt);
     const double *Ab = A + r0 + r0 * lda;
     double *o = out + (int64_t)blk * nbt * nbt;
-    for (int i = 0; i < nbt; ++i) {
+    const int i0 = blockIdx.y * kCleanCols;
+    double v[kCleanCols];
+#pragma unroll
+    for (int q = 0; q < kCleanCols; ++q) {
         // element (j, i): threads run down a column, coalesced
-        double v = 0.0;
+        const int i = i0 + q;
+        v[q] = 0.0;
         if (i < len && j < len) {
-            if (i == j) v = unit ? 1.0 : Ab[j + (int64_t)i * lda];
-            else if (lower ? (j > i) : (j < i)) v = Ab[j + (int64_t)i * lda];
+            if (i == j) v[q] = unit ? 1.0 : Ab[j + (int64_t)i * lda];
+            else if (lower ? (j > i) : (j < i)) v[q] = Ab[j + (int64_t)i * lda];
         }
-        o[j + i * nbt] = v;
     }
+#pragma unroll
+    for (int q = 0; q < kCleanCols; ++q)
+        if (i0 + q < nbt) o[j + (int64_t)(i0 + q) * nbt] = v[q];
+}
+
+// the work tile of a leaf that cannot be multiplied in place, allocated when the first such leaf turns up
+static bool trmm_work_tile(TrsmCtx &c)
+{
+    if (c.W) return true;
+    const int64_t wel = c.left ? (int64_t)c.leaf * c.n : c.m * (int64_t)c.leaf;
+    c.W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
+    if (!c.W) c.status = ULMB200_CUDA_ERROR;
+    return c.W != nullptr;
 }
 
 static void mul_left(TrsmCtx &c, double alpha, int64_t r0, int64_t len)
@@ -576,6 +601,7 @@ static void mul_left(TrsmCtx &c, double alpha, int64_t r0, int64_t len)
         const double *tb = c.inv + (r0 / c.leaf) * c.leaf * c.leaf;
         const int r = dgemm_leaf_inplace(c.st, 1, c.eff_lower, c.trans, len, c.n, alpha, tb, c.leaf, c.B + r0, c.ldb, c.err);
         if (r >= 0) { c.status = r; return; }
+        if (!trmm_work_tile(c)) return;
         gemm_chk(c, c.trans, 0, len, c.n, len, alpha, tb, c.leaf, c.B + r0, c.ldb, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + r0, c.ldb, c.W, c.ldw, len, c.n);
         return;
@@ -601,6 +627,7 @@ static void mul_right(TrsmCtx &c, double alpha, int64_t c0, int64_t len)
         const double *tb = c.inv + (c0 / c.leaf) * c.leaf * c.leaf;
         const int r = dgemm_leaf_inplace(c.st, 0, c.eff_lower, c.trans, len, c.m, alpha, tb, c.leaf, c.B + c0 * c.ldb, c.ldb, c.err);
         if (r >= 0) { c.status = r; return; }
+        if (!trmm_work_tile(c)) return;
         gemm_chk(c, 0, c.trans, c.m, len, len, alpha, c.B + c0 * c.ldb, c.ldb, tb, c.leaf, 0.0, c.W, c.ldw);
         launch_copy(c, c.B + c0 * c.ldb, c.ldb, c.W, c.ldw, c.m, len);
         return;
@@ -628,23 +655,33 @@ int dtrmm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
     if (m == 0 || n == 0) return set_status(ULMB200_OK);
     if (int s = ensure_device()) return set_status(s);
     if (alpha == 0.0) return set_status(scale_matrix_device(st, B, ldb, m, n, 0.0, 0));      // trlmm.tcc:46-49
-    // Diagonal blocks of 256 once the triangle spans several: a leaf is then one product instead of
-    // three small ones (its zero half costs 256/dim extra flops).  Measured at 8192^2: 17.85 ms with
-    // 128-wide blocks, 17.61 with 256, 18.01 with 512.
-    const int leaf = dim > 256 ? 256 : kNB;
+    // Diagonal blocks copied with their other triangle zero-filled, multiplied in place by the triangular leaf
+    // of the GEMM kernel.  256 once the triangle spans several (a leaf is then one product instead of three
+    // small ones); 1024 and 2048 for large triangles with many columns, where the leaf multiplies only the
+    // blocks of the triangle and the recursion above it keeps just its large updates.
+    const int64_t other = (side == 0) ? n : m;
+    int leaf = dim > 256 ? 256 : kNB;
+    if (dim >= 2048 && other >= 1024 && large_leaf_ok(st, 1024, dim, other, A, lda, B, ldb)) leaf = 1024;
+    if (dim >= 4096 && other >= 1024 && large_leaf_ok(st, 2048, dim, other, A, lda, B, ldb)) leaf = 2048;
+    const int forced = settings().trsm_leaf;
+    if (forced == 128 || forced == 256 ||
+        ((forced == 512 || forced == 1024 || forced == 2048) && large_leaf_ok(st, forced, dim, other, A, lda, B, ldb))) {
+        leaf = forced;
+        while (leaf > kNB && leaf / 2 >= dim) leaf /= 2;
+    }
     const int64_t nblk = (dim + leaf - 1) / leaf;
     double *blk = static_cast<double *>(device_scratch(3, (size_t)nblk * leaf * leaf * sizeof(double)));
-    const int64_t wel = (side == 0) ? (int64_t)leaf * n : m * (int64_t)leaf;
-    double *W = static_cast<double *>(device_scratch(4, (size_t)wel * sizeof(double)));
-    if (!blk || !W) return set_status(ULMB200_CUDA_ERROR);
-    trclean_blocks_kernel<<<(int)nblk, leaf, 0, st>>>(A, lda, dim, lower, unit, blk, leaf);
+    if (!blk) return set_status(ULMB200_CUDA_ERROR);
+    const int cta = leaf < 256 ? leaf : 256;
+    trclean_blocks_kernel<<<dim3((unsigned)(nblk * ((leaf + cta - 1) / cta)), (unsigned)((leaf + kCleanCols - 1) / kCleanCols)), cta, 0, st>>>(
+        A, lda, dim, lower, unit, blk, leaf);
     count_launch();
     if (int e = check_cuda(cudaGetLastError(), "trclean_blocks_kernel", __FILE__, __LINE__)) return e;
     TrsmCtx c;
     c.st = st; c.left = (side == 0); c.lower = lower; c.trans = transA;
     c.eff_lower = (lower != 0) != (transA != 0);
     c.m = m; c.n = n; c.A = A; c.lda = lda; c.B = B; c.ldb = ldb;
-    c.inv = blk; c.W = W; c.ldw = c.left ? leaf : m;
+    c.inv = blk; c.W = nullptr; c.ldw = c.left ? leaf : m;
     c.leaf = leaf;
     c.err = nullptr;
     c.status = ULMB200_OK;
