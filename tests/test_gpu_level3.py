@@ -70,6 +70,34 @@ def test_sgemm_shapes_and_transposes(ulm, mode, monkeypatch):
                 assert ratio <= 1.0, (mode, m, n, k, ta, tb, alpha, beta, ratio)
 
 
+@pytest.mark.parametrize("pre", ["1", "0"])
+def test_sgemm_large_k_contiguous_operands(ulm, pre, monkeypatch):
+    """From 1024 rows (columns) of the other operand on, a K-contiguous operand (A with transA = T, B with
+    transB = N) is copied once into the M/N-contiguous layout TMA can feed straight to the consumers;
+    ULMB200_SGEMM_PRETRANSPOSE=0 keeps the transposition inside the kernel.  Ragged sizes, padded leading
+    dimensions, all four transpositions, both settings."""
+    monkeypatch.setenv("ULMB200_SGEMM", "fp32")
+    monkeypatch.setenv("ULMB200_SGEMM_PRETRANSPOSE", pre)
+    ulm.reload_env()
+    seed = 9500
+    for (m, n, k) in [(1100, 1300, 300), (1027, 1025, 259)]:
+        for ta, tb in itertools.product("NT", "NT"):
+            seed += 3
+            ra, ca = (m, k) if ta == "N" else (k, m)
+            rb, cb = (k, n) if tb == "N" else (n, k)
+            A, Ab = padded(det_uniform(seed, ra, ca, np.float32), ra + 3)
+            B, Bb = padded(det_uniform(seed + 1, rb, cb, np.float32), rb + 4)
+            C0v, C0b = padded(det_uniform(seed + 2, m, n, np.float32), m + 4)
+            want = reference_sgemm(ta, tb, m, n, k, 0.7, A, B, 1.3, np.asfortranarray(C0v))
+            got = C0b.copy(order="F")
+            Ab0, Bb0 = Ab.copy(order="F"), Bb.copy(order="F")
+            assert ulm.sgemm(ta, tb, m, n, k, 0.7, A, B, 1.3, got[:m, :n], lda=ra + 3, ldb=rb + 4, ldc=m + 4) == ulm.OK
+            assert np.array_equal(Ab, Ab0) and np.array_equal(Bb, Bb0), "an input operand was modified"
+            assert np.array_equal(got[m:, :], C0b[m:, :]), "padding rows of C were written"
+            ratio = bound_ratio(got[:m, :n], want, gemm_gauge(0.7, op(A, ta), op(B, tb), 1.3, C0v), k, EPS32)
+            assert ratio <= 1.0, (pre, m, n, k, ta, tb, ratio)
+
+
 def test_sgemm_split_k_tail(ulm, monkeypatch):
     """Tile counts a little above a multiple of the SM count: the FP32 kernel gives the last few tiles
     to several CTAs each, one K range per CTA, added in a fixed order.  Checked on sampled columns

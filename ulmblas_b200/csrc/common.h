@@ -59,6 +59,7 @@ int *sched_words(cudaStream_t st);
 //   ULMB200_SGEMM=fp32|3xtf32    arithmetic of sgemm_ / cblas_sgemm
 //   ULMB200_WORKSPACE_CAP_MB=n   upper limit of the cached device work memory
 //   ULMB200_DGEMM_TILE=64|128, ULMB200_DGEMM_PATH=ldg, ULMB200_DGEMM_SPLITK=0   (test hooks)
+//   ULMB200_SGEMM_PRETRANSPOSE=0   never copy K-contiguous operands of sgemm (test hook)
 //   ULMB200_TRSM_LEAF=128|256|512|1024|2048   order of the diagonal blocks (leaves) of dtrsm and dtrmm (test hook)
 struct Settings {
     int trace = 0;
@@ -66,6 +67,7 @@ struct Settings {
     int64_t workspace_cap = -1;          // bytes, -1 = none
     int dgemm_tile = 0, dgemm_ldg = 0, dgemm_split = 1;
     int sgemm_path = 0;                  // 0 auto, 1 force the plain-load kernel
+    int sgemm_pretranspose = 1;          // 0: K-contiguous operands are always transposed inside the kernel
     int trsm_leaf = 0;                   // 0 auto
 };
 const Settings &settings();

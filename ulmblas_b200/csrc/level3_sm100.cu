@@ -475,7 +475,7 @@ int dtrsm_device(cudaStream_t st, int side, int lower, int transA, int unit, int
     double *W = nullptr, *pairs = nullptr;
     if (leaf > 2 * kNB) {
         // the large leaves are applied in place only: no work tile, but room for the batched products
-        pairs = static_cast<double *>(device_scratch(5, (size_t)nblk * leaf * leaf / 4 * sizeof(double)));
+        pairs = static_cast<double *>(device_scratch(7, (size_t)nblk * leaf * leaf / 4 * sizeof(double)));
         if (!pairs) return set_status(ULMB200_CUDA_ERROR);
     } else {
         const int64_t wel = (side == 0) ? (int64_t)leaf * n : m * (int64_t)leaf;

@@ -252,6 +252,38 @@ static int launch_fp32(cudaStream_t st, const SgemmParams &p, int grid)
     return ULMB200_OK;
 }
 
+// out(i, p) = in(p, i): in is rows x cols with the rows contiguous (element (p, i) at in[p + i * ldi]), out is
+// cols x rows with ITS rows contiguous (element (i, p) at out[i + p * ldo]).  32 x 32 tiles through shared
+// memory, both sides coalesced; any alignment.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float *in, int64_t ldi, int64_t rows, int64_t cols,
+                                                            float *out, int64_t ldo, int64_t tiles_r)
+{
+    __shared__ float tile[32][33];
+    const int64_t tr = blockIdx.x % tiles_r, tc = blockIdx.x / tiles_r;
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;               // 32 x 8 threads
+    const int64_t p0 = tr * 32, i0 = tc * 32;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int64_t p = p0 + x, i = i0 + y + 8 * q;
+        tile[y + 8 * q][x] = (p < rows && i < cols) ? in[p + i * ldi] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int64_t i = i0 + x, p = p0 + y + 8 * q;
+        if (i < cols && p < rows) out[i + p * ldo] = tile[x][y + 8 * q];
+    }
+}
+
+static int transpose_f32(cudaStream_t st, const float *in, int64_t ldi, int64_t rows, int64_t cols, float *out, int64_t ldo)
+{
+    const int64_t tiles_r = (rows + 31) / 32, tiles_c = (cols + 31) / 32;
+    if (tiles_r * tiles_c >= (1ll << 31)) return -1;
+    transpose_f32_kernel<<<(unsigned)(tiles_r * tiles_c), 256, 0, st>>>(in, ldi, rows, cols, out, ldo, tiles_r);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "transpose_f32_kernel", __FILE__, __LINE__);
+}
+
 int sgemm_3xtf32_device(cudaStream_t st, int transA, int transB, int64_t m, int64_t n, int64_t k,
                         float alpha, const float *A, int64_t lda, const float *B, int64_t ldb,
                         float beta, float *C, int64_t ldc);
@@ -284,7 +316,29 @@ int sgemm_device(cudaStream_t st, int mode, int transA, int transB, int64_t m, i
         return set_status(sgemm_3xtf32_device(st, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc));
 
     if (!settings().sgemm_path) {
-        const int r = sgemm_ws_device(st, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
+        // A K-contiguous operand (op(A) = A^T, op(B) = B) is transposed by the producer threads inside the
+        // kernel, tile by tile (global loads along k, 4-byte shared stores), and that traffic through the
+        // load/store pipe costs the consumers: 55 TFLOP/s with both operands K-contiguous against 62 with
+        // both arriving by TMA.  For large products it is cheaper to write the M/N-contiguous copy once --
+        // the reference's pack_A / pack_B done for the whole operand -- at 8 bytes of traffic per element
+        // (2 % of the product's time at 4096^3) and to let TMA feed every tile.  An operand is copied when
+        // the other dimension makes the product per element long enough to pay for it.
+        const float *Au = A, *Bu = B;
+        int64_t ldau = lda, ldbu = ldb;
+        int tau = transA, tbu = transB;
+        const bool pre = settings().sgemm_pretranspose != 0 && k >= 256;
+        if (pre && transA && n >= 1024 && m >= 256) {
+            const int64_t ldt = (m + 3) & ~3ll;
+            float *At = static_cast<float *>(device_scratch(15, sizeof(float) * (size_t)ldt * k));
+            if (At && transpose_f32(st, A, lda, k, m, At, ldt) == ULMB200_OK) { Au = At; ldau = ldt; tau = 0; }
+        }
+        if (pre && !transB && m >= 1024 && n >= 256) {
+            const int64_t ldt = (n + 3) & ~3ll;
+            float *Bt = static_cast<float *>(device_scratch(14, sizeof(float) * (size_t)ldt * k));
+            if (Bt && transpose_f32(st, B, ldb, k, n, Bt, ldt) == ULMB200_OK) { Bu = Bt; ldbu = ldt; tbu = 1; }
+        }
+        int r = sgemm_ws_device(st, tau, tbu, m, n, k, alpha, Au, ldau, Bu, ldbu, beta, C, ldc);
+        if (r < 0 && (Au != A || Bu != B)) r = sgemm_ws_device(st, transA, transB, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc);
         if (r >= 0) return set_status(r);
     }
     SgemmParams p;
