@@ -323,6 +323,45 @@ def test_shared_tiles_forced_on_and_off(ulm, mode, monkeypatch):
     assert np.array_equal(c1, c2), "sharing tiles must not make results depend on timing"
 
 
+def test_shared_tiles_second_piece_per_cta_is_repeatable(ulm, torch_cuda, monkeypatch):
+    """Products whose last tiles are shared so that most CTAs take two pieces (the head of one tile, then the
+    tail of the tile before it), repeated while another stream keeps the SMs busy.  Two things went wrong here
+    once and are pinned by this test: a CTA's release of a pipeline stage overtaking its own shared loads (the
+    TMA refill for the second piece changed the stage under them: wrong values of a few k in one 16-row block,
+    in up to two launches out of three), and old values of C read from a stale L1 line when the columns of C do
+    not start on 128-byte boundaries (ldc = 1300).  Every result must equal the first bit for bit and lie
+    inside the bound."""
+    torch = torch_cuda
+    monkeypatch.setenv("ULMB200_DGEMM_TILE", "128")
+    monkeypatch.setenv("ULMB200_DGEMM_SPLITK", "2")
+    ulm.reload_env()
+    side = torch.cuda.Stream()
+    X = torch.rand(2048, 2048, device="cuda")
+    Y = torch.empty_like(X)
+    for (m, n, k, reps) in [(1280, 640, 4744, 40), (1300, 550, 3976, 25), (2100, 900, 700, 12)]:
+        A, B, C0 = det_uniform(400 + m, m, k), det_uniform(401 + m, k, n), det_uniform(402 + m, m, n)
+        want = reference_dgemm("N", "N", m, n, k, -0.7, A, B, 1.0, C0, m)
+        gauge = gemm_gauge(-0.7, A, B, 1.0, C0)
+        dA, dB = (torch.from_numpy(np.ascontiguousarray(X_.T)).cuda() for X_ in (A, B))
+        dC0 = torch.from_numpy(np.ascontiguousarray(C0.T)).cuda()
+        first = None
+        for rep in range(reps):
+            dC = dC0.clone()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    torch.mm(X, X, out=Y)
+            ulm.dev_dgemm(0, 0, m, n, k, -0.7, dA.data_ptr(), m, dB.data_ptr(), k, 1.0, dC.data_ptr(), m)
+            torch.cuda.synchronize()
+            got = dC.cpu().numpy().T
+            if first is None:
+                first = got
+                assert bound_ratio(got, want, gauge, k, EPS64) <= 1.0, (m, n, k)
+            else:
+                assert np.array_equal(got, first), (m, n, k, rep, "results of identical calls differ")
+    assert ulm.check_device_error() == 0
+
+
 def test_launches_on_two_streams_do_not_disturb_each_other(ulm, torch_cuda):
     """One large product on stream A while 160 small ones go out on stream B: the persistent kernels'
     tile counters and fold flags belong to the stream, so neither side can advance or reset the

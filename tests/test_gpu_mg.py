@@ -65,6 +65,20 @@ from helpers import EPS64, bound_ratio, det_uniform, gemm_gauge
 from test_gpu_dgemm import reference_dgemm
 m, n, k = 1300, 1100, 5000
 A, B, C0 = det_uniform(61, m, k), det_uniform(62, k, n), det_uniform(63, m, n)
+
+
+def agree(ok, what):
+    # Every rank learns whether all ranks passed this step (a tiny all-reduce between steps, nothing else in
+    # flight); if one did not, all leave together instead of one leaving its peers inside a collective.
+    t = torch.tensor([1.0 if ok else 0.0], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if t.item() < 0.5:
+        if not ok:
+            print("FAILED on rank %%d: %%s" %% (rank, what), flush=True)
+        dist.destroy_process_group()
+        sys.exit(1 if not ok else 0)
+
+
 eng = ShardedDgemm(m, n, k, first=256)
 j0, j1 = eng.plan.cols
 nr = j1 - j0
@@ -79,11 +93,25 @@ for rep in range(2):                     # the second call plans with the measur
     dC.copy_(dev(C0[:, j0:j1]))
     eng.run(-0.7, dA, dB, 1.3, dC)
     torch.cuda.synchronize()
-assert eng.wait(20000) == ulm.OK
+agree(eng.wait(20000) == ulm.OK, "a kernel gave up on a bounded wait (device-resident)")
 widths, reserve, rate, _ = eng.last_plan()
-assert sum(widths) == k and reserve[-1] == 0 and rate > 0.0, (widths, reserve, rate)
-assert bound_ratio(dC.cpu().numpy().T, want, gauge, k, EPS64) <= 1.0, "device-resident block wrong on rank %%d" %% rank
-assert rank == 0 or np.array_equal(dA.cpu().numpy().T, A), "A did not arrive intact"
+agree(sum(widths) == k and reserve[-1] == 0 and rate > 0.0, "plan %%s %%s %%s" %% (widths, reserve, rate))
+
+
+def where_off(got):
+    bad = np.argwhere(np.abs(got - want) > 2 * k * EPS64 * gauge)
+    if len(bad) == 0:
+        return ""
+    tiles = sorted(set((int(r) // 128, int(c) // 128) for r, c in bad))
+    return "; %%d entries off in %%d tiles %%s, rows %%d..%%d, first %%s, got/want %%s" %% (
+        len(bad), len(tiles), tiles[:16], bad[:, 0].min(), bad[:, 0].max(), bad[:4].tolist(),
+        [(float(got[r, c]), float(want[r, c])) for r, c in bad[:3]])
+
+
+got = dC.cpu().numpy().T
+ratio = bound_ratio(got, want, gauge, k, EPS64)
+agree(ratio <= 1.0, "device-resident block wrong: error / bound = %%g, plan %%s%%s" %% (ratio, widths, where_off(got)))
+agree(rank == 0 or np.array_equal(dA.cpu().numpy().T, A), "A did not arrive intact")
 # 2. host-resident, A pushed by the root; 3. every rank holds A and brings its share
 for every in (False, True):
     hA = pin(A) if (rank == 0 or every) else None
@@ -92,9 +120,12 @@ for every in (False, True):
     wB, wC = torch.zeros_like(dB), torch.zeros_like(dC)
     eng.run(-0.7, wA, wB, 1.3, wC, host=(hA, hB, hC), every_rank_has_a=every)
     torch.cuda.synchronize()
-    assert eng.wait(20000) == ulm.OK
-    assert bound_ratio(hC.numpy().T, want, gauge, k, EPS64) <= 1.0, "host-resident block wrong on rank %%d (every=%%s)" %% (rank, every)
-    assert np.array_equal(wA.cpu().numpy().T, A), "A did not arrive intact (every=%%s)" %% every
+    agree(eng.wait(20000) == ulm.OK, "a kernel gave up on a bounded wait (host-resident, every=%%s)" %% every)
+    got = hC.numpy().T
+    ratio = bound_ratio(got, want, gauge, k, EPS64)
+    where = where_off(got) if ratio > 1.0 else ""
+    agree(ratio <= 1.0, "host-resident block wrong (every=%%s): error / bound = %%g, plan %%s%%s" %% (every, ratio, eng.last_plan()[0], where))
+    agree(np.array_equal(wA.cpu().numpy().T, A), "A did not arrive intact (every=%%s)" %% every)
 dist.barrier()
 eng.close()
 if rank == 0:
@@ -112,9 +143,32 @@ def test_ranks_on_several_gpus(torch_cuda, tmp_path):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     script = tmp_path / "rank.py"
     script.write_text(_RANK % dict(root=ROOT))
-    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world), str(port)], stdout=subprocess.PIPE,
-                              stderr=subprocess.PIPE, text=True) for r in range(world)]
-    outs = [p.communicate(timeout=600) for p in procs]
-    for p, (o, e) in zip(procs, outs):
-        assert p.returncode == 0, e[-3000:]
-    assert "OK" in outs[0][0]
+    logs = [open(tmp_path / f"rank{r}.log", "w+") for r in range(world)]
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world), str(port)], stdout=logs[r],
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    # A rank that fails an assertion leaves its peers waiting in their next collective: as soon as one rank
+    # has exited with an error (or after five minutes) the others are stopped, by PID, and the first failure
+    # is reported.
+    import time
+    deadline = time.time() + 300
+    failed = None
+    while any(p.poll() is None for p in procs) and time.time() < deadline and failed is None:
+        for r, p in enumerate(procs):
+            if p.poll() not in (None, 0):
+                failed = r
+        time.sleep(0.5)
+    for p in procs:
+        if p.poll() is None:
+            if failed is None and time.time() < deadline:
+                continue
+            p.kill()
+    for p in procs:
+        p.wait()
+
+    def log(r):
+        logs[r].seek(0)
+        return logs[r].read()[-3000:]
+    if failed is None:
+        failed = next((r for r, p in enumerate(procs) if p.returncode != 0), None)
+    assert failed is None, f"rank {failed} failed:\n" + log(failed)
+    assert "OK" in log(0)

@@ -141,6 +141,7 @@ int *device_error_word()
         if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
         g_allocs.fetch_add(1, std::memory_order_relaxed);
         cudaMemset(p, 0, 256);
+        cudaDeviceSynchronize();
         d.err_word = p;
     }
     return d.err_word;
@@ -212,7 +213,10 @@ int *sched_words(cudaStream_t st)
             return nullptr;
         }
         g_allocs.fetch_add(1, std::memory_order_relaxed);
+        // the memset runs on the legacy default stream, which non-blocking streams do not wait for: make sure
+        // the words are zero before any launch on any stream can see them
         cudaMemset(p, 0, bytes);
+        cudaDeviceSynchronize();
         d.sched = p;
     }
     auto it = d.sched_of_stream.find(id);

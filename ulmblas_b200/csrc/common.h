@@ -154,6 +154,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Release of a buffer the caller has read with shared loads.  `seen` is computed from the registers those
+// loads wrote; it is stored to `sink` (a word of shared memory nobody reads) before the arrive, so the
+// store cannot issue before the loads have returned, and the arrive -- a release -- follows the store.
+__device__ __forceinline__ void mbar_arrive_after(uint64_t *bar, uint32_t seen, volatile uint32_t *sink)
+{
+    asm volatile("st.shared.u32 [%1], %2;\n\t"
+                 "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)), "r"(smem_u32(const_cast<uint32_t *>(sink))), "r"(seen)
+                 : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;

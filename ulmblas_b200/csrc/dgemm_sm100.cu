@@ -122,10 +122,27 @@ __device__ __forceinline__ double2 lds128(uint32_t addr)
     return v;
 }
 
+// Releases a stage the warp has finished reading.  The tensor-core instructions that consume the
+// fragments may be scheduled after a plain arrive, and then nothing makes the arrive wait for the stage's
+// last shared loads: a TMA refill was seen to overtake a load still in flight (wrong values of one to four
+// k in one 16-row block of a tile, about once in 10^2 launches of a product whose CTAs take a second piece
+// of work).  So every lane reads one more word of the stage after the stage's tensor-core instructions --
+// shared loads of a warp return in the order they were issued -- and lane 0 stores that word before it
+// arrives: the store cannot issue before the load has returned, and the arrive, a release, follows the store.
+// (The same load issued right behind the fragment loads, ahead of the tensor-core instructions, did not
+// close the window: measured.)
+__device__ __forceinline__ void release_stage(uint64_t *empty_bar, uint32_t stage_addr, volatile uint32_t *sink, int lane)
+{
+    uint32_t last;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(last) : "r"(stage_addr + 4u * (uint32_t)lane) : "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive_after(empty_bar, last, sink);
+}
+
 // One pipeline stage (16 k) of a warp's MT x NT grid of m16n8 tiles.
 template <int MAJOR_A, int MAJOR_B, int MT, int NT>
 __device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32_t (&ba)[2],
-                                          const uint32_t (&bb)[2], double (&acc)[MT][NT][4])
+                                              const uint32_t (&bb)[2], double (&acc)[MT][NT][4])
 {
     static_assert(NT % 2 == 0, "n8 tiles come in pairs");
 #pragma unroll
@@ -167,7 +184,11 @@ __device__ __forceinline__ void mma_stage(uint32_t sA, uint32_t sB, const uint32
 }
 
 // C(row, col) <- alpha*acc + beta*C for the warp's accumulators; rows/cols
-// outside m x n (and outside the requested triangle) are skipped.  The old values of C
+// outside m x n (and outside the requested triangle) are skipped.  The old values are read past
+// L1 (ld.global.cg): the pieces of a shared tile hand their partial sums on through C, and a CTA
+// that works on two tiles may hold a line in L1 that straddles both -- when the columns of C do not
+// start on 128-byte boundaries the last rows of one tile share a line with the first of the next --
+// from before the other tile's previous piece was written.  The old values of C
 // of G m16 tiles are fetched first (independent loads in flight together), then combined
 // and stored: the epilogue costs G times fewer memory round trips.  With M-contiguous A the
 // two rows a lane holds are adjacent (2g, 2g+1), so a 16-byte aligned C moves them as one
@@ -200,7 +221,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, double *__restrict
                         const bool v = col < p.n;
                         ok[g][j][w] = ok[g][j][2 + w] = v;
                         double2 o = make_double2(0.0, 0.0);
-                        if (use_c && v) o = *reinterpret_cast<const double2 *>(C + r0 + col * p.ldc);
+                        if (use_c && v) o = __ldcg(reinterpret_cast<const double2 *>(C + r0 + col * p.ldc));
                         old[g][j][w] = o.x; old[g][j][2 + w] = o.y;
                     }
             } else {
@@ -214,7 +235,7 @@ __device__ __forceinline__ void epilogue(const GemmParams &p, double *__restrict
                         if (p.tri == 1) v = v && row <= col;
                         if (p.tri == 2) v = v && row >= col;
                         ok[g][j][e] = v;
-                        old[g][j][e] = (v && use_c) ? C[row + col * p.ldc] : 0.0;
+                        old[g][j][e] = (v && use_c) ? __ldcg(C + row + col * p.ldc) : 0.0;
                     }
             }
         }
@@ -340,6 +361,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     StashInfo *info = reinterpret_cast<StashInfo *>(stash_full + 1);               // [2], tiles alternate
     volatile int *abort_flag = reinterpret_cast<volatile int *>(info + 2);
     volatile int *tile_slot = abort_flag + 1;      // tile id carried by each stage, -1 = no more work
+    volatile uint32_t *release_sink = reinterpret_cast<volatile uint32_t *>(tile_slot + STAGES);     // one word per consumer warp
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -554,8 +576,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             const uint32_t sA = smem_base + s * STAGE_BYTES;
             mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
+            release_stage(&empty[s], sA, release_sink + warp, lane);
         }
         return true;
     };
@@ -668,8 +689,7 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
                 const uint32_t sA = smem_base + s * STAGE_BYTES;
                 mma_stage<MAJOR_A, MAJOR_B, MT, NT>(sA, sA + A_BYTES, ba, bb, acc);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
+                release_stage(&empty[s], sA, release_sink + warp, lane);
             }
             if (!stash_tile(0.0)) return;
             continue;
@@ -915,7 +935,7 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
     if ((p.leaf || p.nbatch > 1) && !q.c_tma) return -1;     // those tiles only leave through the buffer
 
     constexpr size_t SMEM = (size_t)STAGES * (BM + BN) * 128 + (CTAS_PER_SM == 1 ? (size_t)BM * BN * 8 : 0) +
-                            (2 * STAGES + 3) * 8 + 2 * sizeof(StashInfo) + 16 + 4 * STAGES + 1024;
+                            (2 * STAGES + 3) * 8 + 2 * sizeof(StashInfo) + 16 + 4 * STAGES + 4 * 16 + 1024;
     auto kern = dgemm_tma_kernel<BM, BN, WARPS_M, WARPS_N, MAJOR_A, MAJOR_B, STAGES, CTAS_PER_SM>;
     static bool attr_done[kMaxDevices] = {};
     const int dev = current_device();

@@ -143,6 +143,7 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     volatile int *unit_seq = abort_flag + 1;                  // how many units producer thread 0 has drawn so far
     volatile int *unit_ring = abort_flag + 2;                 // [8]: the units drawn, for the other producer threads
     volatile int *unit_of_stage = abort_flag + 10;            // [STAGES]: unit a stage belongs to, -1 = end
+    volatile uint32_t *release_sink = reinterpret_cast<volatile uint32_t *>(abort_flag + 16);      // one word per consumer warp
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -347,12 +348,23 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int i = 0; i < 8; ++i) sw_ffma2(acc[i][j], a2[cb][i], b2[j]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
+            // Release through one more load of the stage and a store of what it returned (shared loads of a warp
+            // return in issue order; the store cannot issue before the load is back; the arrive follows the
+            // store): a plain arrive may overtake fragment loads whose packed FMAs were scheduled after it, and
+            // the TMA refill then changes the stage under them.
+            {
+                uint32_t last;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(last) : "r"(sa + 4u * (uint32_t)lane) : "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_after(&empty[s], last, release_sink + warp);
+            }
         }
         return true;
     };
 
+    // Old values of C are read past L1 (ld.global.cg): the pieces of a shared tile hand their partial sums on
+    // through C, and a line that straddles two tiles (columns of C not on 128-byte boundaries) may sit in this
+    // SM's L1 from before the other tile's previous piece was written.
     // C(row, col) <- alpha*acc + beta*C for this thread's 16 x 8 outputs, 4 consecutive rows per
     // 16-byte access where C allows it
     auto epilogue = [&](float beta, int64_t m0, int64_t n0) {
@@ -372,7 +384,7 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (vec && row + 3 < p.m) {
                     float4 o = make_float4(alpha * v[0], alpha * v[1], alpha * v[2], alpha * v[3]);
                     if (beta != 0.0f) {
-                        const float4 old = *reinterpret_cast<const float4 *>(c);
+                        const float4 old = __ldcg(reinterpret_cast<const float4 *>(c));      // past L1: see below
                         o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y);
                         o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w);
                     }
@@ -382,7 +394,7 @@ sgemm_ws_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int e = 0; e < 4; ++e) {
                         if (row + e < p.m) {
                             float o = alpha * v[e];
-                            if (beta != 0.0f) o = fmaf(beta, c[e], o);
+                            if (beta != 0.0f) o = fmaf(beta, __ldcg(c + e), o);
                             c[e] = o;
                         }
                     }
