@@ -244,9 +244,8 @@ def main():
     torch.cuda.synchronize()
 
     # roofline denominator: FP64 tensor-pipe throughput measured on this GPU, register operands only
-    peak_tf = None
-    if rank == 0:
-        peak_tf = max(ulm.peak_probe(2, 4000)[0], ulm.peak_probe(2, 20000)[0])
+    # (every rank probes its own GPU; rank 0's figure is the line's roofline.peak)
+    peak_tf = max(ulm.peak_probe(2, 4000)[0], ulm.peak_probe(2, 20000)[0])
 
     eng = ShardedDgemm(m, n, k, first=a.kp_first, reserve_sms=a.nccl_ctas)
 
@@ -296,6 +295,14 @@ def main():
     kdur = eng.last_gemm_ms()
     kflops = [2.0 * m * nr * w for w in widths][:len(kdur)]
     ach_tf = (sum(kflops) / (sum(kdur) * 1e-3)) * 1e-12 if kdur and sum(kdur) > 0 else None
+    # every rank's kernel time and pipe probe: the step ends with the slowest GPU
+    rank_ms, rank_peak = [round(sum(kdur), 3)], [round(peak_tf, 2) if peak_tf else None]
+    if world > 1:
+        both = torch.tensor([sum(kdur), peak_tf or 0.0], dtype=torch.float64, device=dev)
+        gathered = [torch.zeros_like(both) for _ in range(world)]
+        dist.all_gather(gathered, both)
+        rank_ms = [round(float(g[0].item()), 3) for g in gathered]
+        rank_peak = [round(float(g[1].item()), 2) for g in gathered]
 
     # parity on sampled rows x columns of this rank's block against the CPU oracle
     parity = None
@@ -343,7 +350,8 @@ def main():
                          "peak_source": "FP64 DMMA (mma.sync m16n8k8.f64) register-only probe run on this GPU "
                                         "just before the timed region; MEASURED_PEAKS.json holds no FP64 figure",
                          "kernel": "dgemm_tma_kernel<128,128>", "launches_timed": len(kdur),
-                         "launch_ms_last_step": [round(x, 3) for x in kdur]},
+                         "launch_ms_last_step": [round(x, 3) for x in kdur],
+                         "kernel_ms_last_step_by_rank": rank_ms, "peak_by_rank": rank_peak},
             "cpu_baseline": cpu,
             "e2e": e2e,
             "gpu_launches": launches,
