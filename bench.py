@@ -351,6 +351,7 @@ def main():
                                         "just before the timed region; MEASURED_PEAKS.json holds no FP64 figure",
                          "kernel": "dgemm_tma_kernel<128,128>", "launches_timed": len(kdur),
                          "launch_ms_last_step": [round(x, 3) for x in kdur],
+                         "launch_start_ms_last_step": [round(x, 3) for x in eng.last_gemm_start_ms()] if world > 1 else None,
                          "kernel_ms_last_step_by_rank": rank_ms, "peak_by_rank": rank_peak},
             "cpu_baseline": cpu,
             "e2e": e2e,

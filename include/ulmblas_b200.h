@@ -339,8 +339,9 @@ int ulmb200_mg_plan_panels(int64_t m, int64_t n_block, int64_t k, int world, int
                            double transport_gbs, double gemm_tflops, int64_t *widths, int *reserve, int cap);
 /* Plan of the communicator's last call, and the transport rates (GB/s of A reaching the ranks:
  * device-resident calls, host calls; 0 = nothing measured yet).  Every rank measures; on the second
- * and on the fourth call of a kind the ranks agree on the smallest measurement (their plans must be
- * identical) with one tiny all-reduce and a host-side wait, and keep that value afterwards.          */
+ * and on the third call of a kind the ranks agree on the smallest of their measurements of the call before
+ * (their plans must be identical) with one tiny all-reduce and a host-side wait for that call's transfers,
+ * and keep the last value afterwards.                                                                  */
 int ulmb200_mg_last_plan(void *handle, int64_t *widths, int *reserve, int cap,
                          double *device_rate_gbs, double *host_rate_gbs);
 /* Overrides the rates the next plan uses (<= 0 leaves one as it is); every rank must pass the same.  */
@@ -349,6 +350,9 @@ int ulmb200_mg_set_rates(void *handle, double transport_gbs, double host_gbs, do
  * recorded while profiling is switched on; read after the call has finished.                       */
 int ulmb200_mg_profile(void *handle, int on);
 int ulmb200_mg_last_gemm_ms(void *handle, double *ms, int cap);
+/* When each of those products started, in ms after the call's first transfer was queued (device-resident
+ * call on more than one rank; shows a product waiting for its panel).                                   */
+int ulmb200_mg_last_gemm_start_ms(void *handle, double *ms, int cap);
 
 /* The persistent DGEMM grid normally takes every SM.  A caller that runs a collective
  * (e.g. the NCCL broadcast of the next A panel) beside it can ask the following DGEMM

@@ -126,6 +126,7 @@ lib.ulmb200_mg_last_plan.argtypes = [_vp, _pi64, _pi, _int, _pd, _pd]
 lib.ulmb200_mg_set_rates.argtypes = [_vp, _dbl, _dbl, _dbl]
 lib.ulmb200_mg_profile.argtypes = [_vp, _int]
 lib.ulmb200_mg_last_gemm_ms.argtypes = [_vp, _pd, _int]
+lib.ulmb200_mg_last_gemm_start_ms.argtypes = [_vp, _pd, _int]
 
 CblasRowMajor, CblasColMajor = 101, 102
 CblasNoTrans, CblasTrans, CblasConjTrans, AtlasConj = 111, 112, 113, 114

@@ -112,6 +112,7 @@ struct MgComm {
     cudaEvent_t ev[kMgEvents] = {};
     cudaEvent_t t0 = nullptr, t1 = nullptr;      // transport timing: first panel queued .. last panel landed
     bool timed = false;
+    int timed_which = 0;                         // which kind of call (device / host operands) the events belong to
     double timed_bytes = 0.0;
     double rate_gbs[2] = {0.0, 0.0};             // transport rate the plans use: [0] device-resident, [1] host staging
     double seen_gbs[2] = {0.0, 0.0};             // what this rank has measured itself since the ranks last agreed
@@ -132,21 +133,32 @@ struct MgComm {
 
 // The K-panel plan must be the same on every rank -- the ranks' collectives have to match -- so the
 // rate it is computed from is never a rank's own measurement.  Each rank measures the transport of its
-// calls; on the second and on the fourth call of a kind the ranks agree on the smallest of their
-// measurements (one tiny all-reduce and a host-side wait), and that value stands from then on.
+// calls; on the second and on the third call of a kind the ranks agree on the smallest of their latest
+// measurements (one tiny all-reduce and a host-side wait), and the last value stands from then on.
+// The ranks agree on the transport rate at the start of their second and third call of a kind.
+constexpr int kAgreeCalls = 2;
+
 static int fold_rate(MgComm *c, int which, NcclApi *N)
 {
     const int call = c->calls[which]++;
-    if (c->timed) {
-        // the transport of the previous call has long finished
-        c->timed = false;
+    // The plan of a call rests on the transport rate seen in the call before it, under that call's own plan
+    // and beside its products.  Every call first waits (host side) for the previous call's transfers -- they
+    // end early in a call, and the host still has the whole of that call's last product to queue this one --
+    // and takes their rate.  On the second and third call the ranks then agree on the smallest rate (one tiny
+    // all-reduce, which has to wait for an SM until the previous call's last product is done): ranks'
+    // collectives must match, so must their plans.  Later calls keep the agreed rate.
+    const bool agree_now = c->world > 1 && N && c->agree && call >= 1 && call <= kAgreeCalls;
+    if (c->timed && c->timed_which == which) {
+        if (c->world > 1) ULMB_CUDA(cudaStreamSynchronize(c->comm_stream));
         float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, c->t0, c->t1) == cudaSuccess && ms > 0.f)
+        if (cudaEventElapsedTime(&ms, c->t0, c->t1) == cudaSuccess && ms > 0.f) {
             c->seen_gbs[which] = c->timed_bytes / (ms * 1e-3) * 1e-9;
-        else
-            cudaGetLastError();
+            c->timed = false;
+        } else {
+            cudaGetLastError();          // still under way: the rate stays what it was
+        }
     }
-    if (c->world <= 1 || !N || !c->agree || (call != 1 && call != 3)) return ULMB200_OK;
+    if (!agree_now) return ULMB200_OK;
     double mine = c->seen_gbs[which] > 0.0 ? c->seen_gbs[which] : 1e9;       // "no opinion"
     ULMB_CUDA(cudaMemcpyAsync(c->agree, &mine, sizeof mine, cudaMemcpyHostToDevice, c->comm_stream));
     if (int s = check_nccl(N, N->AllReduce(c->agree, c->agree, 1, kNcclFloat64, kNcclMin, c->comm, c->comm_stream), "ncclAllReduce"))
@@ -231,6 +243,7 @@ static int mg_dgemm_device(MgComm *c, cudaStream_t user, int64_t m, int64_t n, i
         }
         MG_CUDA(cudaEventRecord(c->t1, c->comm_stream));
         c->timed = true;
+        c->timed_which = 0;
         c->timed_bytes = 8.0 * (double)m * (double)k;
         l0 = 0;
         for (int p = 0; p < np; ++p) {
@@ -337,6 +350,7 @@ static int mg_dgemm_host(MgComm *c, cudaStream_t user, int64_t m, int64_t n, int
     }
     MG_CUDA(cudaEventRecord(c->t1, c->comm_stream));
     c->timed = c->world > 1;
+    c->timed_which = 1;
     c->timed_bytes = 8.0 * (double)m * (double)k;
 
     // All panels but the last are applied to the whole column block; the last one -- by plan the
@@ -506,6 +520,19 @@ extern "C" int ulmb200_mg_profile(void *handle, int on)
     if (on && !c->profile) c->profiled = 0;
     c->profile = on != 0;
     return set_status(ULMB200_OK);
+}
+
+extern "C" int ulmb200_mg_last_gemm_start_ms(void *handle, double *ms, int cap)
+{
+    MgComm *c = static_cast<MgComm *>(handle);
+    if (!c || !ms) return -1;
+    int n = 0;
+    for (; n < c->profiled && n < cap; ++n) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, c->t0, c->g0[n]) != cudaSuccess) { cudaGetLastError(); return -1; }
+        ms[n] = t;
+    }
+    return n;
 }
 
 extern "C" int ulmb200_mg_last_gemm_ms(void *handle, double *ms, int cap)

@@ -168,6 +168,12 @@ class ShardedDgemm:
         n = self.api.lib.ulmb200_mg_last_gemm_ms(self.handle, ms, 32)
         return [float(ms[i]) for i in range(max(n, 0))]
 
+    def last_gemm_start_ms(self):
+        """Start of each product of the last call, in ms after its first transfer was queued (world > 1)."""
+        ms = (C.c_double * 32)()
+        n = self.api.lib.ulmb200_mg_last_gemm_start_ms(self.handle, ms, 32)
+        return [float(ms[i]) for i in range(max(n, 0))]
+
     def last_plan(self):
         """(widths, reserve flags, measured device transport GB/s, measured host transport GB/s) of the last call."""
         w, r = (C.c_int64 * 32)(), (C.c_int * 32)()
