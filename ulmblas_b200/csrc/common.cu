@@ -67,6 +67,7 @@ static void read_settings()
     if (const char *e = getenv("ULMB200_DGEMM_TILE")) s.dgemm_tile = atoi(e);
     if (const char *e = getenv("ULMB200_DGEMM_PATH")) s.dgemm_ldg = (e[0] == 'l');
     if (const char *e = getenv("ULMB200_DGEMM_SPLITK")) s.dgemm_split = atoi(e);
+    if (const char *e = getenv("ULMB200_DGEMM_EPI")) s.dgemm_epi = atoi(e);
     if (const char *e = getenv("ULMB200_TRSM_LEAF")) s.trsm_leaf = atoi(e);
     if (const char *e = getenv("ULMB200_SGEMM_PRETRANSPOSE")) s.sgemm_pretranspose = atoi(e);
     if (const char *e = getenv("ULMB200_SGEMM_PATH")) s.sgemm_path = (e[0] == 'l');

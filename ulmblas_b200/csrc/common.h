@@ -66,6 +66,7 @@ struct Settings {
     int sgemm_3xtf32 = 0;
     int64_t workspace_cap = -1;          // bytes, -1 = none
     int dgemm_tile = 0, dgemm_ldg = 0, dgemm_split = 1;
+    int dgemm_epi = 0;            // test hook: epilogue cost (in pipeline stages) the share planner assumes, 0 = built in
     int sgemm_path = 0;                  // 0 auto, 1 force the plain-load kernel
     int sgemm_pretranspose = 1;          // 0: K-contiguous operands are always transposed inside the kernel
     int trsm_leaf = 0;                   // 0 auto
@@ -208,6 +209,15 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int32_t x, int32_t y, const void *smem_src)
 {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+
+// The same tile added to what global memory holds (one IEEE addition per element, done in the memory
+// system); part of the thread's current bulk group.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, int32_t x, int32_t y, const void *smem_src)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
                  : "memory");
 }

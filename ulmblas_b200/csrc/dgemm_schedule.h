@@ -31,6 +31,9 @@ constexpr int kRegionMax = 160;           // most tiles the shared region of a l
 // tile, about 9 us) in units of one pipeline stage of the main loop (2.1 us); only used to decide
 // whether sharing the last tiles pays.
 constexpr int kEpilogueStages = 4;
+// The same for a piece that leaves through the CTA's tile buffer: the consumers only write the buffer and go
+// on; one thread stores the head piece, or adds a later piece to C, with bulk tensor copies.
+constexpr int kBufferedEpilogueStages = 2;
 
 struct Piece {
     int r;          // index of the tile within the region
@@ -72,18 +75,18 @@ struct SharePlan {
 // adds one more epilogue at the end.  With unit boundaries on tile boundaries the pieces of a tile
 // all finish computing at the same moment and the whole chain is exposed: measured, such plans run
 // about 15 % over this count (1024^3 in two halves per tile, 200 x 3000 x 1000 in thirds).
-inline long long shared_cost(int rem, int kt, int nsu)
+inline long long shared_cost(int rem, int kt, int nsu, int epi = kEpilogueStages)
 {
     const long long S = (long long)rem * kt;
     const long long share = (S + nsu - 1) / nsu;
     const bool aligned = nsu % rem == 0;                       // unit boundaries fall on tile boundaries
     const long long pieces = aligned ? nsu / rem : (kt + share - 1) / share + 1;
     const long long own = aligned ? 1 : 2;                     // epilogues in a unit's own time line
-    const long long cost = share + (own + (pieces - 1)) * kEpilogueStages;
+    const long long cost = share + (own + (pieces - 1)) * epi;
     return aligned ? (cost * 115 + 99) / 100 : cost;
 }
 
-inline SharePlan plan_shared_tiles(long long nreal, int kt, int slots, bool force)
+inline SharePlan plan_shared_tiles(long long nreal, int kt, int slots, bool force, int epi = kEpilogueStages)
 {
     SharePlan none = {0, 0};
     if (slots < 2 || kt < 2) return none;
@@ -92,14 +95,14 @@ inline SharePlan plan_shared_tiles(long long nreal, int kt, int slots, bool forc
     const long long S = (long long)rem * kt;
     // candidates: every CTA takes part, or each tile is cut into p equal pieces (p = 2, 3, ...)
     int best = (int)(S < slots ? S : slots);
-    long long best_cost = best >= 2 ? shared_cost(rem, kt, best) : (1ll << 60);
+    long long best_cost = best >= 2 ? shared_cost(rem, kt, best, epi) : (1ll << 60);
     for (int p = 2; p <= 16 && (long long)rem * p <= slots && p <= kt; ++p) {
-        const long long c = shared_cost(rem, kt, rem * p);
+        const long long c = shared_cost(rem, kt, rem * p, epi);
         if (c < best_cost) { best_cost = c; best = rem * p; }
     }
     if (best < 2) return none;
     // one more wave of whole tiles costs kt stages and an epilogue
-    const bool pays = best_cost < kt + kEpilogueStages;
+    const bool pays = best_cost < kt + epi;
     if (!pays && !force) return none;
     SharePlan p = {rem, best};
     return p;

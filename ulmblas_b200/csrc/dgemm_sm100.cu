@@ -78,6 +78,10 @@ struct StashInfo {
     int load;                // beta != 0: the old tile is fetched into the buffer first
     int unit;                // -1: no more tiles
     int wait_idx, expect;    // leaf mode: the counter that must reach expect before C may be written, -1 = none
+    // piece of a shared tile: fold flag (-1 = none), the value it must show before this piece may be folded
+    // (0: the head, which waits for nothing), the value to leave there afterwards, and whether the piece is
+    // added to C (every piece but the head) instead of stored
+    int flag_idx, flag_wait, flag_pub, add;
 };
 
 // batch mode: coordinate shifts of product b
@@ -486,64 +490,115 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         __nanosleep(256);
             }
         }
-        if (STASH && warp == NCW + 1 && lane == 0 && p.c_tma) {
-            // ---------------- output thread ----------------
+        if (STASH && warp == NCW + 1 && p.c_tma) {
+            // ---------------- output warp ----------------
+            // Lane 0 (the output thread) does all the waiting and issues the bulk copies; the other lanes only
+            // help with the one row a store map cannot reach (below).
             for (uint32_t nt = 0;; ++nt) {
-                const StashInfo *I = info + (nt & 1);
-                if (*abort_flag) break;
-                if (!mbar_wait(tile_started, nt & 1)) {
-                    if (!*abort_flag) {                    // not merely left behind by consumers that gave up
-                        *abort_flag = 1;
-                        atomicExch(p.err, 105);
+                int row = 0, col = 0, flag_idx = -1, flag_pub = 0, add = 0;
+                int go = 0;
+                if (lane == 0) go = [&]() -> int {
+                    const StashInfo *I = info + (nt & 1);
+                    if (*abort_flag) return 0;
+                    if (!mbar_wait(tile_started, nt & 1)) {
+                        if (!*abort_flag) {                    // not merely left behind by consumers that gave up
+                            *abort_flag = 1;
+                            atomicExch(p.err, 105);
+                        }
+                        return 0;
                     }
-                    break;
-                }
-                if (I->unit < 0) break;
-                const int row = I->row, col = I->col;
-                const int wait_idx = I->wait_idx, expect = I->expect;
-                // the buffer is free: the stores of the tile before this one have read it (end of the loop body)
-                if (I->load) {
-                    mbar_expect_tx(stash_ready, BM * BN * 8);
+                    if (I->unit < 0) return 0;
+                    row = I->row; col = I->col;
+                    const int wait_idx = I->wait_idx, expect = I->expect, flag_wait = I->flag_wait;
+                    flag_idx = I->flag_idx; flag_pub = I->flag_pub; add = I->add;
+                    // the buffer is free: the stores of the tile before this one have read it (end of the loop body)
+                    if (I->load) {
+                        mbar_expect_tx(stash_ready, BM * BN * 8);
 #pragma unroll
-                    for (int b = 0; b < BN / CBOX; ++b)
-                        tma_load_2d(stash + b * CBOX * BM, &tmC, row, col + CBOX * b, stash_ready);
-                } else {
-                    mbar_arrive(stash_ready);
-                }
-                if (!mbar_wait(stash_full, nt & 1)) {
-                    if (!*abort_flag) {
-                        *abort_flag = 1;
-                        atomicExch(p.err, 105);
+                        for (int b = 0; b < BN / CBOX; ++b)
+                            tma_load_2d(stash + b * CBOX * BM, &tmC, row, col + CBOX * b, stash_ready);
+                    } else {
+                        mbar_arrive(stash_ready);
                     }
-                    break;
-                }
-                if (wait_idx >= 0) {
-                    // in-place leaf: the longer tiles of the strip must have read these rows (columns) first
-                    int *cnt = p.sched + 2 + wait_idx;
-                    bool ok = false;
-                    for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
-                        ok = *reinterpret_cast<volatile int *>(cnt) == expect;
-                        if (!ok) __nanosleep(64);
+                    if (!mbar_wait(stash_full, nt & 1)) {
+                        if (!*abort_flag) {
+                            *abort_flag = 1;
+                            atomicExch(p.err, 105);
+                        }
+                        return 0;
                     }
-                    if (!ok) { *abort_flag = 1; atomicExch(p.err, 104); break; }
-                    atomicExch(cnt, 0);                    // back to zero for the next launch on this stream
-                    __threadfence();
-                }
+                    if (wait_idx >= 0) {
+                        // in-place leaf: the longer tiles of the strip must have read these rows (columns) first
+                        int *cnt = p.sched + 2 + wait_idx;
+                        bool ok = false;
+                        for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                            ok = *reinterpret_cast<volatile int *>(cnt) == expect;
+                            if (!ok) __nanosleep(64);
+                        }
+                        if (!ok) { *abort_flag = 1; atomicExch(p.err, 104); return 0; }
+                        atomicExch(cnt, 0);                    // back to zero for the next launch on this stream
+                        __threadfence();
+                    }
+                    if (flag_idx >= 0 && flag_wait > 0) {
+                        // piece of a shared tile: the piece before it in k must be in C, completely
+                        int *flag = p.sched + 2 + flag_idx;
+                        bool ok = false;
+                        for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {
+                            ok = *reinterpret_cast<volatile int *>(flag) == flag_wait;
+                            if (!ok) __nanosleep(32);
+                        }
+                        if (!ok) { *abort_flag = 1; atomicExch(p.err, 103); return 0; }
+                        __threadfence();
+                        fence_proxy_async();                   // the bulk copies below come after what was just seen
+                    }
+                    if (add) {
+#pragma unroll
+                        for (int b = 0; b < BN / CBOX; ++b)
+                            tma_reduce_add_2d(&tmCs, row, col + CBOX * b, stash + b * CBOX * BM);
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < BN / CBOX; ++b)
+                            tma_store_2d(&tmCs, row, col + CBOX * b, stash + b * CBOX * BM);
+                    }
+                    bulk_commit_group();
+                    return 1;
+                }();
+                go = __shfl_sync(0xffffffffu, go, 0);
+                if (!go) break;
                 // A TMA store clips the rows of a tile in units of 16 bytes: with an odd number of rows it would
                 // write the element below the last one as well.  The store map therefore ends at the last even
-                // row, and the one row it leaves out is written here.
-#pragma unroll
-                for (int b = 0; b < BN / CBOX; ++b)
-                    tma_store_2d(&tmCs, row, col + CBOX * b, stash + b * CBOX * BM);
-                bulk_commit_group();
-                if ((p.c_m & 1) && (int64_t)row + BM >= p.c_m) {
-                    const int r = (int)(p.c_m - 1 - row);
-                    double *last = p.C + (p.c_m - 1) + (int64_t)col * p.ldc;
-                    for (int c = 0; c < BN && col + c < p.c_n; ++c) last[(int64_t)c * p.ldc] = stash[c * BM + r];
+                // row, and the one row it leaves out is written (or added to, in the memory system as well) by
+                // the lanes of this warp, a few columns each.
+                if (p.c_m & 1) {
+                    row = __shfl_sync(0xffffffffu, row, 0);
+                    if ((int64_t)row + BM >= p.c_m) {
+                        col = __shfl_sync(0xffffffffu, col, 0);
+                        add = __shfl_sync(0xffffffffu, add, 0);
+                        __syncwarp();
+                        const int r = (int)(p.c_m - 1 - row);
+                        double *last = p.C + (p.c_m - 1) + (int64_t)col * p.ldc;
+                        for (int c = lane; c < BN && col + c < p.c_n; c += 32) {
+                            double *at = last + (int64_t)c * p.ldc;
+                            if (add) atomicAdd(at, stash[c * BM + r]);
+                            else *at = stash[c * BM + r];
+                        }
+                        __threadfence();
+                        __syncwarp();
+                    }
                 }
-                bulk_wait_read_all();
+                if (lane == 0) {
+                    if (flag_idx >= 0) {
+                        // the next piece of the tile may follow once this one is in C, not merely read from the buffer
+                        bulk_wait_all();
+                        __threadfence();
+                        atomicExch(p.sched + 2 + flag_idx, flag_pub);
+                    } else {
+                        bulk_wait_read_all();
+                    }
+                }
+                __syncwarp();           // the buffer is not handed back before every lane has read its row of it
             }
-            bulk_wait_all();
+            if (lane == 0) bulk_wait_all();
         }
         return;
     }
@@ -596,6 +651,18 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             StashInfo *I = info + (nstash & 1);
             I->row = row; I->col = col; I->load = load ? 1 : 0;
             I->unit = unit; I->wait_idx = wait_idx; I->expect = expect;
+            I->flag_idx = -1; I->flag_wait = 0; I->flag_pub = 0; I->add = 0;
+            mbar_arrive(tile_started);
+        }
+    };
+    // The same for the piece [kc0, kc1) of shared tile r: the head is stored (beta applied), later pieces are
+    // added, each once the tile's flag shows that the piece before it is in C.
+    auto announce_piece = [&](int unit, int row, int col, int r, int kc0, int kc1) {
+        if (threadIdx.x == 0) {
+            StashInfo *I = info + (nstash & 1);
+            I->row = row; I->col = col; I->load = (kc0 == 0 && p.beta != 0.0) ? 1 : 0;
+            I->unit = unit; I->wait_idx = -1; I->expect = 0;
+            I->flag_idx = r; I->flag_wait = kc0; I->flag_pub = kc1 == kt ? 0 : kc1; I->add = kc0 > 0 ? 1 : 0;
             mbar_arrive(tile_started);
         }
     };
@@ -731,6 +798,15 @@ dgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!run_piece(pc.kc0, pc.kc1, first)) return;
                 first = false;
                 if (!stash_tile(p.beta)) return;
+                continue;
+            }
+            if (!whole && through_stash((int)m0, (int)n0)) {
+                // A piece of a shared tile leaves through the buffer as well: the consumers go on with their
+                // next piece while the output thread waits for the tile's turn (same order of k as below)
+                announce_piece(unit, (int)m0, (int)n0, pc.r, pc.kc0, pc.kc1);
+                if (!run_piece(pc.kc0, pc.kc1, first)) return;
+                first = false;
+                if (!stash_tile(pc.kc0 == 0 ? p.beta : 0.0)) return;
                 continue;
             }
             if (pc.kc0 > 0 || p.beta != 0.0) prefetch_c<MAJOR_A, MAJOR_B, MT, NT>(p, m0, n0, wm0, wn0, lane);
@@ -970,7 +1046,8 @@ static int launch_tma(cudaStream_t st, const GemmParams &p, const double *A, con
                 for (int tm = 0; tm < p.tiles_m; ++tm)
                     nreal += !tile_skipped(p.tri, (int64_t)tm * BM, (int64_t)tn * BN, BM, BN);
         }
-        const SharePlan sp = plan_shared_tiles(nreal, kt, slots, mode == 2);
+        const int epi = settings().dgemm_epi > 0 ? settings().dgemm_epi : (q.c_tma && p.tri == 0 ? kBufferedEpilogueStages : kEpilogueStages);
+        const SharePlan sp = plan_shared_tiles(nreal, kt, slots, mode == 2, epi);
         if (sp.nsu > 0) {
             int first = tiles, found = 0;
             while (first > 0 && found < sp.region_tiles) { --first; found += real(first); }
@@ -1022,7 +1099,7 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
     // can share the last tiles' stages among all CTAs; half tiles (128 x 64, one CTA per SM) put a product of
     // few large tiles on twice as many SMs; small tiles (64 x 64, two CTAs per SM) waste least on padding
     // and fill the machine with the fewest rows and columns.  Per-SM times in microseconds, measured on
-    // this part: one 16-k stage of a large tile 2.09, of a half tile 1.2, of a small tile 1.15 when two CTAs
+    // this part: one 16-k stage of a large tile 2.09, of a half tile 1.2, of a small tile 1.2 when two CTAs
     // share the SM (their operand traffic from L2 is twice the large tiles') and 0.70 when one has it
     // alone; an epilogue 1 (large and half tiles leave through shared memory beside the next tile's
     // main loop) / 2.
@@ -1031,16 +1108,19 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
     const int64_t t64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
     const int kt = (int)((p.k + kBK - 1) / kBK);
     const int sms = sm_count();
-    constexpr double kStage128 = 2.09, kStageHalf = 1.2, kStage64Pair = 1.15, kStage64Alone = 0.70, kEpi128 = 1.0,
+    constexpr double kStage128 = 2.09, kStageHalf = 1.2, kStage64Pair = 1.2, kStage64Alone = 0.70, kEpi128 = 1.0,
                      kEpi64 = 2.0;
     const bool sharing = tma_ok && may_share && p.sched && cfg.dgemm_split != 0 && p.tri == 0;
+    // pieces of shared tiles leave through the tile buffer when C can have a tensor map (as launch_tma decides)
+    const bool c_map = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 2 == 0 && p.m > 1;
+    const int epi = cfg.dgemm_epi > 0 ? cfg.dgemm_epi : (c_map ? kBufferedEpilogueStages : kEpilogueStages);
     // one CTA per SM: whole waves, the last one shared among all CTAs where that is cheaper
     auto one_per_sm = [&](int64_t tiles, double stage) {
         double t = (double)((tiles + sms - 1) / sms) * (kt * stage + kEpi128);
         if (sharing) {
-            const SharePlan sp = plan_shared_tiles(tiles, kt, sms, false);
+            const SharePlan sp = plan_shared_tiles(tiles, kt, sms, false, epi);
             if (sp.nsu > 0)
-                t = (double)(tiles / sms) * (kt * stage + kEpi128) + (double)shared_cost(sp.region_tiles, kt, sp.nsu) * stage;
+                t = (double)(tiles / sms) * (kt * stage + kEpi128) + (double)shared_cost(sp.region_tiles, kt, sp.nsu, epi) * stage;
         }
         return t;
     };
