@@ -175,6 +175,47 @@ def test_device_padding_below_an_odd_number_of_rows(ulm, torch_cuda, tile, monke
         assert ratio <= 1.0, (tile, m, n, k, ta, tb, beta, ratio)
 
 
+def test_shared_tile_pieces_with_an_odd_number_of_rows(ulm, torch_cuda, monkeypatch):
+    """Tiles shared among CTAs leave through the tile buffer piece by piece: the head is stored, the later
+    pieces are added to C by bulk tensor reductions in order of k.  With an odd number of rows the last row
+    of each piece is stored (or added) by the output warp's lanes.  Device-resident C with padding rows,
+    sharing forced on: full comparison, padding bit for bit, and bit-identical repeats."""
+    torch = torch_cuda
+    monkeypatch.setenv("ULMB200_DGEMM_TILE", "128")
+    monkeypatch.setenv("ULMB200_DGEMM_SPLITK", "2")
+    ulm.reload_env()
+    seed = 700
+    for (m, n, k, ta, tb, beta) in [(3001, 2047, 513, "N", "N", 1.3), (1001, 1001, 1001, "T", "N", 0.5), (1601, 1500, 520, "T", "T", 0.0),
+                                    (769, 641, 4099, "N", "T", 1.0), (129, 1100, 3000, "N", "N", -0.5)]:
+        seed += 5
+        ra, ca = (m, k) if ta == "N" else (k, m)
+        rb, cb = (k, n) if tb == "N" else (n, k)
+        lda, ldb, ldc = ra + (ra % 2), rb + 2 + (rb % 2), m + 3
+        A, B, C0 = det_uniform(seed, ra, ca), det_uniform(seed + 1, rb, cb), det_uniform(seed + 2, m, n)
+
+        def dev(h, ld):
+            t = torch.full((h.shape[1], ld), ROGUE, dtype=torch.float64, device="cuda")
+            t[:, :h.shape[0]] = torch.from_numpy(np.ascontiguousarray(h.T)).cuda()
+            return t
+        dA, dB, dC0 = dev(A, lda), dev(B, ldb), dev(C0, ldc)
+        want = reference_dgemm(ta, tb, m, n, k, -0.7, A, B, beta, C0, m)
+        gauge = gemm_gauge(-0.7, op(A, ta), op(B, tb), beta, C0)
+        first = None
+        for rep in range(3):
+            dC = dC0.clone()
+            ulm.dev_dgemm(ta == "T", tb == "T", m, n, k, -0.7, dA.data_ptr(), lda, dB.data_ptr(), ldb, beta, dC.data_ptr(), ldc)
+            torch.cuda.synchronize()
+            assert ulm.check_device_error() == 0
+            got = dC.cpu().numpy().T
+            assert (got[m:, :] == ROGUE).all(), (m, n, k, ta, tb, "padding rows of C were written")
+            if first is None:
+                first = got
+                ratio = bound_ratio(got[:m, :], want, gauge, k, EPS64)
+                assert ratio <= 1.0, (m, n, k, ta, tb, beta, ratio)
+            else:
+                assert np.array_equal(got, first), (m, n, k, rep, "results of identical calls differ")
+
+
 def test_golden_fixture_cases_on_gpu(ulm):
     """The committed outputs of the compiled reference, reproduced on the GPU within the bound."""
     for name, c in load_golden().items():
