@@ -58,7 +58,8 @@ int *sched_words(cudaStream_t st);
 //   ULMB200_TRACE=1              one line per call on stderr
 //   ULMB200_SGEMM=fp32|3xtf32    arithmetic of sgemm_ / cblas_sgemm
 //   ULMB200_WORKSPACE_CAP_MB=n   upper limit of the cached device work memory
-//   ULMB200_DGEMM_TILE=64|128, ULMB200_DGEMM_PATH=ldg, ULMB200_DGEMM_SPLITK=0   (test hooks)
+//   ULMB200_DGEMM_TILE=64|128|12864, ULMB200_DGEMM_PATH=ldg, ULMB200_DGEMM_SPLITK=0|2,
+//   ULMB200_DGEMM_EPI=n (epilogue cost, in pipeline stages, assumed by the share planner)   (test hooks)
 //   ULMB200_SGEMM_PRETRANSPOSE=0   never copy K-contiguous operands of sgemm (test hook)
 //   ULMB200_TRSM_LEAF=128|256|512|1024|2048   order of the diagonal blocks (leaves) of dtrsm and dtrmm (test hook)
 struct Settings {
