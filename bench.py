@@ -260,10 +260,12 @@ def main():
 
     for _ in range(a.warmup):
         step()
-    barrier()
+    # the sampler's child process is started before the barrier: forking a process with a CUDA context takes
+    # rank 0 (the root of every broadcast) some 20 ms, which the other ranks would spend inside their timed region
     sampler = ClockSampler(range(world)) if rank == 0 else None
     if sampler:
         sampler.start()
+    barrier()
     launches0 = ulm.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     eng.profile(True)            # CUDA events around every product, on the stream it is launched on

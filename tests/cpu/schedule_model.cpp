@@ -4,7 +4,9 @@
 //   * the pieces of a shared tile fold into C in order of k when the units run one after the
 //     other in increasing order (so a unit only ever waits for a unit picked up before it, and
 //     within that unit for its first pieces),
-//   * every fold flag is back at zero when the launch ends, and
+//   * every fold flag is back at zero when the launch ends (a CTA's output thread folds its pieces in
+//     the order its consumers multiplied them, so the same order holds for pieces that leave through
+//     the tile buffer), and
 //   * no unit's share is more than one stage longer than any other's.
 // Prints OK.
 #include <cstdio>
@@ -15,9 +17,9 @@
 
 using namespace ulmb200;
 
-static int check(long long nreal, int kt, int slots, bool force)
+static int check(long long nreal, int kt, int slots, bool force, int epi = kEpilogueStages)
 {
-    const SharePlan sp = plan_shared_tiles(nreal, kt, slots, force);
+    const SharePlan sp = plan_shared_tiles(nreal, kt, slots, force, epi);
     if (sp.nsu == 0) return 0;
     if (sp.region_tiles != nreal % slots || sp.region_tiles > kRegionMax || sp.nsu > slots || sp.nsu < 2) {
         printf("bad plan: nreal %lld kt %d slots %d -> region %d nsu %d\n", nreal, kt, slots, sp.region_tiles, sp.nsu);
@@ -67,13 +69,16 @@ int main()
     for (int slots : slot_list)
         for (int kt : {1, 2, 3, 8, 16, 17, 33, 64, 256, 1024})
             for (long long nreal = 1; nreal <= 3 * slots + 5; ++nreal)
-                for (int force = 0; force < 2; ++force) {
-                    bad += check(nreal, kt, slots, force != 0);
-                    ++plans;
-                }
+                for (int force = 0; force < 2; ++force)
+                    for (int epi : {kEpilogueStages, kBufferedEpilogueStages, 1}) {      // the planner's two cost settings, and a lower one
+                        bad += check(nreal, kt, slots, force != 0, epi);
+                        ++plans;
+                    }
     // the shapes the schedule was written for
     bad += check(64, 64, 148, false);        // 1024^3
     bad += check(384, 33, 148, false);       // 3001 x 2047 x 513
+    bad += check(384, 33, 148, false, kBufferedEpilogueStages);
+    bad += check(64, 64, 148, false, kBufferedEpilogueStages);
     bad += check(2080, 256, 148, false);     // triangle of order 8192, k = 4096
     bad += check(262144, 1024, 148, false);  // 65536 x 65536 x 16384
     if (plan_shared_tiles(64, 64, 148, false).nsu != 128) { printf("1024^3 is not cut into halves\n"); ++bad; }
