@@ -142,6 +142,14 @@ void cblas_dsyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo,
                  enum CBLAS_TRANSPOSE trans, int n, int k,
                  double alpha, const double *A, int ldA, double beta, double *C, int ldC);
 
+/* replaces CBLAS(strsm), interfaces/blas/C/trsm.cc:311-384, and CBLAS(ssyrk), syrk.cc:146-203     */
+void cblas_strsm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n,
+                 float alpha, const float *A, int ldA, float *B, int ldB);
+void cblas_ssyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE trans, int n, int k,
+                 float alpha, const float *A, int ldA, float beta, float *C, int ldC);
+
 /* column-major-only twins, ULMBLAS(dgemm) interfaces/blas/C/gemm.cc:76-138 ...*/
 void ulmblas_dgemm(enum CBLAS_TRANSPOSE transA, enum CBLAS_TRANSPOSE transB,
                    int m, int n, int k, double alpha, const double *A, int ldA,
@@ -154,6 +162,12 @@ void ulmblas_dtrsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
                    double alpha, const double *A, int ldA, double *B, int ldB);
 void ulmblas_dsyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k,
                    double alpha, const double *A, int ldA, double beta, double *C, int ldC);
+/* ULMBLAS(strsm) interfaces/blas/C/trsm.cc:12-80, ULMBLAS(ssyrk) syrk.cc:11-39 */
+void ulmblas_strsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                   enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n,
+                   float alpha, const float *A, int ldA, float *B, int ldB);
+void ulmblas_ssyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k,
+                   float alpha, const float *A, int ldA, float beta, float *C, int ldC);
 
 /* replace CBLAS(zgemm) and ULMBLAS(zgemm), interfaces/blas/C/gemm.cc:584-677, :219-292;
  * AtlasConj = conjugate without transposing                                            */

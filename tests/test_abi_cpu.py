@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(ulm):
     assert {"dgemm_", "sgemm_", "dtrsm_", "dsyrk_", "xerbla_", "cblas_dgemm", "cblas_sgemm",
             "cblas_dtrsm", "cblas_dsyrk", "cblas_xerbla", "ulmblas_dgemm", "ulmb200_dgemm",
             "ulmb200_sgemm", "ulmb200_dtrsm", "ulmb200_dsyrk", "zgemm_", "cblas_zgemm", "ulmblas_zgemm",
-            "ulmb200_zgemm"} <= set(funcs)
+            "ulmb200_zgemm", "cblas_strsm", "cblas_ssyrk", "ulmblas_strsm", "ulmblas_ssyrk"} <= set(funcs)
     for name in funcs:
         assert hasattr(ulm.lib, name), f"{name} is declared in include/ulmblas_b200.h but not exported"
     for name in data:
@@ -148,7 +148,7 @@ def test_error_exits_match_the_reference_case_by_case(ulm, tmp_path):
     routines = {r["routine"] for r in rows}
     assert {"dgemm_", "sgemm_", "zgemm_", "dtrsm_", "strsm_", "dtrmm_", "dsyrk_", "ssyrk_", "dsymm_", "dsyr2k_",
             "cblas_dgemm", "cblas_sgemm", "cblas_zgemm", "cblas_dtrsm", "cblas_dtrmm", "cblas_dsyrk",
-            "cblas_dsymm", "cblas_dsyr2k"} <= routines
+            "cblas_dsymm", "cblas_dsyr2k", "cblas_strsm", "cblas_ssyrk"} <= routines
     hook = str(tmp_path / "libxerbla_hook.so")
     subprocess.run(["gcc", "-shared", "-fPIC", "-o", hook, HOOK_SRC], check=True)
     code = _GOLDEN_DRIVER % dict(tests=os.path.join(ROOT, "tests"), root=ROOT, hook=hook, golden=golden)

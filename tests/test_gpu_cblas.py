@@ -6,7 +6,7 @@ leading dimension is one more than the row length; the padding is filled with th
 value and must come back untouched, inputs must come back bit-identical, and for triangular and
 symmetric operands the unreferenced triangle holds the rogue value too.  Results are compared
 with the compiled reference's own cblas_* (oracle/_ref/libulmref_cblas.so, interfaces/blas/C/
-gemm.cc:296-485, trsm.cc:387-459, syrk.cc:206-263) wherever that is finite, and against a float64
+gemm.cc:296-485, trsm.cc:311-459, syrk.cc:146-263) wherever that is finite, and against a float64
 numpy expectation under the componentwise bound everywhere."""
 import ctypes as C
 import itertools
@@ -30,7 +30,7 @@ def _reflib():
     if not oracle.have_ref("cblas"):
         return None
     L = C.CDLL(oracle.ref_path("cblas"))
-    for name in ("cblas_dgemm", "cblas_sgemm", "cblas_dtrsm", "cblas_dsyrk"):
+    for name in ("cblas_dgemm", "cblas_sgemm", "cblas_dtrsm", "cblas_dsyrk", "cblas_strsm", "cblas_ssyrk"):
         getattr(L, name).restype = None
     return L
 
@@ -169,34 +169,43 @@ def _tri(seed, na, upper_view, unit):
     return T, stored
 
 
-def _trsm_case(ulm, order, side, uplo, ta, diag, m, n, alpha, seed, twin=False):
+def _trsm_case(ulm, order, side, uplo, ta, diag, m, n, alpha, seed, twin=False, dtype=np.float64):
     na = m if side == LE else n
     T, stored = _tri(seed, na, uplo == UP, diag == UN)
     B0 = det_uniform(seed + 1, m, n)
+    single = dtype == np.float32
+    if single:
+        # the values the routine sees are the rounded ones; the expectation is formed from those in float64
+        T, stored, B0 = (x.astype(np.float32) for x in (T, stored, B0))
+    name = "strsm" if single else "dtrsm"
+    eps = EPS32 if single else EPS64
     mA, mB = Mat(order, stored), Mat(order, B0)
     got = mB.copy()
-    args = [C.c_int(side), C.c_int(uplo), C.c_int(ta), C.c_int(diag), C.c_int(m), C.c_int(n), C.c_double(alpha),
+    args = [C.c_int(side), C.c_int(uplo), C.c_int(ta), C.c_int(diag), C.c_int(m), C.c_int(n), _real(dtype)(alpha),
             mA.ptr, C.c_int(mA.ld), got.ptr, C.c_int(got.ld)]
-    f = getattr(ulm.lib, "ulmblas_dtrsm" if twin else "cblas_dtrsm")
+    T, B0 = T.astype(np.float64), B0.astype(np.float64)
+    f = getattr(ulm.lib, ("ulmblas_" if twin else "cblas_") + name)
     f.restype = None
     f(*(args if twin else [C.c_int(order)] + args))
     assert ulm.last_status() == ulm.OK
     assert mA.unchanged(), "the triangular operand was modified"
     assert got.padding_untouched(), "padding of B was written"
-    X = got.view
+    X = got.view.astype(np.float64)
     assert np.isfinite(X).all(), "the unreferenced triangle (rogue) leaked into the result"
     oT = opm(T, ta)
     # multiply back, the reference tester's check (test/F77/dblat3.f:1130-1155)
     back = oT @ X if side == LE else X @ oT
     gauge = (np.abs(oT) @ np.abs(X) if side == LE else np.abs(X) @ np.abs(oT)) + abs(alpha) * np.abs(B0)
-    assert bound_ratio(back, alpha * B0, gauge, na, EPS64) <= 1.0, (order, side, uplo, ta, diag, m, n)
+    assert bound_ratio(back, alpha * B0, gauge, na, eps) <= 1.0, (name, order, side, uplo, ta, diag, m, n)
     if REF is not None and not twin:
         ref = mB.copy()
-        REF.cblas_dtrsm(C.c_int(order), *args[:7], mA.ptr, C.c_int(mA.ld), ref.ptr, C.c_int(ref.ld))
+        getattr(REF, "cblas_" + name)(C.c_int(order), *args[:7], mA.ptr, C.c_int(mA.ld), ref.ptr, C.c_int(ref.ld))
         fin = np.isfinite(ref.view)          # the reference's SSE build can emit NaN on edge tiles
         assert fin.mean() > 0.5
         scale = max(1.0, np.abs(ref.view[fin]).max())
-        assert np.abs(X[fin] - ref.view[fin]).max() <= 1e-10 * scale, (order, side, uplo, ta, diag)
+        # the C interface's single-precision solve works in float throughout (trsm.cc:12-80): na roundings
+        tol = 16 * na * EPS32 if single else 1e-10
+        assert np.abs(X[fin] - ref.view[fin]).max() <= tol * scale, (name, order, side, uplo, ta, diag)
 
 
 @pytest.mark.parametrize("order", [COL, ROW])
@@ -217,18 +226,38 @@ def test_column_major_dtrsm_twin(ulm):
         _trsm_case(ulm, COL, side, uplo, ta, diag, 70, 45, 0.7, seed, twin=True)
 
 
+@pytest.mark.parametrize("order", [COL, ROW])
+def test_cblas_strsm_both_orders(ulm, order):
+    """Single precision through CBLAS(strsm) (trsm.cc:311-384) and its column-major twin: same sixteen
+    variants, multiply-back bound with the single-precision epsilon."""
+    seed = 45000 + (5 if order == ROW else 0)
+    for (m, n) in [(31, 12), (130, 70), (70, 257)]:
+        for side, uplo, ta, diag in itertools.product((LE, RI), (UP, LO), (NT, TR), (NU, UN)):
+            seed += 11
+            _trsm_case(ulm, order, side, uplo, ta, diag, m, n, 0.7 if (seed % 2) else 1.0, seed, dtype=np.float32)
+    if order == COL:
+        for side, uplo in itertools.product((LE, RI), (UP, LO)):
+            seed += 11
+            _trsm_case(ulm, COL, side, uplo, TR, NU, 70, 45, 0.7, seed, twin=True, dtype=np.float32)
+
+
 # ------------------------------------------------------------------------------------ syrk
 
-def _syrk_case(ulm, order, uplo, tr, n, k, alpha, beta, seed, twin=False):
-    A = det_uniform(seed, *((n, k) if tr == NT else (k, n)))
-    C0 = det_uniform(seed + 1, n, n)
+def _syrk_case(ulm, order, uplo, tr, n, k, alpha, beta, seed, twin=False, dtype=np.float64):
+    A = det_uniform(seed, *((n, k) if tr == NT else (k, n)), dtype)
+    C0 = det_uniform(seed + 1, n, n, dtype)
+    single = dtype == np.float32
+    name = "ssyrk" if single else "dsyrk"
+    eps = EPS32 if single else EPS64
+    ft = _real(dtype)
     tri = np.triu(np.ones((n, n), bool)) if uplo == UP else np.tril(np.ones((n, n), bool))
-    stored = np.where(tri, C0, ROGUE)
+    stored = np.where(tri, C0, dtype(ROGUE)).astype(dtype)
     mA, mC = Mat(order, A), Mat(order, stored)
     got = mC.copy()
-    args = [C.c_int(uplo), C.c_int(tr), C.c_int(n), C.c_int(k), C.c_double(alpha), mA.ptr, C.c_int(mA.ld),
-            C.c_double(beta), got.ptr, C.c_int(got.ld)]
-    f = getattr(ulm.lib, "ulmblas_dsyrk" if twin else "cblas_dsyrk")
+    args = [C.c_int(uplo), C.c_int(tr), C.c_int(n), C.c_int(k), ft(alpha), mA.ptr, C.c_int(mA.ld),
+            ft(beta), got.ptr, C.c_int(got.ld)]
+    A, C0 = A.astype(np.float64), C0.astype(np.float64)
+    f = getattr(ulm.lib, ("ulmblas_" if twin else "cblas_") + name)
     f.restype = None
     f(*(args if twin else [C.c_int(order)] + args))
     assert ulm.last_status() == ulm.OK
@@ -237,14 +266,15 @@ def _syrk_case(ulm, order, uplo, tr, n, k, alpha, beta, seed, twin=False):
     oa = opm(A, tr)
     want = alpha * (oa @ oa.T) + beta * C0
     gauge = abs(alpha) * (np.abs(oa) @ np.abs(oa.T)) + abs(beta) * np.abs(C0)
-    r = bound_ratio(np.where(tri, got.view, 0), np.where(tri, want, 0), gauge, k, EPS64)
-    assert r <= 1.0, (order, uplo, tr, n, k, r)
+    r = bound_ratio(np.where(tri, got.view, 0), np.where(tri, want, 0), gauge, k, eps)
+    # the float64 expectation is exact to 2^-52, the float result is rounded once more
+    assert r <= 1.0 + (0.5 if single else 0.0), (name, order, uplo, tr, n, k, r)
     if REF is not None and not twin:
         ref = mC.copy()
-        REF.cblas_dsyrk(C.c_int(order), *args[:6], C.c_int(mA.ld), C.c_double(beta), ref.ptr, C.c_int(ref.ld))
+        getattr(REF, "cblas_" + name)(C.c_int(order), *args[:6], C.c_int(mA.ld), ft(beta), ref.ptr, C.c_int(ref.ld))
         fin = np.isfinite(ref.view) & tri
-        r2 = bound_ratio(np.where(fin, got.view, 0), np.where(fin, ref.view, 0), gauge, k, EPS64)
-        assert r2 <= 1.0, ("vs reference", order, uplo, tr, n, k, r2)
+        r2 = bound_ratio(np.where(fin, got.view, 0), np.where(fin, ref.view, 0), gauge, k, eps)
+        assert r2 <= 1.0, (name, "vs reference", order, uplo, tr, n, k, r2)
 
 
 @pytest.mark.parametrize("order", [COL, ROW])
@@ -263,6 +293,21 @@ def test_column_major_dsyrk_twin(ulm):
     for uplo, tr in itertools.product((UP, LO), (NT, TR)):
         seed += 5
         _syrk_case(ulm, COL, uplo, tr, 70, 45, 0.7, 1.3, seed, twin=True)
+
+
+@pytest.mark.parametrize("order", [COL, ROW])
+def test_cblas_ssyrk_both_orders(ulm, order):
+    """Single precision through CBLAS(ssyrk) (syrk.cc:146-203) and its column-major twin."""
+    seed = 46000 + (5 if order == ROW else 0)
+    for (n, k) in [(31, 12), (130, 70), (257, 33)]:
+        for uplo, tr in itertools.product((UP, LO), (NT, TR)):
+            for alpha, beta in [(0.75, 1.25), (1.0, 0.0)]:
+                seed += 5
+                _syrk_case(ulm, order, uplo, tr, n, k, alpha, beta, seed, dtype=np.float32)
+    if order == COL:
+        for uplo, tr in itertools.product((UP, LO), (NT, TR)):
+            seed += 5
+            _syrk_case(ulm, COL, uplo, tr, 70, 45, 0.75, 1.25, seed, twin=True, dtype=np.float32)
 
 
 # ------------------------------------------------------------------- quick paths with dummy operands

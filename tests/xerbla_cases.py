@@ -88,8 +88,8 @@ def cases():
             cs += [(r, (order, BAD, BAD, -1, 3, 5, 4, 5, 4)), (r, (order, NT, NT, -1, -1, 5, 1, 1, 1)),
                    (r, (order, NT, NT, 4, 3, 5, 1, 1, 1))]
         cs += [(r, (BAD, BAD, NT, 4, 3, 5, 4, 5, 4))]
-    # cblas_dtrsm / cblas_dtrmm(order, side, uplo, ta, diag, m, n, lda, ldb)
-    for r in ("cblas_dtrsm", "cblas_dtrmm"):
+    # cblas_?trsm / cblas_dtrmm(order, side, uplo, ta, diag, m, n, lda, ldb)
+    for r in ("cblas_dtrsm", "cblas_strsm", "cblas_dtrmm"):
         for order in (COL, ROW):
             for side, uplo, ta, diag in [(LE, LO, NT, NU), (RI, UP, TR, UN), (LE, UP, CT, NU), (RI, LO, AC, UN)]:
                 m, n = 4, 3
@@ -99,15 +99,16 @@ def cases():
                 cs += [(r, a) for a in _variants(base, [BAD, BAD, BAD, BAD, BAD, -1, -1, dim - 1, ldb - 1])]
             cs += [(r, (order, LE, LO, NT, NU, -1, -1, 4, 4)), (r, (order, BAD, BAD, NT, NU, 4, 3, 4, 4)),
                    (r, (order, LE, LO, NT, NU, 4, 3, 1, 1))]
-    # cblas_dsyrk(order, uplo, trans, n, k, lda, ldc)
-    for order in (COL, ROW):
-        for uplo, tr in [(UP, NT), (LO, TR), (UP, CT), (LO, AC)]:
-            n, k = 4, 3
-            no = tr in (NT, AC)
-            rows = (n if no else k) if order == COL else (k if no else n)
-            base = (order, uplo, tr, n, k, rows, n)
-            cs += [("cblas_dsyrk", a) for a in _variants(base, [BAD, BAD, BAD, -1, -1, rows - 1, n - 1])]
-        cs += [("cblas_dsyrk", (order, UP, NT, -1, -1, 1, 1)), ("cblas_dsyrk", (order, UP, NT, 4, 3, 1, 1))]
+    # cblas_?syrk(order, uplo, trans, n, k, lda, ldc)
+    for r in ("cblas_dsyrk", "cblas_ssyrk"):
+        for order in (COL, ROW):
+            for uplo, tr in [(UP, NT), (LO, TR), (UP, CT), (LO, AC)]:
+                n, k = 4, 3
+                no = tr in (NT, AC)
+                rows = (n if no else k) if order == COL else (k if no else n)
+                base = (order, uplo, tr, n, k, rows, n)
+                cs += [(r, a) for a in _variants(base, [BAD, BAD, BAD, -1, -1, rows - 1, n - 1])]
+            cs += [(r, (order, UP, NT, -1, -1, 1, 1)), (r, (order, UP, NT, 4, 3, 1, 1))]
     # cblas_dsymm(order, side, uplo, m, n, lda, ldb, ldc)
     for order in (COL, ROW):
         for side, uplo in [(LE, UP), (RI, LO)]:

@@ -1083,6 +1083,45 @@ void cblas_sgemm(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE transA, enum CBLAS
     else                        ulmblas_sgemm(transB, transA, n, m, k, alpha, B, ldB, A, ldA, beta, C, ldC);
 }
 
+// First bad argument of CBLAS(?trsm), interfaces/blas/C/trsm.cc:325-371 (s) and :400-446 (d): the same
+// order of tests for both types; m and n change places in the row-major numbering.
+static int cblas_trsm_info(int order, int side, int upLo, int transA, int diag, int m, int n, int ldA, int ldB)
+{
+    const int rowsA = (side == CblasLeft) ? m : n;
+    if (order != CblasColMajor && order != CblasRowMajor) return 1;
+    if (side != CblasLeft && side != CblasRight) return 2;
+    if (upLo != CblasLower && upLo != CblasUpper) return 3;
+    if (!c_valid_trans((enum CBLAS_TRANSPOSE)transA)) return 4;
+    if (diag != CblasUnit && diag != CblasNonUnit) return 5;
+    if (order == CblasColMajor) {
+        if (m < 0) return 6;
+        if (n < 0) return 7;
+        if (ldA < std::max(1, rowsA)) return 10;
+        if (ldB < std::max(1, m)) return 12;
+    } else {
+        if (n < 0) return 6;
+        if (m < 0) return 7;
+        if (ldA < std::max(1, rowsA)) return 10;
+        if (ldB < std::max(1, n)) return 12;
+    }
+    return 0;
+}
+
+// First bad argument of CBLAS(?syrk), interfaces/blas/C/syrk.cc:158-190 (s) and :218-250 (d).
+static int cblas_syrk_info(int order, int upLo, int trans, int n, int k, int ldA, int ldC)
+{
+    if (order != CblasColMajor && order != CblasRowMajor) return 1;
+    if (upLo != CblasLower && upLo != CblasUpper) return 2;
+    if (!c_valid_trans((enum CBLAS_TRANSPOSE)trans)) return 3;
+    const bool no = c_notrans((enum CBLAS_TRANSPOSE)trans);
+    const int rowsA = order == CblasColMajor ? (no ? n : k) : (no ? k : n);
+    if (n < 0) return 4;
+    if (k < 0) return 5;
+    if (ldA < std::max(1, rowsA)) return 8;
+    if (ldC < std::max(1, n)) return 11;
+    return 0;
+}
+
 void ulmblas_dtrsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE transA,
                    enum CBLAS_DIAG diag, int m, int n, double alpha, const double *A, int ldA,
                    double *B, int ldB)
@@ -1095,24 +1134,7 @@ void cblas_dtrsm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO u
                  enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n, double alpha,
                  const double *A, int ldA, double *B, int ldB)
 {
-    const int rowsA = (side == CblasLeft) ? m : n;
-    int info = 0;
-    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
-    else if (side != CblasLeft && side != CblasRight) info = 2;
-    else if (upLo != CblasLower && upLo != CblasUpper) info = 3;
-    else if (!c_valid_trans(transA)) info = 4;
-    else if (diag != CblasUnit && diag != CblasNonUnit) info = 5;
-    else if (order == CblasColMajor) {
-        if (m < 0) info = 6;
-        else if (n < 0) info = 7;
-        else if (ldA < std::max(1, rowsA)) info = 10;
-        else if (ldB < std::max(1, m)) info = 12;
-    } else {
-        if (n < 0) info = 6;
-        else if (m < 0) info = 7;
-        else if (ldA < std::max(1, rowsA)) info = 10;
-        else if (ldB < std::max(1, n)) info = 12;
-    }
+    const int info = cblas_trsm_info(order, side, upLo, transA, diag, m, n, ldA, ldB);
     if (info != 0) {
         cblas_xerbla(info, "cblas_dtrsm", "");
         set_status(ULMB200_BAD_ARGUMENT);
@@ -1136,17 +1158,7 @@ void ulmblas_dsyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int 
 void cblas_dsyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n,
                  int k, double alpha, const double *A, int ldA, double beta, double *C, int ldC)
 {
-    int rowsA;
-    if (order == CblasColMajor) rowsA = c_notrans(trans) ? n : k;
-    else                        rowsA = c_notrans(trans) ? k : n;
-    int info = 0;
-    if (order != CblasColMajor && order != CblasRowMajor) info = 1;
-    else if (upLo != CblasLower && upLo != CblasUpper) info = 2;
-    else if (!c_valid_trans(trans)) info = 3;
-    else if (n < 0) info = 4;
-    else if (k < 0) info = 5;
-    else if (ldA < std::max(1, rowsA)) info = 8;
-    else if (ldC < std::max(1, n)) info = 11;
+    const int info = cblas_syrk_info(order, upLo, trans, n, k, ldA, ldC);
     if (info != 0) {
         cblas_xerbla(info, "cblas_dsyrk", "");
         set_status(ULMB200_BAD_ARGUMENT);
@@ -1157,6 +1169,59 @@ void cblas_dsyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSP
     } else {
         // interfaces/blas/C/syrk.cc:259-261
         ulmblas_dsyrk(upLo == CblasUpper ? CblasLower : CblasUpper,
+                      c_notrans(trans) ? CblasTrans : CblasNoTrans, n, k, alpha, A, ldA, beta, C, ldC);
+    }
+}
+
+// ---- single precision: CBLAS(strsm) interfaces/blas/C/trsm.cc:311-384, CBLAS(ssyrk) syrk.cc:146-203 ----
+// (the kernels accumulate in double and round once, as the Fortran entry points strsm_ / ssyrk_ do)
+
+void ulmblas_strsm(enum CBLAS_SIDE side, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE transA,
+                   enum CBLAS_DIAG diag, int m, int n, float alpha, const float *A, int ldA, float *B, int ldB)
+{
+    strsm_any(side == CblasLeft ? 0 : 1, upLo == CblasLower, !c_notrans(transA), diag == CblasUnit, m, n,
+              alpha, A, ldA, B, ldB);
+}
+
+void cblas_strsm(enum CBLAS_ORDER order, enum CBLAS_SIDE side, enum CBLAS_UPLO upLo,
+                 enum CBLAS_TRANSPOSE transA, enum CBLAS_DIAG diag, int m, int n, float alpha,
+                 const float *A, int ldA, float *B, int ldB)
+{
+    const int info = cblas_trsm_info(order, side, upLo, transA, diag, m, n, ldA, ldB);
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_strsm", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) {
+        ulmblas_strsm(side, upLo, transA, diag, m, n, alpha, A, ldA, B, ldB);
+    } else {
+        // interfaces/blas/C/trsm.cc:380-382
+        ulmblas_strsm(side == CblasLeft ? CblasRight : CblasLeft,
+                      upLo == CblasUpper ? CblasLower : CblasUpper, transA, diag, n, m, alpha, A, ldA, B, ldB);
+    }
+}
+
+void ulmblas_ssyrk(enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n, int k, float alpha,
+                   const float *A, int ldA, float beta, float *C, int ldC)
+{
+    ssyrk_any(upLo == CblasLower, !c_notrans(trans), n, k, alpha, A, ldA, beta, C, ldC);
+}
+
+void cblas_ssyrk(enum CBLAS_ORDER order, enum CBLAS_UPLO upLo, enum CBLAS_TRANSPOSE trans, int n,
+                 int k, float alpha, const float *A, int ldA, float beta, float *C, int ldC)
+{
+    const int info = cblas_syrk_info(order, upLo, trans, n, k, ldA, ldC);
+    if (info != 0) {
+        cblas_xerbla(info, "cblas_ssyrk", "");
+        set_status(ULMB200_BAD_ARGUMENT);
+        return;
+    }
+    if (order == CblasColMajor) {
+        ulmblas_ssyrk(upLo, trans, n, k, alpha, A, ldA, beta, C, ldC);
+    } else {
+        // interfaces/blas/C/syrk.cc:199-201
+        ulmblas_ssyrk(upLo == CblasUpper ? CblasLower : CblasUpper,
                       c_notrans(trans) ? CblasTrans : CblasNoTrans, n, k, alpha, A, ldA, beta, C, ldC);
     }
 }

@@ -1100,7 +1100,7 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
     // few large tiles on twice as many SMs; small tiles (64 x 64, two CTAs per SM) waste least on padding
     // and fill the machine with the fewest rows and columns.  Per-SM times in microseconds, measured on
     // this part: one 16-k stage of a large tile 2.09, of a half tile 1.2, of a small tile 1.2 when two CTAs
-    // share the SM (their operand traffic from L2 is twice the large tiles') and 0.70 when one has it
+    // share the SM (their operand traffic from L2 is twice the large tiles') and 0.85 when one has it
     // alone; an epilogue 1 (large and half tiles leave through shared memory beside the next tile's
     // main loop) / 2.
     const int64_t t128 = ((p.m + 127) / 128) * ((p.n + 127) / 128);
@@ -1108,7 +1108,7 @@ static int dispatch(cudaStream_t st, GemmParams p, bool tma_ok, bool may_share)
     const int64_t t64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
     const int kt = (int)((p.k + kBK - 1) / kBK);
     const int sms = sm_count();
-    constexpr double kStage128 = 2.09, kStageHalf = 1.2, kStage64Pair = 1.2, kStage64Alone = 0.70, kEpi128 = 1.0,
+    constexpr double kStage128 = 2.09, kStageHalf = 1.2, kStage64Pair = 1.2, kStage64Alone = 0.85, kEpi128 = 1.0,
                      kEpi64 = 2.0;
     const bool sharing = tma_ok && may_share && p.sched && cfg.dgemm_split != 0 && p.tri == 0;
     // pieces of shared tiles leave through the tile buffer when C can have a tensor map (as launch_tma decides)
