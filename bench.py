@@ -299,12 +299,20 @@ def main():
     ach_tf = (sum(kflops) / (sum(kdur) * 1e-3)) * 1e-12 if kdur and sum(kdur) > 0 else None
     # every rank's kernel time and pipe probe: the step ends with the slowest GPU
     rank_ms, rank_peak = [round(sum(kdur), 3)], [round(peak_tf, 2) if peak_tf else None]
+    rank_start, rank_gap = None, None
     if world > 1:
-        both = torch.tensor([sum(kdur), peak_tf or 0.0], dtype=torch.float64, device=dev)
+        starts = eng.last_gemm_start_ms()
+        gap = eng.last_step_gap_ms() if a.steps > 1 else None
+        both = torch.tensor([sum(kdur), peak_tf or 0.0, starts[0] if starts else -1.0, gap if gap is not None else -1.0],
+                            dtype=torch.float64, device=dev)
         gathered = [torch.zeros_like(both) for _ in range(world)]
         dist.all_gather(gathered, both)
         rank_ms = [round(float(g[0].item()), 3) for g in gathered]
         rank_peak = [round(float(g[1].item()), 2) for g in gathered]
+        # where a step's time goes besides the kernels: the wait for the first panel, and the time between the end
+        # of a rank's last product and the start of the next step's transfers (all ranks must have finished)
+        rank_start = [round(float(g[2].item()), 3) for g in gathered]
+        rank_gap = [round(float(g[3].item()), 3) for g in gathered]
 
     # parity on sampled rows x columns of this rank's block against the CPU oracle
     parity = None
@@ -354,7 +362,8 @@ def main():
                          "kernel": "dgemm_tma_kernel<128,128>", "launches_timed": len(kdur),
                          "launch_ms_last_step": [round(x, 3) for x in kdur],
                          "launch_start_ms_last_step": [round(x, 3) for x in eng.last_gemm_start_ms()] if world > 1 else None,
-                         "kernel_ms_last_step_by_rank": rank_ms, "peak_by_rank": rank_peak},
+                         "kernel_ms_last_step_by_rank": rank_ms, "peak_by_rank": rank_peak,
+                         "first_launch_start_ms_by_rank": rank_start, "ms_between_steps_by_rank": rank_gap},
             "cpu_baseline": cpu,
             "e2e": e2e,
             "gpu_launches": launches,

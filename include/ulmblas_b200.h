@@ -367,6 +367,11 @@ int ulmb200_mg_last_gemm_ms(void *handle, double *ms, int cap);
 /* When each of those products started, in ms after the call's first transfer was queued (device-resident
  * call on more than one rank; shows a product waiting for its panel).                                   */
 int ulmb200_mg_last_gemm_start_ms(void *handle, double *ms, int cap);
+/* Time between the end of the last product of the call before the last one and the moment the last call's
+ * first transfer was queued on the device (both calls device-resident, profiled, more than one rank): what a
+ * rank spends between two back-to-back calls, mostly waiting for the slowest rank.  0 on success, -1 when
+ * there are no two such calls.                                                                            */
+int ulmb200_mg_last_step_gap_ms(void *handle, double *ms);
 
 /* The persistent DGEMM grid normally takes every SM.  A caller that runs a collective
  * (e.g. the NCCL broadcast of the next A panel) beside it can ask the following DGEMM

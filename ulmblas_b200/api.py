@@ -127,6 +127,7 @@ lib.ulmb200_mg_set_rates.argtypes = [_vp, _dbl, _dbl, _dbl]
 lib.ulmb200_mg_profile.argtypes = [_vp, _int]
 lib.ulmb200_mg_last_gemm_ms.argtypes = [_vp, _pd, _int]
 lib.ulmb200_mg_last_gemm_start_ms.argtypes = [_vp, _pd, _int]
+lib.ulmb200_mg_last_step_gap_ms.argtypes = [_vp, _pd]
 
 CblasRowMajor, CblasColMajor = 101, 102
 CblasNoTrans, CblasTrans, CblasConjTrans, AtlasConj = 111, 112, 113, 114

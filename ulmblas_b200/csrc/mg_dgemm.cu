@@ -125,6 +125,8 @@ struct MgComm {
     bool profile = false;
     cudaEvent_t g0[kMgMaxPanels] = {}, g1[kMgMaxPanels] = {};
     int profiled = 0;
+    cudaEvent_t gend[2] = {};                    // end of the last product of the two latest profiled calls
+    int ended = 0;
     // what the last call did (ulmb200_mg_last_plan)
     int last_npanels = 0;
     int64_t last_widths[kMgMaxPanels] = {};
@@ -260,6 +262,12 @@ static int mg_dgemm_device(MgComm *c, cudaStream_t user, int64_t m, int64_t n, i
             l0 += widths[p];
         }
         c->profiled = (c->profile && nr > 0) ? np : 0;
+        if (c->profile) {
+            MG_CUDA(cudaEventRecord(c->gend[c->ended & 1], c->compute));
+            ++c->ended;
+        } else {
+            c->ended = 0;
+        }
         MG_TRY(stream_after(c, cursor, user, c->comm_stream));
     } else if (nr > 0) {
         if (c->profile) MG_CUDA(cudaEventRecord(c->g0[0], c->compute));
@@ -442,6 +450,8 @@ extern "C" int ulmb200_mg_init(const char id[128], int rank, int world, void **h
     if (e == cudaSuccess && world > 1) e = cudaMalloc(&c->agree, 64);
     if (e == cudaSuccess) e = cudaEventCreate(&c->t0);
     if (e == cudaSuccess) e = cudaEventCreate(&c->t1);
+    if (e == cudaSuccess) e = cudaEventCreate(&c->gend[0]);
+    if (e == cudaSuccess) e = cudaEventCreate(&c->gend[1]);
     if (e != cudaSuccess) { check_cuda(e, "stream/event creation", __FILE__, __LINE__); return fail(ULMB200_CUDA_ERROR); }
     *handle = c;
     return set_status(ULMB200_OK);
@@ -467,6 +477,8 @@ extern "C" int ulmb200_mg_finalize(void *handle)
     if (c->agree) cudaFree(c->agree);
     if (c->t0) cudaEventDestroy(c->t0);
     if (c->t1) cudaEventDestroy(c->t1);
+    for (cudaEvent_t e : c->gend)
+        if (e) cudaEventDestroy(e);
     delete c;
     return set_status(ULMB200_OK);
 }
@@ -533,6 +545,16 @@ extern "C" int ulmb200_mg_last_gemm_start_ms(void *handle, double *ms, int cap)
         ms[n] = t;
     }
     return n;
+}
+
+extern "C" int ulmb200_mg_last_step_gap_ms(void *handle, double *ms)
+{
+    MgComm *c = static_cast<MgComm *>(handle);
+    if (!c || !ms || c->world < 2 || c->ended < 2) return -1;
+    float t = 0.f;
+    if (cudaEventElapsedTime(&t, c->gend[c->ended & 1], c->t0) != cudaSuccess) { cudaGetLastError(); return -1; }
+    *ms = t;
+    return 0;
 }
 
 extern "C" int ulmb200_mg_last_gemm_ms(void *handle, double *ms, int cap)

@@ -174,6 +174,12 @@ class ShardedDgemm:
         n = self.api.lib.ulmb200_mg_last_gemm_start_ms(self.handle, ms, 32)
         return [float(ms[i]) for i in range(max(n, 0))]
 
+    def last_step_gap_ms(self):
+        """ms between the end of the previous call's last product and the start of the last call's transfers
+        (None unless the two latest calls were device-resident, profiled and on more than one rank)."""
+        ms = (C.c_double * 1)()
+        return float(ms[0]) if self.api.lib.ulmb200_mg_last_step_gap_ms(self.handle, ms) == 0 else None
+
     def last_plan(self):
         """(widths, reserve flags, measured device transport GB/s, measured host transport GB/s) of the last call."""
         w, r = (C.c_int64 * 32)(), (C.c_int * 32)()
