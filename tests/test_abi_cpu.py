@@ -214,6 +214,15 @@ def test_inplace_leaf_protocol_model(tmp_path):
     assert r.returncode == 0 and r.stdout.strip().startswith("OK"), r.stdout
 
 
+def test_buffered_piece_protocol_model(tmp_path):
+    """CPU model of shared tiles leaving piece by piece through each CTA's single tile buffer: pieces reach C in
+    order of k, nothing waits for a buffer or a flag for ever, flags end at zero."""
+    exe = str(tmp_path / "piece_model")
+    subprocess.run(["g++", "-O1", "-std=c++17", "-o", exe, os.path.join(ROOT, "tests", "cpu", "piece_model.cpp")], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip().startswith("OK"), r.stdout
+
+
 def test_trace_and_environment_reload(ulm, monkeypatch, capfd):
     """ULMB200_TRACE=1 prints one line per call; the environment is read once and again on request."""
     A = np.ones((4, 4), order="F")
