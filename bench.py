@@ -651,8 +651,37 @@ def other_configurations(ulm, torch, np, peak64):
         ulm.release_workspace()
     except (MemoryError, RuntimeError) as exc:
         e2e.append({"workload": "dgemm_ 16384^3 pageable", "unavailable": str(exc)})
+    try:
+        e2e.append(config1_e2e(ulm, np))
+    except Exception as exc:      # noqa: BLE001 - an extra figure must not take the bench line down
+        e2e.append({"workload": "dgemm_ 1024^3 pageable", "unavailable": str(exc)})
     return {"device_resident": out, "e2e_pageable": e2e, "checker": kind,
             "fp32_fma_peak_tflops": round(peak32, 2)}
+
+
+def config1_e2e(ulm, np):
+    """dgemm_ on config 1's shape with plain (pageable) host arrays: what a caller of the reference sees for a
+    small product, copies and launch included.  Best of five blocking calls, result checked in full."""
+    from oracle.inputs import EPS64
+    n = 1024
+    rng = np.random.default_rng(42)
+    A, B, C0 = (np.asfortranarray(rng.uniform(-1.0, 1.0, (n, n))) for _ in range(3))
+    want = 1.5 * (A @ B) + 0.5 * C0
+    gauge = 1.5 * (np.abs(A) @ np.abs(B)) + 0.5 * np.abs(C0)
+    ts, ok = [], True
+    for _ in range(6):
+        Cm = C0.copy(order="F")
+        t0 = time.perf_counter()
+        st = ulm.dgemm("N", "N", n, n, n, 1.5, A, B, 0.5, Cm)
+        ts.append(time.perf_counter() - t0)
+        if st != ulm.OK:
+            raise RuntimeError(ulm.status_string(st))
+        ok = ok and bool((np.abs(Cm - want) <= 2.0 * n * EPS64 * gauge).all())
+    best = min(ts[1:])
+    return {"workload": "dgemm_ 1024^3 (config 1 shape) alpha=1.5 beta=0.5, pageable host arrays, ulmb200_set_pin_host(0)",
+            "ms": round(1e3 * best, 3), "tflops": round(2.0 * n ** 3 / best * 1e-12, 3),
+            "h2d_bytes": 3 * 8 * n * n, "d2h_bytes": 8 * n * n, "result_checked": ok,
+            "timer": "host wall clock around the blocking call, best of five after one warm-up"}
 
 
 class SharedHostMatrix:
